@@ -1,0 +1,151 @@
+/*
+ * tq_b200.h — C ABI of the B200 (sm_100a) TurboQuant packed-KV library.
+ *
+ * Every entry point is extern "C", takes plain pointers and sizes, returns an
+ * int32 status (0 = ok, negative = error, see TQ_ERR_*), never throws and —
+ * except tq_ctx_create / tq_ctx_destroy — never allocates: the caller owns all
+ * device buffers and passes the CUDA stream to launch on.  Kernels are
+ * asynchronous on that stream.  A tq_ctx is bound to one device and may be used
+ * from one host thread at a time.
+ *
+ * The functions replace these pieces of the reference (paths relative to the
+ * reference project root):
+ *
+ *   tq_ctx_create       PackedMSELayer.lazy_initialization / _build_codebook_tensors
+ *                       src/turboquant/runtime/packed_qmse_cache.py:226-283
+ *   tq_pack             PackedMSELayer.initialize_from_dense, _encode_group,
+ *                       _encode_keys_qjl_group, and the quantize_decode=True branch of
+ *                       _update_lazy + PackedTensorMSE.append / PackedQJL.append
+ *                       src/turboquant/runtime/packed_qmse_cache.py:285-310,332-402,626-668,81-92,135-140
+ *   tq_decode_attn      fused_attention + _tile_attention_kernel + cross-tile reduce +
+ *                       dense-tail merge + un-rotation
+ *                       src/turboquant/runtime/triton_kernels.py:84-198,238-368
+ *                       (and, for batch > 1, chunked_turboquant_attention,
+ *                       src/turboquant/runtime/attention.py:215-304)
+ *   tq_dequant          _decode_group / _decode_keys_qjl_group / triton_decode_group
+ *                       src/turboquant/runtime/packed_qmse_cache.py:312-330,404-435
+ *                       src/turboquant/runtime/triton_kernels.py:36-55,227-236
+ *   tq_key_norm_mean    the per-layer mean key norm of build_packed_mse_cache
+ *                       src/turboquant/runtime/packed_qmse_cache.py:918-920
+ */
+#ifndef TQ_B200_H
+#define TQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TQ_OK 0
+#define TQ_ERR_ARG (-1)          /* null pointer, negative size, misaligned buffer */
+#define TQ_ERR_UNSUPPORTED (-2)  /* head_dim != 128, bits outside 2..4, too many query heads per KV head */
+#define TQ_ERR_CUDA (-3)         /* a CUDA runtime call failed; see tq_last_cuda_error */
+#define TQ_ERR_WORKSPACE (-4)    /* workspace smaller than tq_decode_workspace_bytes */
+
+#define TQ_DTYPE_F32 0
+#define TQ_DTYPE_F16 1
+#define TQ_DTYPE_BF16 2
+
+#define TQ_HEAD_DIM 128
+#define TQ_MAX_GROUPS 8 /* query heads per KV head */
+
+typedef struct tq_ctx tq_ctx;
+typedef void *tq_stream; /* a cudaStream_t */
+
+/* Codec set-up, all pointers to HOST memory, row-major float32.
+ *   rot_k, rot_v : [128][128] orthogonal rotations R; encode computes u @ R^T.
+ *                  For Q_mse (use_qjl = 0) pass the same matrix for both.
+ *   qjl          : [128][128] Gaussian projection S (NULL when use_qjl = 0).
+ *   centers_k/v  : 2^key_bits / 2^bits Lloyd-Max centres; bounds_k/v one fewer.
+ *                  key_bits = bits - 1 when use_qjl, else bits. */
+typedef struct {
+    int32_t head_dim; /* must be 128 */
+    int32_t bits;     /* 2, 3 or 4: total bits per coordinate */
+    int32_t use_qjl;  /* 1 = Q_prod keys (bits-1 Lloyd-Max + 1-bit QJL residual sketch) */
+    const float *rot_k;
+    const float *rot_v;
+    const float *qjl;
+    const float *centers_k;
+    const float *bounds_k;
+    const float *centers_v;
+    const float *bounds_v;
+} tq_codec_desc;
+
+/* The packed cache of one layer: six device streams, token axis innermost but one.
+ * Row (b, h) of a stream starts at element offset (b*stride_b + h*stride_h) tokens;
+ * a token is key_bits*16 bytes of k_codes, bits*16 bytes of v_codes, 16 bytes of
+ * k_signs, one fp16 for each norm stream.  With stride_h == capacity == n_tokens and
+ * stride_b == kv_heads*capacity, the first n_tokens of every row are byte-for-byte the
+ * reference's PackedTensorMSE.packed_indices / norms and PackedQJL tensors.
+ * All stream pointers must be 16-byte aligned and stride_b, stride_h multiples of 8. */
+typedef struct {
+    uint8_t *k_codes;
+    uint16_t *k_norms;  /* fp16 bit patterns */
+    uint8_t *k_signs;   /* NULL unless use_qjl */
+    uint16_t *k_rnorms; /* NULL unless use_qjl */
+    uint8_t *v_codes;
+    uint16_t *v_norms;
+    int32_t batch;
+    int32_t kv_heads;
+    int32_t capacity; /* tokens allocated per (b, h) row */
+    int64_t stride_b; /* in tokens */
+    int64_t stride_h; /* in tokens */
+} tq_cache_desc;
+
+/* A dense [batch, heads, tokens, 128] tensor with arbitrary outer strides (in elements);
+ * the last axis is contiguous. */
+typedef struct {
+    const void *data;
+    int32_t dtype; /* TQ_DTYPE_* */
+    int64_t stride_b;
+    int64_t stride_h;
+    int64_t stride_t;
+} tq_dense_desc;
+
+int32_t tq_abi_version(void);
+const char *tq_last_cuda_error(void);
+
+/* Allocates the device copy of the codec tables on `device` (the only allocating calls). */
+int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_desc *codec);
+int32_t tq_ctx_destroy(tq_ctx *ctx);
+
+/* Quantise n_tokens new tokens of K and V and write them at token positions
+ * [pos0, pos0 + n_tokens) of every (b, h) row of the cache: prefill packing
+ * (pos0 = 0) and the O(1) in-place append of a decoded token (n_tokens = 1). */
+int32_t tq_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,
+                const tq_cache_desc *cache, int32_t pos0, tq_stream stream);
+
+/* Bytes of scratch tq_decode_attn needs for this shape. */
+size_t tq_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t n_splits);
+/* A split count that fills the GPU for this shape (>= 1). */
+int32_t tq_decode_suggest_splits(tq_ctx *ctx, int32_t batch, int32_t kv_heads, int32_t seq_len);
+
+/* One decode step of attention straight from the packed cache.
+ *   q     : [batch, q_heads, 128] contiguous, dtype q_dtype (one query token per sequence)
+ *   out   : [batch, q_heads, 128] contiguous, same dtype (== [batch, 1, q_heads, 128])
+ *   seq_len tokens of every cache row are attended; softmax scale is 1/sqrt(128).
+ *   tail_k/tail_v (optional, may be NULL): n_tail un-quantised tokens
+ *   [batch, kv_heads, n_tail, 128] attended after the packed ones (quantize_decode = False).
+ * fp32 queries take an fp32-exact CUDA-core kernel; fp16/bf16 queries take the
+ * tensor-core kernel. */
+int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                       const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
+                       const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
+                       void *workspace, size_t workspace_bytes, void *out, tq_stream stream);
+
+/* Dequantise tokens [pos0, pos0 + n_tokens) of the keys (which = 0) or values (which = 1)
+ * into a dense [batch, kv_heads, n_tokens, 128] tensor of dtype out->dtype. */
+int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,
+                   int32_t n_tokens, const tq_dense_desc *out, tq_stream stream);
+
+/* Sum of the L2 norms of all key vectors of a dense tensor, accumulated into
+ * *sum_out (a device float64 the caller zeroes); mean = sum / (batch*heads*tokens). */
+int32_t tq_key_norm_sum(const tq_dense_desc *k, int32_t batch, int32_t heads, int32_t n_tokens,
+                        double *sum_out, tq_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TQ_B200_H */

@@ -1,0 +1,205 @@
+// C-ABI entry points: context life-cycle, argument checking, dispatch.
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <vector>
+
+#include "tq_common.cuh"
+
+static thread_local char g_err[256] = "";
+
+void tq_set_cuda_error(cudaError_t e, const char *where) {
+    snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));
+}
+
+extern "C" const char *tq_last_cuda_error(void) { return g_err; }
+extern "C" int32_t tq_abi_version(void) { return 1; }
+
+namespace {
+
+// Split a float into a TF32-representable high part (10 explicit mantissa bits,
+// truncated) and the remainder, so that hi + lo == x exactly in fp32.
+inline void split_tf32(float x, float *hi, float *lo) {
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    u &= 0xffffe000u;
+    float h;
+    memcpy(&h, &u, 4);
+    *hi = h;
+    float r = x - h;
+    memcpy(&u, &r, 4);
+    u &= 0xffffe000u;
+    memcpy(&r, &u, 4);
+    *lo = r;
+}
+
+}  // namespace
+
+extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_desc *c) {
+    if (!out || !c || !c->rot_k || !c->rot_v || !c->centers_k || !c->bounds_k || !c->centers_v || !c->bounds_v)
+        return TQ_ERR_ARG;
+    if (c->head_dim != TQ_D || c->bits < 2 || c->bits > 4) return TQ_ERR_UNSUPPORTED;
+    if (c->use_qjl && !c->qjl) return TQ_ERR_ARG;
+    TQ_CUDA_CHECK(cudaSetDevice(device));
+
+    const int kb = c->use_qjl ? c->bits - 1 : c->bits;
+    const size_t M = (size_t)TQ_D * TQ_D;
+    // 6 plain matrices + 8 split matrices + 4 tables of 16 floats.
+    const size_t n_float = 14 * M + 4 * 16;
+    std::vector<float> h(n_float, 0.0f);
+    auto mat = [&](int i) { return h.data() + (size_t)i * M; };
+    auto transpose = [&](const float *src, float *dst) {
+        for (int r = 0; r < TQ_D; ++r)
+            for (int cc = 0; cc < TQ_D; ++cc) dst[(size_t)cc * TQ_D + r] = src[(size_t)r * TQ_D + cc];
+    };
+    auto split = [&](const float *src, float *hi, float *lo) {
+        for (size_t i = 0; i < M; ++i) split_tf32(src[i], hi + i, lo + i);
+    };
+    memcpy(mat(0), c->rot_k, M * 4);
+    transpose(c->rot_k, mat(1));
+    memcpy(mat(2), c->rot_v, M * 4);
+    transpose(c->rot_v, mat(3));
+    if (c->use_qjl) {
+        memcpy(mat(4), c->qjl, M * 4);
+        transpose(c->qjl, mat(5));
+    }
+    split(mat(0), mat(6), mat(7));    // R_k
+    split(mat(2), mat(8), mat(9));    // R_v
+    split(mat(1), mat(10), mat(11));  // R_k^T
+    split(mat(4), mat(12), mat(13));  // S
+    float *tab = h.data() + 14 * M;
+    for (int i = 0; i < 16; ++i) {
+        tab[i] = i < (1 << kb) ? c->centers_k[i] : 0.0f;
+        tab[16 + i] = i < (1 << kb) - 1 ? c->bounds_k[i] : INFINITY;
+        tab[32 + i] = i < (1 << c->bits) ? c->centers_v[i] : 0.0f;
+        tab[48 + i] = i < (1 << c->bits) - 1 ? c->bounds_v[i] : INFINITY;
+    }
+
+    tq_ctx *ctx = new tq_ctx();
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->device = device;
+    ctx->bits = c->bits;
+    ctx->key_bits = kb;
+    ctx->use_qjl = c->use_qjl ? 1 : 0;
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) {
+        tq_set_cuda_error(e, "cudaGetDeviceProperties");
+        delete ctx;
+        return TQ_ERR_CUDA;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->base_bytes = n_float * sizeof(float);
+    e = cudaMalloc(&ctx->base, ctx->base_bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(ctx->base, h.data(), ctx->base_bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        tq_set_cuda_error(e, "tq_ctx_create upload");
+        if (ctx->base) cudaFree(ctx->base);
+        delete ctx;
+        return TQ_ERR_CUDA;
+    }
+    float *d = (float *)ctx->base;
+    auto dm = [&](int i) { return d + (size_t)i * M; };
+    ctx->rot_k = dm(0);
+    ctx->rot_k_t = dm(1);
+    ctx->rot_v = dm(2);
+    ctx->rot_v_t = dm(3);
+    ctx->qjl = dm(4);
+    ctx->qjl_t = dm(5);
+    ctx->rot_k_hi = dm(6);
+    ctx->rot_k_lo = dm(7);
+    ctx->rot_v_hi = dm(8);
+    ctx->rot_v_lo = dm(9);
+    ctx->rot_kT_hi = dm(10);
+    ctx->rot_kT_lo = dm(11);
+    ctx->qjl_hi = dm(12);
+    ctx->qjl_lo = dm(13);
+    ctx->centers_k = d + 14 * M;
+    ctx->bounds_k = ctx->centers_k + 16;
+    ctx->centers_v = ctx->centers_k + 32;
+    ctx->bounds_v = ctx->centers_k + 48;
+    *out = ctx;
+    return TQ_OK;
+}
+
+extern "C" int32_t tq_ctx_destroy(tq_ctx *ctx) {
+    if (!ctx) return TQ_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->base) cudaFree(ctx->base);
+    delete ctx;
+    return TQ_OK;
+}
+
+static int check_cache(const tq_ctx *ctx, const tq_cache_desc *c) {
+    if (!c || !c->k_codes || !c->k_norms || !c->v_codes || !c->v_norms) return TQ_ERR_ARG;
+    if (ctx->use_qjl && (!c->k_signs || !c->k_rnorms)) return TQ_ERR_ARG;
+    if (c->batch <= 0 || c->kv_heads <= 0 || c->capacity <= 0) return TQ_ERR_ARG;
+    if (c->stride_h < c->capacity || c->stride_b < (int64_t)c->kv_heads * c->stride_h) return TQ_ERR_ARG;
+    if ((c->stride_b & 7) || (c->stride_h & 7)) return TQ_ERR_ARG;
+    const uintptr_t all = (uintptr_t)c->k_codes | (uintptr_t)c->k_norms | (uintptr_t)c->v_codes |
+                          (uintptr_t)c->v_norms | (uintptr_t)c->k_signs | (uintptr_t)c->k_rnorms;
+    if (all & 15) return TQ_ERR_ARG;
+    return TQ_OK;
+}
+
+extern "C" int32_t tq_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,
+                           const tq_cache_desc *cache, int32_t pos0, tq_stream stream) {
+    if (!ctx || !k || !v || !k->data || !v->data) return TQ_ERR_ARG;
+    int rc = check_cache(ctx, cache);
+    if (rc) return rc;
+    if (n_tokens < 0 || pos0 < 0 || (int64_t)pos0 + n_tokens > cache->capacity) return TQ_ERR_ARG;
+    if (k->dtype != v->dtype || k->dtype < 0 || k->dtype > 2) return TQ_ERR_ARG;
+    if (n_tokens == 0) return TQ_OK;
+    return tq_launch_pack(ctx, k, v, n_tokens, cache, pos0, (cudaStream_t)stream);
+}
+
+extern "C" size_t tq_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t n_splits) {
+    if (batch <= 0 || q_heads <= 0 || n_splits <= 0) return 0;
+    // rotated query + projected query (+ padding row), then (max, sum, acc[128]) per split.
+    size_t rows = (size_t)batch * q_heads;
+    size_t floats = rows * (2 * TQ_D + 8) + rows * (size_t)n_splits * (TQ_D + 2);
+    return ((floats * 4 + 255) / 256) * 256;
+}
+
+extern "C" int32_t tq_decode_suggest_splits(tq_ctx *ctx, int32_t batch, int32_t kv_heads, int32_t seq_len) {
+    if (!ctx || batch <= 0 || kv_heads <= 0 || seq_len <= 0) return 1;
+    const int rows = batch * kv_heads;
+    const int target = ctx->sm_count * 4;  // CTAs wanted in flight
+    int splits = (target + rows - 1) / rows;
+    const int max_by_len = (seq_len + 255) / 256;  // at least 256 tokens per split
+    if (splits > max_by_len) splits = max_by_len;
+    if (splits < 1) splits = 1;
+    if (splits > 256) splits = 256;
+    return splits;
+}
+
+extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                                  const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
+                                  const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
+                                  void *workspace, size_t workspace_bytes, void *out, tq_stream stream) {
+    if (!ctx || !q || !out || !workspace) return TQ_ERR_ARG;
+    int rc = check_cache(ctx, cache);
+    if (rc) return rc;
+    if (q_dtype < 0 || q_dtype > 2) return TQ_ERR_ARG;
+    if (seq_len < 0 || seq_len > cache->capacity || n_tail < 0 || n_splits < 1) return TQ_ERR_ARG;
+    if (seq_len + n_tail == 0) return TQ_ERR_ARG;
+    if (n_tail > 0 && (!tail_k || !tail_v || !tail_k->data || !tail_v->data)) return TQ_ERR_ARG;
+    if (q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
+    if (q_heads / cache->kv_heads > TQ_MAX_GROUPS) return TQ_ERR_UNSUPPORTED;
+    if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)workspace) & 15) return TQ_ERR_ARG;
+    if (workspace_bytes < tq_decode_workspace_bytes(cache->batch, q_heads, n_splits)) return TQ_ERR_WORKSPACE;
+    return tq_launch_decode_exact(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
+                                  workspace, out, (cudaStream_t)stream);
+}
+
+extern "C" int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,
+                              int32_t n_tokens, const tq_dense_desc *out, tq_stream stream) {
+    if (!ctx || !out || !out->data) return TQ_ERR_ARG;
+    int rc = check_cache(ctx, cache);
+    if (rc) return rc;
+    if (which < 0 || which > 1 || out->dtype < 0 || out->dtype > 2) return TQ_ERR_ARG;
+    if (n_tokens < 0 || pos0 < 0 || (int64_t)pos0 + n_tokens > cache->capacity) return TQ_ERR_ARG;
+    if (n_tokens == 0) return TQ_OK;
+    return tq_launch_dequant(ctx, cache, which, pos0, n_tokens, out, (cudaStream_t)stream);
+}

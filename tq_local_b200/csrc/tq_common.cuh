@@ -1,0 +1,93 @@
+// Shared declarations for the sm_100a TurboQuant kernels: context layout, dtype
+// helpers, error plumbing.  Internal to the library; the public surface is
+// include/tq_b200.h.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tq_b200.h"
+
+#define TQ_D 128
+
+// Device-resident codec tables.  Matrices are [128][128] fp32, row-major.
+struct tq_ctx {
+    int device;
+    int bits;      // total bits
+    int key_bits;  // bits-1 with QJL, else bits
+    int use_qjl;
+    int sm_count;
+    float *rot_k;    // R_k[j][d]
+    float *rot_k_t;  // R_k^T[d][j]
+    float *rot_v;    // R_v[j][d]
+    float *rot_v_t;
+    float *qjl;      // S[i][d]
+    float *qjl_t;    // S^T[d][i]
+    float *centers_k;  // [16] (padded)
+    float *bounds_k;   // [16] (padded with +inf)
+    float *centers_v;
+    float *bounds_v;
+    // Split-precision copies for the tensor-core pack kernel (TF32 hi/lo parts).
+    float *rot_k_hi, *rot_k_lo;   // R_k      as [j][d] (B operand of u @ R_k^T, K-major)
+    float *rot_v_hi, *rot_v_lo;
+    float *rot_kT_hi, *rot_kT_lo; // R_k^T    as [d][j] (B operand of c @ R_k)
+    float *qjl_hi, *qjl_lo;       // S        as [i][d]
+    void *base;       // one allocation holding everything above
+    size_t base_bytes;
+};
+
+void tq_set_cuda_error(cudaError_t e, const char *where);
+
+#define TQ_CUDA_CHECK(expr)                         \
+    do {                                            \
+        cudaError_t _e = (expr);                    \
+        if (_e != cudaSuccess) {                    \
+            tq_set_cuda_error(_e, #expr);           \
+            return TQ_ERR_CUDA;                     \
+        }                                           \
+    } while (0)
+
+template <typename T> __device__ __forceinline__ float tq_to_float(T x);
+template <> __device__ __forceinline__ float tq_to_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ float tq_to_float<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float tq_to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T tq_from_float(float x);
+template <> __device__ __forceinline__ float tq_from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half tq_from_float<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 tq_from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// Round a float through storage type T and back (the reference's `.to(dtype).float()`).
+template <typename T> __device__ __forceinline__ float tq_round_through(float x) {
+    return tq_to_float<T>(tq_from_float<T>(x));
+}
+
+__device__ __forceinline__ float tq_half_bits_to_float(uint16_t h) {
+    return __half2float(__ushort_as_half(h));
+}
+__device__ __forceinline__ uint16_t tq_float_to_half_bits(float x) {
+    return __half_as_ushort(__float2half_rn(x));
+}
+
+__device__ __forceinline__ float tq_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float tq_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Entry points implemented in the other translation units.
+int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,
+                       const tq_cache_desc *cache, int32_t pos0, cudaStream_t stream);
+int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                               const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
+                               const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
+                               void *workspace, void *out, cudaStream_t stream);
+int32_t tq_launch_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,
+                          int32_t n_tokens, const tq_dense_desc *out, cudaStream_t stream);

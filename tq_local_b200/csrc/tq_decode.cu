@@ -1,0 +1,373 @@
+// Decode attention over the packed cache, fp32-exact CUDA-core variant, plus the
+// pieces every variant shares: query preparation (rotate / project) and the
+// split combine (+ dense tail merge + un-rotation).
+//
+//   logit[n] = (1/sqrt(D)) * ( |k_n| * <q R_k^T, c_k[idx_n]> + sqrt(pi/2)/D * |r_n| * <q S^T, sign_n> )
+//   out      = ( sum_n softmax(logit)_n * |v_n| * c_v[idx_n] ) @ R_v
+#include <math.h>
+
+#include "tq_common.cuh"
+#include "tq_decode_shared.cuh"
+
+namespace {
+
+constexpr int kExactWarps = 4;
+
+struct ExactArgs {
+    const uint8_t *k_codes;
+    const uint16_t *k_norms;
+    const uint8_t *k_signs;
+    const uint16_t *k_rnorms;
+    const uint8_t *v_codes;
+    const uint16_t *v_norms;
+    int64_t cache_sb, cache_sh;
+    int Hkv, G, N, n_splits;
+    const float *qrot;   // [B*Hq][128]
+    const float *qproj;  // [B*Hq][128]
+    float *part_m, *part_l, *part_acc;
+    const float *centers_k, *centers_v;
+};
+
+template <int BITS> __device__ __forceinline__ uint32_t code_at(const uint32_t *w, int j) {
+    const int o = j * BITS, wi = o >> 5, s = o & 31;
+    uint32_t v = w[wi] >> s;
+    if (s + BITS > 32) v |= w[wi + 1] << (32 - s);
+    return v & ((1u << BITS) - 1u);
+}
+
+template <int KB, int VB, bool QJL>
+__global__ void __launch_bounds__(kExactWarps * 32) tq_decode_exact_kernel(ExactArgs a) {
+    __shared__ float s_q[TQ_MAX_GROUPS][TQ_D];
+    __shared__ float s_qp[QJL ? TQ_MAX_GROUPS : 1][TQ_D];
+    __shared__ float s_ck[16], s_cv[16];
+    __shared__ float s_p[kExactWarps][TQ_MAX_GROUPS][32];
+    __shared__ float s_m[kExactWarps][TQ_MAX_GROUPS], s_l[kExactWarps][TQ_MAX_GROUPS];
+    __shared__ float s_acc[kExactWarps][TQ_MAX_GROUPS][TQ_D];
+
+    const int split = blockIdx.x;
+    const int bh = blockIdx.y;  // b * Hkv + h
+    const int b = bh / a.Hkv, h = bh % a.Hkv;
+    const int G = a.G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t q_row0 = ((int64_t)b * a.Hkv + h) * G;  // first query head of this KV head
+
+    for (int i = threadIdx.x; i < G * TQ_D; i += blockDim.x) {
+        s_q[i / TQ_D][i % TQ_D] = a.qrot[q_row0 * TQ_D + i];
+        if (QJL) s_qp[i / TQ_D][i % TQ_D] = a.qproj[q_row0 * TQ_D + i];
+    }
+    if (threadIdx.x < 16) {
+        s_ck[threadIdx.x] = a.centers_k[threadIdx.x];
+        s_cv[threadIdx.x] = a.centers_v[threadIdx.x];
+    }
+    __syncthreads();
+
+    const int chunks = (a.N + 31) / 32;
+    const int chunks_per_split = (chunks + a.n_splits - 1) / a.n_splits;
+    const int c_begin = split * chunks_per_split;
+    const int c_end = min(chunks, c_begin + chunks_per_split);
+    const int64_t row0 = (int64_t)b * a.cache_sb + (int64_t)h * a.cache_sh;
+    const float hs = 0.08838834764831845f;                    // 1/sqrt(128)
+    const float qjl_scale = 1.2533141373155003f / (float)TQ_D;  // sqrt(pi/2)/D
+
+    float m[TQ_MAX_GROUPS], l[TQ_MAX_GROUPS], acc[TQ_MAX_GROUPS][4];
+#pragma unroll
+    for (int g = 0; g < TQ_MAX_GROUPS; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+        acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+    }
+
+    for (int c = c_begin + warp; c < c_end; c += kExactWarps) {
+        const int base = c * 32;
+        const int tok = base + lane;
+        const bool valid = tok < a.N;
+        const int64_t row = row0 + (valid ? tok : base);
+        // ---- phase A: one token per lane, all G logits
+        uint32_t kw[4 * KB + 1];
+        {
+            const uint4 *src = (const uint4 *)(a.k_codes + row * (16 * KB));
+#pragma unroll
+            for (int i = 0; i < KB; ++i) {
+                const uint4 t = __ldg(src + i);
+                kw[4 * i] = t.x, kw[4 * i + 1] = t.y, kw[4 * i + 2] = t.z, kw[4 * i + 3] = t.w;
+            }
+            kw[4 * KB] = 0;
+        }
+        float dot[TQ_MAX_GROUPS];
+#pragma unroll
+        for (int g = 0; g < TQ_MAX_GROUPS; ++g) dot[g] = 0.f;
+#pragma unroll
+        for (int j = 0; j < TQ_D; ++j) {
+            const float cv = s_ck[code_at<KB>(kw, j)];
+#pragma unroll
+            for (int g = 0; g < TQ_MAX_GROUPS; ++g)
+                if (g < G) dot[g] = fmaf(cv, s_q[g][j], dot[g]);
+        }
+        const float kn = tq_half_bits_to_float(a.k_norms[row]);
+        float logit[TQ_MAX_GROUPS];
+#pragma unroll
+        for (int g = 0; g < TQ_MAX_GROUPS; ++g) logit[g] = dot[g] * kn * hs;
+        if (QJL) {
+            const uint4 sw4 = __ldg((const uint4 *)(a.k_signs + row * 16));
+            const uint32_t sw[4] = {sw4.x, sw4.y, sw4.z, sw4.w};
+            float dq[TQ_MAX_GROUPS];
+#pragma unroll
+            for (int g = 0; g < TQ_MAX_GROUPS; ++g) dq[g] = 0.f;
+#pragma unroll
+            for (int j = 0; j < TQ_D; ++j) {
+                const float sg = ((sw[j >> 5] >> (j & 31)) & 1u) ? 1.0f : -1.0f;
+#pragma unroll
+                for (int g = 0; g < TQ_MAX_GROUPS; ++g)
+                    if (g < G) dq[g] = fmaf(sg, s_qp[g][j], dq[g]);
+            }
+            const float rn = tq_half_bits_to_float(a.k_rnorms[row]);
+#pragma unroll
+            for (int g = 0; g < TQ_MAX_GROUPS; ++g) logit[g] += qjl_scale * rn * dq[g] * hs;
+        }
+        // ---- phase B: online softmax over the 32 tokens of the chunk
+        const float vn = tq_half_bits_to_float(a.v_norms[row]);
+        __syncwarp();
+#pragma unroll
+        for (int g = 0; g < TQ_MAX_GROUPS; ++g) {
+            if (g < G) {
+                const float lg = valid ? logit[g] : -INFINITY;
+                const float nm = fmaxf(m[g], tq_warp_max(lg));
+                const float corr = (m[g] == -INFINITY) ? 0.f : expf(m[g] - nm);
+                const float p = valid ? expf(lg - nm) : 0.f;
+                l[g] = l[g] * corr + tq_warp_sum(p);
+                acc[g][0] *= corr, acc[g][1] *= corr, acc[g][2] *= corr, acc[g][3] *= corr;
+                m[g] = nm;
+                s_p[warp][g][lane] = p * vn;
+            }
+        }
+        __syncwarp();
+        // ---- phase C: lane owns value dims 4*lane..4*lane+3
+        const int n_here = min(32, a.N - base);
+        for (int t = 0; t < n_here; ++t) {
+            const uint8_t *vr = a.v_codes + (row0 + base + t) * (16 * VB);
+            uint32_t v;
+            if (VB == 2) {
+                v = vr[lane];
+            } else if (VB == 4) {
+                v = ((const uint16_t *)vr)[lane];
+            } else {  // 3 bits: 12 bits starting at bit 12*lane
+                const int by = (3 * lane) >> 1;
+                v = ((uint32_t)vr[by] | ((uint32_t)vr[by + 1] << 8)) >> ((lane & 1) * 4);
+            }
+            float cv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cv[i] = s_cv[(v >> (VB * i)) & ((1u << VB) - 1u)];
+#pragma unroll
+            for (int g = 0; g < TQ_MAX_GROUPS; ++g) {
+                if (g < G) {
+                    const float w = s_p[warp][g][t];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[g][i] = fmaf(w, cv[i], acc[g][i]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    // ---- merge the warps of this CTA and write the split partial
+#pragma unroll
+    for (int g = 0; g < TQ_MAX_GROUPS; ++g) {
+        if (g < G) {
+            if (lane == 0) s_m[warp][g] = m[g], s_l[warp][g] = l[g];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s_acc[warp][g][4 * lane + i] = acc[g][i];
+        }
+    }
+    __syncthreads();
+    const int d = threadIdx.x;  // 128 threads == 128 dims
+    for (int g = 0; g < G; ++g) {
+        float M = -INFINITY;
+        for (int w = 0; w < kExactWarps; ++w) M = fmaxf(M, s_m[w][g]);
+        float L = 0.f, A = 0.f;
+        for (int w = 0; w < kExactWarps; ++w) {
+            const float sc = (s_m[w][g] == -INFINITY) ? 0.f : expf(s_m[w][g] - M);
+            L += s_l[w][g] * sc;
+            A += s_acc[w][g][d] * sc;
+        }
+        const int64_t prow = (q_row0 + g) * a.n_splits + split;
+        a.part_acc[prow * TQ_D + d] = A;
+        if (d == 0) a.part_m[prow] = M, a.part_l[prow] = L;
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Shared pieces: query preparation and split combine
+// ---------------------------------------------------------------------------
+
+template <typename T>
+__global__ void __launch_bounds__(TQ_D) tq_qprep_kernel(const T *q, const float *rot_k_t, const float *qjl_t,
+                                                       float *qrot, float *qproj, int use_qjl) {
+    __shared__ float s_q[TQ_D];
+    const int64_t row = blockIdx.x;
+    const int j = threadIdx.x;
+    s_q[j] = tq_to_float<T>(q[row * TQ_D + j]);
+    __syncthreads();
+    float r = 0.f, p = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < TQ_D; ++d) r = fmaf(s_q[d], __ldg(rot_k_t + d * TQ_D + j), r);
+    qrot[row * TQ_D + j] = r;
+    if (use_qjl) {
+#pragma unroll 8
+        for (int d = 0; d < TQ_D; ++d) p = fmaf(s_q[d], __ldg(qjl_t + d * TQ_D + j), p);
+        qproj[row * TQ_D + j] = p;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(TQ_D) tq_combine_kernel(CombineArgs a) {
+    extern __shared__ float s_dyn[];  // tail logits
+    __shared__ float s_o[TQ_D];
+    __shared__ float s_q[TQ_D];
+    __shared__ float s_red[4];
+    const int64_t row = blockIdx.x;  // b * Hq + hq
+    const int e = threadIdx.x;
+    const int warp = e >> 5, lane = e & 31;
+    const int b = (int)(row / a.Hq), hq = (int)(row % a.Hq);
+    const float hs = 0.08838834764831845f;
+
+    float M = -INFINITY;
+    for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, a.part_m[row * a.n_splits + s]);
+
+    // dense tail logits (quantize_decode = False buffer)
+    const T *tk = nullptr, *tv = nullptr;
+    if (a.n_tail > 0) {
+        const int hkv = hq / a.G;
+        tk = (const T *)a.tail_k + b * a.tk_sb + hkv * a.tk_sh;
+        tv = (const T *)a.tail_v + b * a.tv_sb + hkv * a.tv_sh;
+        s_q[e] = tq_to_float<T>(((const T *)a.q)[row * TQ_D + e]);
+        __syncthreads();
+        float wmax = -INFINITY;
+        for (int t = warp; t < a.n_tail; t += 4) {
+            const T *kr = tk + (int64_t)t * a.tk_st + 4 * lane;
+            float dsum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dsum = fmaf(s_q[4 * lane + i], tq_to_float<T>(kr[i]), dsum);
+            dsum = tq_warp_sum(dsum) * hs;
+            if (lane == 0) s_dyn[t] = dsum;
+            wmax = fmaxf(wmax, dsum);
+        }
+        if (lane == 0) s_red[warp] = wmax;
+        __syncthreads();
+        M = fmaxf(M, fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3])));
+    }
+
+    float L = 0.f, o = 0.f;
+    for (int s = 0; s < a.n_splits; ++s) {
+        const float ms = a.part_m[row * a.n_splits + s];
+        const float w = (ms == -INFINITY) ? 0.f : expf(ms - M);
+        L += a.part_l[row * a.n_splits + s] * w;
+        o += a.part_acc[(row * a.n_splits + s) * TQ_D + e] * w;
+    }
+    s_o[e] = o;
+    __syncthreads();
+    float out = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < TQ_D; ++d) out = fmaf(s_o[d], __ldg(a.rot_v + d * TQ_D + e), out);
+    for (int t = 0; t < a.n_tail; ++t) {
+        const float p = expf(s_dyn[t] - M);
+        L += p;
+        out = fmaf(p, tq_to_float<T>(tv[(int64_t)t * a.tv_st + e]), out);
+    }
+    ((T *)a.out)[row * TQ_D + e] = tq_from_float<T>(out / fmaxf(L, 1e-8f));
+}
+
+int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
+                        cudaStream_t stream) {
+    if (q_dtype == TQ_DTYPE_F32)
+        tq_qprep_kernel<float><<<(unsigned)rows, TQ_D, 0, stream>>>((const float *)q, ctx->rot_k_t, ctx->qjl_t, qrot,
+                                                                    qproj, ctx->use_qjl);
+    else if (q_dtype == TQ_DTYPE_F16)
+        tq_qprep_kernel<__half><<<(unsigned)rows, TQ_D, 0, stream>>>((const __half *)q, ctx->rot_k_t, ctx->qjl_t,
+                                                                     qrot, qproj, ctx->use_qjl);
+    else
+        tq_qprep_kernel<__nv_bfloat16><<<(unsigned)rows, TQ_D, 0, stream>>>((const __nv_bfloat16 *)q, ctx->rot_k_t,
+                                                                            ctx->qjl_t, qrot, qproj, ctx->use_qjl);
+    TQ_CUDA_CHECK(cudaGetLastError());
+    return TQ_OK;
+}
+
+int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, cudaStream_t stream) {
+    const size_t dyn = (size_t)a.n_tail * sizeof(float);
+    if (dyn > 40 * 1024) return TQ_ERR_UNSUPPORTED;
+    if (q_dtype == TQ_DTYPE_F32)
+        tq_combine_kernel<float><<<(unsigned)rows, TQ_D, dyn, stream>>>(a);
+    else if (q_dtype == TQ_DTYPE_F16)
+        tq_combine_kernel<__half><<<(unsigned)rows, TQ_D, dyn, stream>>>(a);
+    else
+        tq_combine_kernel<__nv_bfloat16><<<(unsigned)rows, TQ_D, dyn, stream>>>(a);
+    TQ_CUDA_CHECK(cudaGetLastError());
+    return TQ_OK;
+}
+
+DecodeWorkspace tq_carve_workspace(void *workspace, int64_t rows, int n_splits) {
+    DecodeWorkspace w;
+    float *p = (float *)workspace;
+    w.qrot = p;
+    p += rows * TQ_D;
+    w.qproj = p;
+    p += rows * TQ_D;
+    p += rows * 8;
+    w.part_m = p;
+    p += rows * n_splits;
+    w.part_l = p;
+    p += rows * n_splits;
+    w.part_acc = p;
+    return w;
+}
+
+int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                               const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
+                               const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits, void *workspace,
+                               void *out, cudaStream_t stream) {
+    const int64_t rows = (int64_t)cache->batch * q_heads;
+    DecodeWorkspace w = tq_carve_workspace(workspace, rows, n_splits);
+    int rc = tq_launch_qprep(ctx, q, q_dtype, rows, w.qrot, w.qproj, stream);
+    if (rc) return rc;
+
+    ExactArgs a;
+    a.k_codes = cache->k_codes, a.k_norms = cache->k_norms;
+    a.k_signs = cache->k_signs, a.k_rnorms = cache->k_rnorms;
+    a.v_codes = cache->v_codes, a.v_norms = cache->v_norms;
+    a.cache_sb = cache->stride_b, a.cache_sh = cache->stride_h;
+    a.Hkv = cache->kv_heads, a.G = q_heads / cache->kv_heads, a.N = seq_len, a.n_splits = n_splits;
+    a.qrot = w.qrot, a.qproj = w.qproj;
+    a.part_m = w.part_m, a.part_l = w.part_l, a.part_acc = w.part_acc;
+    a.centers_k = ctx->centers_k, a.centers_v = ctx->centers_v;
+    dim3 grid(n_splits, cache->batch * cache->kv_heads);
+    const int threads = kExactWarps * 32;
+    const int mode = ctx->use_qjl * 10 + ctx->bits;
+    switch (mode) {
+        case 2: tq_decode_exact_kernel<2, 2, false><<<grid, threads, 0, stream>>>(a); break;
+        case 3: tq_decode_exact_kernel<3, 3, false><<<grid, threads, 0, stream>>>(a); break;
+        case 4: tq_decode_exact_kernel<4, 4, false><<<grid, threads, 0, stream>>>(a); break;
+        case 12: tq_decode_exact_kernel<1, 2, true><<<grid, threads, 0, stream>>>(a); break;
+        case 13: tq_decode_exact_kernel<2, 3, true><<<grid, threads, 0, stream>>>(a); break;
+        case 14: tq_decode_exact_kernel<3, 4, true><<<grid, threads, 0, stream>>>(a); break;
+        default: return TQ_ERR_UNSUPPORTED;
+    }
+    TQ_CUDA_CHECK(cudaGetLastError());
+
+    CombineArgs c;
+    c.part_m = w.part_m, c.part_l = w.part_l, c.part_acc = w.part_acc;
+    c.n_splits = n_splits, c.Hq = q_heads, c.G = a.G;
+    c.rot_v = ctx->rot_v;
+    c.q = q, c.out = out;
+    c.n_tail = n_tail;
+    c.tail_k = n_tail ? tail_k->data : nullptr;
+    c.tail_v = n_tail ? tail_v->data : nullptr;
+    if (n_tail) {
+        if (tail_k->dtype != q_dtype || tail_v->dtype != q_dtype) return TQ_ERR_ARG;
+        c.tk_sb = tail_k->stride_b, c.tk_sh = tail_k->stride_h, c.tk_st = tail_k->stride_t;
+        c.tv_sb = tail_v->stride_b, c.tv_sh = tail_v->stride_h, c.tv_st = tail_v->stride_t;
+    } else {
+        c.tk_sb = c.tk_sh = c.tk_st = c.tv_sb = c.tv_sh = c.tv_st = 0;
+    }
+    return tq_launch_combine(c, q_dtype, rows, stream);
+}

@@ -1,0 +1,174 @@
+"""Device storage of one layer's packed KV cache and the calls that touch it.
+
+Layout in HBM (all streams row-major, token axis second to last):
+
+    k_codes  uint8 [B, Hkv, capacity, 16*key_bits]   LSB-first bitstream per token
+    k_norms  fp16  [B, Hkv, capacity]
+    k_signs  uint8 [B, Hkv, capacity, 16]            (Q_prod only) 1 bit per coordinate
+    k_rnorms fp16  [B, Hkv, capacity]                (Q_prod only)
+    v_codes  uint8 [B, Hkv, capacity, 16*bits]
+    v_norms  fp16  [B, Hkv, capacity]
+
+``[:, :, :length]`` of each stream is byte-for-byte what the reference keeps in
+``PackedTensorMSE.packed_indices`` / ``.norms`` and ``PackedQJL.packed_signs`` /
+``.residual_norms`` (``src/turboquant/runtime/packed_qmse_cache.py:58-92,121-140``).
+The spare capacity makes the append of a decoded token an in-place write
+instead of the reference's ``torch.cat`` of the whole cache.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from tq_local_b200.runtime import ffi
+from tq_local_b200.runtime.codec import Codec, dense_desc, tq_dtype
+
+
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+class PackedStore:
+    def __init__(self, codec: Codec, batch: int, kv_heads: int, capacity: int):
+        self.codec = codec
+        self.batch, self.kv_heads = int(batch), int(kv_heads)
+        self.length = 0
+        self._alloc(max(8, _round_up(int(capacity), 8)))
+        self._workspace: torch.Tensor | None = None
+
+    # ------------------------------------------------------------------ storage
+    def _alloc(self, capacity: int) -> None:
+        dev, b, h = self.codec.device, self.batch, self.kv_heads
+        u8 = dict(dtype=torch.uint8, device=dev)
+        f16 = dict(dtype=torch.float16, device=dev)
+        self.capacity = capacity
+        self.k_codes = torch.empty(b, h, capacity, 16 * self.codec.key_bits, **u8)
+        self.k_norms = torch.empty(b, h, capacity, **f16)
+        self.v_codes = torch.empty(b, h, capacity, 16 * self.codec.bits, **u8)
+        self.v_norms = torch.empty(b, h, capacity, **f16)
+        if self.codec.use_qjl:
+            self.k_signs = torch.empty(b, h, capacity, 16, **u8)
+            self.k_rnorms = torch.empty(b, h, capacity, **f16)
+        else:
+            self.k_signs = self.k_rnorms = None
+        self._desc = ffi.CacheDesc(
+            self.k_codes.data_ptr(), self.k_norms.data_ptr(),
+            self.k_signs.data_ptr() if self.k_signs is not None else None,
+            self.k_rnorms.data_ptr() if self.k_rnorms is not None else None,
+            self.v_codes.data_ptr(), self.v_norms.data_ptr(),
+            b, h, capacity, h * capacity, capacity,
+        )
+
+    def streams(self) -> list[torch.Tensor]:
+        return [t for t in (self.k_codes, self.k_norms, self.k_signs, self.k_rnorms, self.v_codes, self.v_norms)
+                if t is not None]
+
+    def reserve(self, capacity: int) -> None:
+        """Grow to at least ``capacity`` tokens per row, keeping the stored tokens."""
+        if capacity <= self.capacity:
+            return
+        old = self.streams()
+        n = self.length
+        self._alloc(_round_up(max(capacity, 2 * self.capacity), 8))
+        for src, dst in zip(old, self.streams()):
+            dst[:, :, :n].copy_(src[:, :, :n])
+
+    def storage_bytes(self) -> int:
+        """Bytes of the ``length`` stored tokens (what the reference's ``storage_bytes`` counts)."""
+        per_token = sum(t[0, 0, 0].numel() * t.element_size() for t in self.streams())
+        return int(per_token * self.batch * self.kv_heads * self.length)
+
+    # ------------------------------------------------------------------ kernels
+    def _stream_ptr(self):
+        return C.c_void_p(torch.cuda.current_stream(self.codec.device).cuda_stream)
+
+    def pack(self, k: torch.Tensor, v: torch.Tensor) -> None:
+        """Quantise ``k``/``v`` [B, Hkv, T, 128] and append them at the current length."""
+        if k.shape != v.shape or k.dtype != v.dtype:
+            raise ValueError("key and value tensors must have the same shape and dtype")
+        if k.shape[0] != self.batch or k.shape[1] != self.kv_heads:
+            raise ValueError("Packed tensor append requires matching batch, head, and dimension shape.")
+        if k.device != self.codec.device:
+            raise ffi.TQError(f"tensor on {k.device}, cache on {self.codec.device}")
+        n = int(k.shape[2])
+        if n == 0:
+            return
+        if k.stride(-1) != 1:
+            k = k.contiguous()
+        if v.stride(-1) != 1:
+            v = v.contiguous()
+        self.reserve(self.length + n)
+        kd, vd = dense_desc(k), dense_desc(v)
+        with torch.cuda.device(self.codec.device):
+            ffi.check(ffi.lib().tq_pack(self.codec.handle, C.byref(kd), C.byref(vd), n, C.byref(self._desc),
+                                        self.length, self._stream_ptr()), "tq_pack")
+        self.length += n
+
+    def suggest_splits(self, seq_len: int | None = None) -> int:
+        n = self.length if seq_len is None else seq_len
+        return int(ffi.lib().tq_decode_suggest_splits(self.codec.handle, self.batch, self.kv_heads, max(n, 1)))
+
+    def _get_workspace(self, q_heads: int, splits: int) -> torch.Tensor:
+        need = int(ffi.lib().tq_decode_workspace_bytes(self.batch, q_heads, splits))
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.codec.device)
+        return self._workspace
+
+    def decode_attn(self, q: torch.Tensor, *, seq_len: int | None = None, tail_k: torch.Tensor | None = None,
+                    tail_v: torch.Tensor | None = None, splits: int | None = None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+        """One decode step: ``q`` [B, Hq, 1, 128] (or [B, Hq, 128]) -> [B, Hq, 1, 128]."""
+        b, hq = int(q.shape[0]), int(q.shape[1])
+        if q.shape[-1] != 128 or q.numel() != b * hq * 128 or b != self.batch:
+            raise ValueError(f"expected a single-token query [B={self.batch}, Hq, 1, 128], got {tuple(q.shape)}")
+        qc = q.reshape(b, hq, 128)
+        if not qc.is_contiguous():
+            qc = qc.contiguous()
+        n = self.length if seq_len is None else int(seq_len)
+        n_tail = 0 if tail_k is None else int(tail_k.shape[2])
+        if n_tail:
+            tkd, tvd = dense_desc(tail_k), dense_desc(tail_v)
+            tk_ref, tv_ref = C.byref(tkd), C.byref(tvd)
+        else:
+            tk_ref = tv_ref = None
+        splits = self.suggest_splits(n) if splits is None else int(splits)
+        ws = self._get_workspace(hq, splits)
+        if out is None:
+            out = torch.empty(b, hq, 1, 128, dtype=q.dtype, device=q.device)
+        with torch.cuda.device(self.codec.device):
+            ffi.check(ffi.lib().tq_decode_attn(self.codec.handle, qc.data_ptr(), tq_dtype(q.dtype), hq,
+                                               C.byref(self._desc), n, tk_ref, tv_ref, n_tail, splits,
+                                               ws.data_ptr(), ws.numel(), out.data_ptr(), self._stream_ptr()),
+                      "tq_decode_attn")
+        return out
+
+    def dequant(self, which: str, lo: int = 0, hi: int | None = None,
+                dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """Dequantise tokens [lo, hi) of ``which`` in {'keys', 'values'} -> [B, Hkv, hi-lo, 128]."""
+        hi = self.length if hi is None else hi
+        n = hi - lo
+        out = torch.empty(self.batch, self.kv_heads, n, 128, dtype=dtype, device=self.codec.device)
+        if n > 0:
+            od = dense_desc(out)
+            with torch.cuda.device(self.codec.device):
+                ffi.check(ffi.lib().tq_dequant(self.codec.handle, C.byref(self._desc), 0 if which == "keys" else 1,
+                                               lo, n, C.byref(od), self._stream_ptr()), "tq_dequant")
+        return out
+
+
+def key_norm_mean(k: torch.Tensor) -> torch.Tensor:
+    """Mean L2 norm over all vectors of ``k`` [B, H, T, 128] as a 0-dim float64 device tensor
+    (no host sync); the norm-guard statistic of ``build_packed_mse_cache``
+    (packed_qmse_cache.py:918-920)."""
+    acc = torch.zeros((), dtype=torch.float64, device=k.device)
+    if k.stride(-1) != 1:
+        k = k.contiguous()
+    kd = dense_desc(k)
+    b, h, t = int(k.shape[0]), int(k.shape[1]), int(k.shape[2])
+    with torch.cuda.device(k.device):
+        ffi.check(ffi.lib().tq_key_norm_sum(C.byref(kd), b, h, t, acc.data_ptr(),
+                                            C.c_void_p(torch.cuda.current_stream(k.device).cuda_stream)),
+                  "tq_key_norm_sum")
+    return acc / (b * h * t)

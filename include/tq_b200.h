@@ -145,6 +145,15 @@ int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32
 int32_t tq_key_norm_sum(const tq_dense_desc *k, int32_t batch, int32_t heads, int32_t n_tokens,
                         double *sum_out, tq_stream stream);
 
+/* Measurement hooks (no reference counterpart; used by the benchmark).  While enabled, each
+ * tq_decode_attn call brackets its main kernel (the one that streams the packed cache)
+ * with CUDA events on the launch stream and counts every kernel the library launches.
+ * tq_profile_read synchronises those events, returns the summed main-kernel time and
+ * the counts, and resets them. */
+int32_t tq_profile_enable(tq_ctx *ctx, int32_t on);
+int32_t tq_profile_read(tq_ctx *ctx, double *main_kernel_ms, int64_t *main_kernel_launches,
+                        int64_t *all_launches);
+
 #ifdef __cplusplus
 }
 #endif

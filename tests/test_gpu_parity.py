@@ -15,8 +15,11 @@ from oracle import tq_oracle as O
 
 pytestmark = pytest.mark.gpu
 
-# Output tolerances: relative to the largest reference magnitude (inf-norm).
-TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-3, torch.float16: 2e-3}
+# Output tolerances, relative to the largest reference magnitude (inf-norm): 1e-5 for fp32,
+# 2e-3 for 16-bit caches.  The kernel writes its result in the query dtype, so when it is
+# compared with an fp32 reference the half-ulp of that final rounding (2^-9 for bf16,
+# 2^-12 for fp16, relative to the element) is added on top.
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-3 + 2.0 ** -9, torch.float16: 2e-3 + 2.0 ** -12}
 
 
 def _golden_layer(g, p, tag) -> O.PackedLayer:
@@ -117,7 +120,7 @@ def test_decode_attention_matches_reference(setup_golden, case, tag):
         got = store.decode_attn(q.cuda(), splits=splits)
         assert got.dtype == q.dtype and tuple(got.shape) == (g.i("B"), g.i("Hq"), 1, 128)
         # (1) against the reference's fused identity, at the headline tolerance
-        assert rel_inf(got, fused32) <= TOL[g.dtype] * (1.0 if g.dtype == torch.float32 else 1.5)
+        assert rel_inf(got, fused32) <= TOL[g.dtype]
         # (2) against dequantise-then-attend: exact-to-tolerance for fp32 caches; for 16-bit caches
         # the reference rounds the dequantised K/V to the cache dtype, which no rotated-space
         # kernel (its own Triton one included) reproduces, so allow that measured gap on top.
@@ -125,7 +128,9 @@ def test_decode_attention_matches_reference(setup_golden, case, tag):
         assert rel_inf(got, want32) <= TOL[g.dtype] + gap
     # the reference's own chunked output (query dtype)
     chunked = g.t(f"{tag}_attn_chunked")
-    assert rel_inf(got, chunked) <= TOL[g.dtype] + (rel_inf(fused32, chunked.float()) if g.dtype != torch.float32 else 0.0)
+    # (both sides are rounded to the query dtype here, hence one more half-ulp)
+    half_ulp = {torch.float32: 0.0, torch.bfloat16: 2.0 ** -9, torch.float16: 2.0 ** -12}[g.dtype]
+    assert rel_inf(got, chunked) <= TOL[g.dtype] + gap + half_ulp
 
 
 @pytest.mark.parametrize("case", LAYER_CASES)
@@ -185,7 +190,7 @@ def test_seeded_layer_against_oracle(setup_golden, bits, qjl, dtype, B, Hq, Hkv,
     fused32 = O.attend_rotated_space(q, mine, groups)
     want32 = O.attend_dequant(q, mine, groups)
     got = store.decode_attn(q.cuda())
-    assert rel_inf(got, fused32) <= TOL[dtype] * (1.0 if dtype == torch.float32 else 1.5)
+    assert rel_inf(got, fused32) <= TOL[dtype]
     gap = rel_inf(fused32, want32) if dtype != torch.float32 else 0.0
     assert rel_inf(got, want32) <= TOL[dtype] + gap
     # split count must not change the answer beyond rounding

@@ -14,6 +14,59 @@ void tq_set_cuda_error(cudaError_t e, const char *where) {
 }
 
 extern "C" const char *tq_last_cuda_error(void) { return g_err; }
+
+struct tq_prof {
+    bool on = false;
+    std::vector<cudaEvent_t> events;  // start/stop pairs, created on first use
+    size_t used = 0;                  // events recorded since the last read
+    int64_t launches = 0;
+};
+
+void tq_prof_count(tq_ctx *ctx, int n) {
+    if (ctx->prof && ctx->prof->on) ctx->prof->launches += n;
+}
+
+static void prof_record(tq_ctx *ctx, cudaStream_t stream) {
+    tq_prof *p = ctx->prof;
+    if (!p || !p->on || p->used >= 8192) return;
+    if (p->used == p->events.size()) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) return;
+        p->events.push_back(e);
+    }
+    cudaEventRecord(p->events[p->used++], stream);
+}
+void tq_prof_begin(tq_ctx *ctx, cudaStream_t stream) { prof_record(ctx, stream); }
+void tq_prof_end(tq_ctx *ctx, cudaStream_t stream) { prof_record(ctx, stream); }
+
+extern "C" int32_t tq_profile_enable(tq_ctx *ctx, int32_t on) {
+    if (!ctx) return TQ_ERR_ARG;
+    if (!ctx->prof) ctx->prof = new tq_prof();
+    ctx->prof->on = on != 0;
+    ctx->prof->used = 0;
+    ctx->prof->launches = 0;
+    return TQ_OK;
+}
+
+extern "C" int32_t tq_profile_read(tq_ctx *ctx, double *main_ms, int64_t *main_launches, int64_t *all_launches) {
+    if (!ctx || !ctx->prof) return TQ_ERR_ARG;
+    tq_prof *p = ctx->prof;
+    double total = 0.0;
+    int64_t n = 0;
+    for (size_t i = 0; i + 1 < p->used; i += 2) {
+        TQ_CUDA_CHECK(cudaEventSynchronize(p->events[i + 1]));
+        float ms = 0.f;
+        TQ_CUDA_CHECK(cudaEventElapsedTime(&ms, p->events[i], p->events[i + 1]));
+        total += ms;
+        ++n;
+    }
+    if (main_ms) *main_ms = total;
+    if (main_launches) *main_launches = n;
+    if (all_launches) *all_launches = p->launches;
+    p->used = 0;
+    p->launches = 0;
+    return TQ_OK;
+}
 extern "C" int32_t tq_abi_version(void) { return 1; }
 
 namespace {
@@ -127,6 +180,10 @@ extern "C" int32_t tq_ctx_destroy(tq_ctx *ctx) {
     if (!ctx) return TQ_OK;
     cudaSetDevice(ctx->device);
     if (ctx->base) cudaFree(ctx->base);
+    if (ctx->prof) {
+        for (cudaEvent_t e : ctx->prof->events) cudaEventDestroy(e);
+        delete ctx->prof;
+    }
     delete ctx;
     return TQ_OK;
 }

@@ -36,7 +36,13 @@ struct tq_ctx {
     float *qjl_hi, *qjl_lo;       // S        as [i][d]
     void *base;       // one allocation holding everything above
     size_t base_bytes;
+    struct tq_prof *prof;  // measurement hooks, see tq_profile_enable
 };
+
+// Measurement hooks: bracket the main decode kernel with events, count launches.
+void tq_prof_begin(tq_ctx *ctx, cudaStream_t stream);
+void tq_prof_end(tq_ctx *ctx, cudaStream_t stream);
+void tq_prof_count(tq_ctx *ctx, int n_launches);
 
 void tq_set_cuda_error(cudaError_t e, const char *where);
 

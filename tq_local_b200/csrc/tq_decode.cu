@@ -343,6 +343,8 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
     dim3 grid(n_splits, cache->batch * cache->kv_heads);
     const int threads = kExactWarps * 32;
     const int mode = ctx->use_qjl * 10 + ctx->bits;
+    tq_prof_count(ctx, 3);
+    tq_prof_begin(ctx, stream);
     switch (mode) {
         case 2: tq_decode_exact_kernel<2, 2, false><<<grid, threads, 0, stream>>>(a); break;
         case 3: tq_decode_exact_kernel<3, 3, false><<<grid, threads, 0, stream>>>(a); break;
@@ -352,6 +354,7 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
         case 14: tq_decode_exact_kernel<3, 4, true><<<grid, threads, 0, stream>>>(a); break;
         default: return TQ_ERR_UNSUPPORTED;
     }
+    tq_prof_end(ctx, stream);
     TQ_CUDA_CHECK(cudaGetLastError());
 
     CombineArgs c;

@@ -333,6 +333,7 @@ int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc 
     else if (k->dtype == TQ_DTYPE_F16) TQ_LAUNCH_PACK(__half);
     else TQ_LAUNCH_PACK(__nv_bfloat16);
 #undef TQ_LAUNCH_PACK
+    tq_prof_count(ctx, 1);
     TQ_CUDA_CHECK(cudaGetLastError());
     return TQ_OK;
 }

@@ -107,6 +107,17 @@ class Codec:
                 cls._cache[key] = cls(device, bits, use_qjl, seed, grid_size, head_dim)
             return cls._cache[key]
 
+    def profile(self, on: bool) -> None:
+        """Switch the library's measurement hooks on or off (see ``tq_profile_enable``)."""
+        ffi.check(ffi.lib().tq_profile_enable(self.handle, int(on)), "tq_profile_enable")
+
+    def profile_read(self) -> tuple[float, int, int]:
+        """(summed main-kernel ms, main-kernel launches, all launches) since the last read."""
+        ms, n_main, n_all = C.c_double(), C.c_int64(), C.c_int64()
+        ffi.check(ffi.lib().tq_profile_read(self.handle, C.byref(ms), C.byref(n_main), C.byref(n_all)),
+                  "tq_profile_read")
+        return ms.value, n_main.value, n_all.value
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             ffi.lib().tq_ctx_destroy(self.handle)

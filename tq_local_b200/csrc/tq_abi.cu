@@ -221,14 +221,23 @@ extern "C" size_t tq_decode_workspace_bytes(int32_t batch, int32_t q_heads, int3
 
 extern "C" int32_t tq_decode_suggest_splits(tq_ctx *ctx, int32_t batch, int32_t kv_heads, int32_t seq_len) {
     if (!ctx || batch <= 0 || kv_heads <= 0 || seq_len <= 0) return 1;
+    // The decode kernel runs two 4-warp CTAs per SM and walks tokens 256 at a time per CTA.
+    // Pick the tokens-per-split (a multiple of 256) that best balances two effects:
+    // the last partial wave of CTAs, and the fixed per-CTA cost (table build, partial
+    // write-back), taken as the time of about 96 tokens.
     const int rows = batch * kv_heads;
-    const int target = ctx->sm_count * 4;  // CTAs wanted in flight
-    int splits = (target + rows - 1) / rows;
-    const int max_by_len = (seq_len + 255) / 256;  // at least 256 tokens per split
-    if (splits > max_by_len) splits = max_by_len;
-    if (splits < 1) splits = 1;
-    if (splits > 256) splits = 256;
-    return splits;
+    const double slots = 2.0 * ctx->sm_count;
+    double best_score = -1.0;
+    int best_splits = 1;
+    for (int tok = 256; tok < seq_len + 256; tok += 256) {
+        const int splits = (seq_len + tok - 1) / tok;
+        if (splits > 1024) continue;
+        const double waves = rows * (double)splits / slots;
+        const double eff = waves / ceil(waves);
+        const double score = eff * tok / (tok + 96.0);
+        if (score > best_score + 1e-9) best_score = score, best_splits = splits;
+    }
+    return best_splits;
 }
 
 extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
@@ -246,8 +255,11 @@ extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, i
     if (q_heads / cache->kv_heads > TQ_MAX_GROUPS) return TQ_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)workspace) & 15) return TQ_ERR_ARG;
     if (workspace_bytes < tq_decode_workspace_bytes(cache->batch, q_heads, n_splits)) return TQ_ERR_WORKSPACE;
-    return tq_launch_decode_exact(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
-                                  workspace, out, (cudaStream_t)stream);
+    if (q_dtype == TQ_DTYPE_F32 || seq_len == 0)
+        return tq_launch_decode_exact(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
+                                      workspace, out, (cudaStream_t)stream);
+    return tq_launch_decode_mma(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
+                                workspace, out, (cudaStream_t)stream);
 }
 
 extern "C" int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,

@@ -201,7 +201,9 @@ def run_gpu_arm(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    w = WORKLOAD
+    w = dict(WORKLOAD)
+    if args.batch_per_gpu:
+        w["batch_per_gpu"] = args.batch_per_gpu
     if w["kv_heads"] % world:
         raise SystemExit(f"{w['kv_heads']} KV heads do not shard over {world} ranks")
     dtype = getattr(torch, w["dtype"])
@@ -226,7 +228,7 @@ def run_gpu_arm(args) -> None:
     q = torch.randn(batch, hq, 1, HEAD_DIM, generator=gen, device=dev).to(dtype)
     out = torch.empty(batch, hq, 1, HEAD_DIM, dtype=dtype, device=dev)
     gathered = torch.empty(world, batch, hq, 1, HEAD_DIM, dtype=dtype, device=dev) if world > 1 else None
-    splits = store.suggest_splits(n_ctx)
+    splits = args.splits or store.suggest_splits(n_ctx)
 
     def step():
         store.decode_attn(q, seq_len=n_ctx, splits=splits, out=out)
@@ -286,15 +288,16 @@ def run_gpu_arm(args) -> None:
             h_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the host needs the result before the next token
 
-    for _ in range(warmup):
+    e2e_steps = 0 if args.skip_e2e else steps
+    for _ in range(0 if args.skip_e2e else warmup):
         e2e_step()
     fence()
     ev0.record()
-    for _ in range(steps):
+    for _ in range(e2e_steps):
         e2e_step()
     ev1.record()
     fence()
-    e2e_ms = ev0.elapsed_time(ev1) / steps
+    e2e_ms = ev0.elapsed_time(ev1) / max(e2e_steps, 1)
     if world > 1:
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -315,7 +318,7 @@ def run_gpu_arm(args) -> None:
                 "workload": w["name"], "global_batch": batch, "q_heads": w["q_heads"], "kv_heads": w["kv_heads"],
                 "context": n_ctx, "bits": w["bits"], "mode": "Q_prod", "bytes_per_token_head": unit_bytes,
                 "parallelism": f"kv-head-shard{world}" if world > 1 else "single",
-                "splits": splits, "l2": "inputs larger than L2 (281 MB of packed cache per GPU per step vs 126 MB)",
+                "splits": splits, "l2": f"inputs larger than L2 ({unit_bytes * batch * hkv * n_ctx / 1e6:.0f} MB of packed cache per GPU per step vs 126 MB)",
             },
             "decode_tok_per_s_layer": batch / (ms * 1e-3),
             "roofline": {
@@ -324,8 +327,9 @@ def run_gpu_arm(args) -> None:
                 "kernel": "tq_decode main kernel (streams the packed cache)",
                 "kernel_ms": main_ms / max(main_n, 1), "traffic": None,
             },
-            "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": None if args.skip_e2e else {
+                "value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(all_launches),
             "clocks": clocks,
             "pack": {"seconds": pack_s, "vectors_per_s": 2 * batch * hkv * n_ctx / pack_s},
@@ -346,6 +350,10 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch-per-gpu", type=int, default=None,
+                    help="override the workload's batch (profiling captures use a smaller one)")
+    ap.add_argument("--splits", type=int, default=None, help="override the library's split choice")
+    ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -221,12 +221,12 @@ extern "C" size_t tq_decode_workspace_bytes(int32_t batch, int32_t q_heads, int3
 
 extern "C" int32_t tq_decode_suggest_splits(tq_ctx *ctx, int32_t batch, int32_t kv_heads, int32_t seq_len) {
     if (!ctx || batch <= 0 || kv_heads <= 0 || seq_len <= 0) return 1;
-    // The decode kernel runs two 4-warp CTAs per SM and walks tokens 256 at a time per CTA.
+    // The decode kernel runs three 4-warp CTAs per SM and walks tokens 256 at a time per CTA.
     // Pick the tokens-per-split (a multiple of 256) that best balances two effects:
     // the last partial wave of CTAs, and the fixed per-CTA cost (table build, partial
     // write-back), taken as the time of about 96 tokens.
     const int rows = batch * kv_heads;
-    const double slots = 2.0 * ctx->sm_count;
+    const double slots = 3.0 * ctx->sm_count;
     double best_score = -1.0;
     int best_splits = 1;
     for (int tok = 256; tok < seq_len + 256; tok += 256) {
@@ -258,6 +258,9 @@ extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, i
     if (q_dtype == TQ_DTYPE_F32 || seq_len == 0)
         return tq_launch_decode_exact(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
                                       workspace, out, (cudaStream_t)stream);
+    if (q_heads / cache->kv_heads <= 4)
+        return tq_launch_decode_mma4(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
+                                     workspace, out, (cudaStream_t)stream);
     return tq_launch_decode_mma(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
                                 workspace, out, (cudaStream_t)stream);
 }

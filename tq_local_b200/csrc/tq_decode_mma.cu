@@ -25,6 +25,7 @@
 
 #include "tq_common.cuh"
 #include "tq_decode_shared.cuh"
+#include "tq_mma_utils.cuh"
 
 namespace {
 
@@ -47,31 +48,6 @@ struct MmaArgs {
     const float *centers_k, *centers_v;
 };
 
-__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                        uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
-    uint32_t y;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
-    return y;
-}
-
-__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
-
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-
 // Byte offset, in a per-lane-replicated table (entry stride 128 bytes), of the entry
 // selected by the WIDTH-bit field at bit `off` of the little-endian word array `w`.
 // `off` is a compile-time constant after unrolling, so this folds to a shift and a mask
@@ -86,12 +62,6 @@ template <int WIDTH> __device__ __forceinline__ uint32_t entry_offset_dyn(const 
         x = __funnelshift_r(w[wi], w[wi + 1], s) << 7;
     }
     return x & kMask;
-}
-
-template <int BITS> __host__ __device__ constexpr uint64_t even_field_mask() {
-    uint64_t m = 0;
-    for (int j = 0; j < 64 / BITS; j += 2) m |= ((1ull << BITS) - 1ull) << (j * BITS);
-    return m;
 }
 
 // Load the 16*VB-bit value chunk of lane group g from one token row (VB*16 bytes).

@@ -51,14 +51,15 @@ struct Mma4Args {
     const float *centers_k, *centers_v;
 };
 
-// Byte offset of the table slot selected by the WIDTH-bit field at bit `off` of the
-// little-endian word array `w` (slot stride 256 B).  `off` is a compile-time constant after
-// unrolling.  A byte-aligned 8-bit field is moved with a single byte permute; any other
-// field takes a shift and a mask (or a funnel shift when it straddles two words; w[off/32+1]
-// must exist).
-template <int WIDTH> __device__ __forceinline__ uint32_t slot_offset(const uint32_t *w, int off) {
+// Byte offset of this lane's copy of the table slot selected by the WIDTH-bit field at bit
+// `off` of the little-endian word array `w`: slot * 256 + lane_bits, where lane_bits < 256
+// is the lane's offset inside a slot.  `off` is a compile-time constant after unrolling.
+// A byte-aligned 8-bit field takes one byte permute (field -> byte 1, lane_bits -> byte 0);
+// any other field takes a shift and one three-input logic op (or a funnel shift first when
+// it straddles two words; w[off/32+1] must exist).
+template <int WIDTH> __device__ __forceinline__ uint32_t slot_offset(const uint32_t *w, int off, uint32_t lane_bits) {
     const int wi = off >> 5, s = off & 31;
-    if (WIDTH == 8 && (s & 7) == 0) return prmt(w[wi], 0u, 0x4404u | ((uint32_t)(s >> 3) << 4));
+    if (WIDTH == 8 && (s & 7) == 0) return prmt(w[wi], lane_bits, 0x5504u | ((uint32_t)(s >> 3) << 4));
     constexpr uint32_t kMask = ((1u << WIDTH) - 1u) << 8;
     uint32_t x;
     if (s + WIDTH <= 32) {
@@ -66,7 +67,7 @@ template <int WIDTH> __device__ __forceinline__ uint32_t slot_offset(const uint3
     } else {
         x = __funnelshift_r(w[wi], w[wi + 1], s) << 8;
     }
-    return x & kMask;
+    return (x & kMask) | lane_bits;
 }
 
 // The 16*VB-bit value chunk of lane group g of one token row (row = VB*16 bytes).
@@ -102,19 +103,12 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
     const int g = lane >> 2, t = lane & 3;
     const int64_t q_row0 = ((int64_t)b * a.Hkv + h) * G;
 
-    // ---- per-lane replicated f16x2 centre-pair tables (keys in the low half of each slot)
-    for (int e = threadIdx.x; e < kEntries; e += blockDim.x) {
-        uint4 *slot = reinterpret_cast<uint4 *>(table + e * kSlotWords);
-        if (e < kKEntries) {
-            const uint32_t w = pack_half2(a.centers_k[e & ((1 << KB) - 1)], a.centers_k[e >> KB]);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) slot[j] = make_uint4(w, w, w, w);
-        }
-        if (e < kVEntries) {
-            const uint32_t w = pack_half2(a.centers_v[e & ((1 << VB) - 1)], a.centers_v[e >> VB]);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) slot[8 + j] = make_uint4(w, w, w, w);
-        }
+    // ---- per-lane replicated f16x2 centre-pair tables (keys in the low half of each slot);
+    // a warp fills one slot at a time, lane l writing words l and 32+l (no bank conflicts)
+    for (int e = warp; e < kEntries; e += kWarps) {
+        uint32_t *slot = table + e * kSlotWords;
+        if (e < kKEntries) slot[lane] = pack_half2(a.centers_k[e & ((1 << KB) - 1)], a.centers_k[e >> KB]);
+        if (e < kVEntries) slot[32 + lane] = pack_half2(a.centers_v[e & ((1 << VB) - 1)], a.centers_v[e >> VB]);
     }
 
     // ---- B fragments: column g = (head g/2, part g%2)
@@ -181,8 +175,9 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
     const int last = a.N - 1;
     const float kA = 0.08838834764831845f * 1.4426950408889634f;  // (1/sqrt(128)) * log2(e)
     const float kB = kA * (1.2533141373155003f / (float)TQ_D);     // ... * sqrt(pi/2)/D
-    const uint8_t *lk = reinterpret_cast<const uint8_t *>(table) + lane * 4;
-    const uint8_t *lv = lk + 128;
+    const uint8_t *lk = smem;        // key copies: bytes [0, 128) of every slot
+    const uint8_t *lv = smem + 128;  // value copies: bytes [128, 256)
+    const uint32_t lane_bits = lane * 4;
     const bool head_live = t < G;
 
     float m_run = -INFINITY, l_run = 0.f;
@@ -211,10 +206,10 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
             for (int s = 0; s < 8; ++s) {
                 constexpr int W = 2 * KB;
                 const int o0 = (2 * s) * W, o1 = (2 * s + 1) * W;
-                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wa, o0));
-                const uint32_t a1 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wb, o0));
-                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wa, o1));
-                const uint32_t a3 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wb, o1));
+                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wa, o0, lane_bits));
+                const uint32_t a1 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wb, o0, lane_bits));
+                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wa, o1, lane_bits));
+                const uint32_t a3 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wb, o1, lane_bits));
                 mma_f16(d1, a0, a1, a2, a3, bq[s][0], bq[s][1]);
             }
             const float2 kn = half2_bits_to_float2(__ldg(reinterpret_cast<const uint32_t *>(a.k_norms + rA)));
@@ -299,10 +294,10 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
 #pragma unroll
             for (int mt = 0; mt < 8; ++mt) {
                 constexpr int W = 2 * VB;
-                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(xa, mt * W));
-                const uint32_t a1 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(ya, mt * W));
-                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(xb, mt * W));
-                const uint32_t a3 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(yb, mt * W));
+                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(xa, mt * W, lane_bits));
+                const uint32_t a1 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(ya, mt * W, lane_bits));
+                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(xb, mt * W, lane_bits));
+                const uint32_t a3 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(yb, mt * W, lane_bits));
                 mma_f16(o[mt], a0, a1, a2, a3, pb[i][0], pb[i][1]);
             }
         }

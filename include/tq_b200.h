@@ -145,6 +145,11 @@ int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32
 int32_t tq_key_norm_sum(const tq_dense_desc *k, int32_t batch, int32_t heads, int32_t n_tokens,
                         double *sum_out, tq_stream stream);
 
+/* Device-side status (no reference counterpart).  Kernels never spin without a limit: a
+ * wait on an asynchronous copy that runs out sets a status word instead of hanging.  This
+ * call synchronises with the device and returns that word (0 = no kernel ever gave up). */
+int32_t tq_device_status(tq_ctx *ctx, int32_t *status_out);
+
 /* Measurement hooks (no reference counterpart; used by the benchmark).  While enabled, each
  * tq_decode_attn call brackets its main kernel (the one that streams the packed cache)
  * with CUDA events on the launch stream and counts every kernel the library launches.

@@ -99,7 +99,7 @@ extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_de
     const int kb = c->use_qjl ? c->bits - 1 : c->bits;
     const size_t M = (size_t)TQ_D * TQ_D;
     // 6 plain matrices + 8 split matrices + 4 tables of 16 floats.
-    const size_t n_float = 14 * M + 4 * 16;
+    const size_t n_float = 14 * M + 4 * 16 + 4;  // + the device status word
     std::vector<float> h(n_float, 0.0f);
     auto mat = [&](int i) { return h.data() + (size_t)i * M; };
     auto transpose = [&](const float *src, float *dst) {
@@ -172,6 +172,7 @@ extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_de
     ctx->bounds_k = ctx->centers_k + 16;
     ctx->centers_v = ctx->centers_k + 32;
     ctx->bounds_v = ctx->centers_k + 48;
+    ctx->error_flag = reinterpret_cast<int *>(ctx->centers_k + 64);  // uploaded as zero
     *out = ctx;
     return TQ_OK;
 }
@@ -221,23 +222,32 @@ extern "C" size_t tq_decode_workspace_bytes(int32_t batch, int32_t q_heads, int3
 
 extern "C" int32_t tq_decode_suggest_splits(tq_ctx *ctx, int32_t batch, int32_t kv_heads, int32_t seq_len) {
     if (!ctx || batch <= 0 || kv_heads <= 0 || seq_len <= 0) return 1;
-    // The decode kernel runs three 4-warp CTAs per SM and walks tokens 256 at a time per CTA.
-    // Pick the tokens-per-split (a multiple of 256) that best balances two effects:
-    // the last partial wave of CTAs, and the fixed per-CTA cost (table build, partial
-    // write-back), taken as the time of about 96 tokens.
+    // The decode kernel runs one 12-warp CTA per SM and walks tokens 384 at a time per CTA.
+    // Pick the tokens-per-split (a multiple of 384) that best balances two effects:
+    // the last partial wave of CTAs, and the fixed per-CTA cost (table build, pipeline
+    // fill, partial write-back), taken as the time of about 256 tokens.
     const int rows = batch * kv_heads;
-    const double slots = 3.0 * ctx->sm_count;
+    const double slots = (double)ctx->sm_count;
+    const int step = 384;
     double best_score = -1.0;
     int best_splits = 1;
-    for (int tok = 256; tok < seq_len + 256; tok += 256) {
+    for (int tok = step; tok < seq_len + step; tok += step) {
         const int splits = (seq_len + tok - 1) / tok;
         if (splits > 1024) continue;
         const double waves = rows * (double)splits / slots;
         const double eff = waves / ceil(waves);
-        const double score = eff * tok / (tok + 96.0);
+        const double score = eff * tok / (tok + 256.0);
         if (score > best_score + 1e-9) best_score = score, best_splits = splits;
     }
     return best_splits;
+}
+
+extern "C" int32_t tq_device_status(tq_ctx *ctx, int32_t *status_out) {
+    if (!ctx || !status_out) return TQ_ERR_ARG;
+    int v = 0;
+    TQ_CUDA_CHECK(cudaMemcpy(&v, ctx->error_flag, sizeof(int), cudaMemcpyDeviceToHost));
+    *status_out = v;
+    return TQ_OK;
 }
 
 extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,

@@ -37,6 +37,7 @@ struct tq_ctx {
     void *base;       // one allocation holding everything above
     size_t base_bytes;
     struct tq_prof *prof;  // measurement hooks, see tq_profile_enable
+    int *error_flag;       // device word, set by a kernel whose bounded wait ran out
 };
 
 // Measurement hooks: bracket the main decode kernel with events, count launches.

@@ -1,25 +1,32 @@
 // Decode attention over the packed cache: tensor-core kernel for fp16 / bf16 queries
 // with at most 4 query heads per KV head (Llama-3.1-8B: 32 / 8).
 //
-// One CTA owns one (batch, KV head) row and one contiguous token range and serves all
-// G <= 4 query heads, so packed bytes are read once.  The 8 columns of every MMA are
-// used as (head, part) pairs, which gives each lane of a quad its own head:
+// One CTA (12 warps, one per SM) owns one (batch, KV head) row and one contiguous token
+// range and serves all G <= 4 query heads, so packed bytes are read from HBM once.
 //
+// Data movement: every warp runs its own 3-stage ring of 32-token stages in shared
+// memory.  Lane 0 fills a stage with six TMA bulk copies (cp.async.bulk: key codes, QJL
+// signs, value codes and the three fp16 norm streams are each contiguous in HBM) that
+// complete on an mbarrier; the warp waits on it with a bounded spin.  No registers and no
+// load/store-unit issue slots are spent on global loads, and HBM latency is hidden by the
+// ring rather than by occupancy.
+//
+// Math: the 8 columns of every MMA are (head, part) pairs, which gives each lane of a
+// quad its own head:
 //   logits   S  [16 tok x (4 heads x {hi, lo})] = Kdeq[16 x 128] * {Qrot_hi, Qrot_lo}   f16 m16n8k16
-//            the rotated query is split in two f16 terms, so its rounding does not show;
+//            (the rotated query is split in two f16 terms, so its rounding does not show)
 //   QJL      S2 [16 tok x (4 heads x {hi, lo})] = -Bit[16 x 128] * {Qp_hi, Qp_lo}       s8 m16n8k32
-//            sign bits become 0 / -1 bytes four at a time (byte permute with sign
-//            replication); the projected query is 16-bit fixed point in two s8 terms;
+//            (sign bits become 0 / -1 bytes four at a time with a sign-replicating byte
+//            permute; the projected query is 16-bit fixed point in two s8 terms)
 //   values   O^T[128 x (4 heads x {P, 0})] += Vdeq^T[128 x 16 tok] * P                   f16 m16n8k16
-//
-// A operands are built in registers from the packed words.  The contraction order and
-// the row order of an MMA are free, so every lane gets codes that sit together in memory:
-//   keys    lane (g, t): dims [32t, 32t+32) of tokens 2g, 2g+1 of a 16-token tile; two
+// A operands are built in registers from the packed words.  The contraction order of an
+// MMA is free, so every lane gets codes that sit together in memory:
+//   keys    lane (g, t): dims [32t, 32t+32) of tokens g and g+8 of a 16-token tile; two
 //           neighbouring codes index a per-lane-replicated shared-memory table of f16x2
-//           centre pairs (entry e of lane l lives in bank l: no bank conflicts);
-//   values  lane (g, t): dims [16g, 16g+16) of tokens 4t .. 4t+3; the codes of two tokens
-//           are interleaved with bit-selects so one look-up yields the (token a, token b)
-//           f16x2 that the MMA wants along its K axis.
+//           centre pairs (slot e, lane l -> bank l: no bank conflicts);
+//   values  lane (g, t): dims [16g, 16g+16) of tokens 2t, 2t+1, 2t+8, 2t+9; the codes of two
+//           tokens are interleaved with bit-selects so one look-up yields the (token a,
+//           token b) f16x2 that the MMA wants along its K axis.
 // Softmax is online, base 2, in registers; P*|v| goes to f16 and is transposed with
 // movmatrix.  Per-CTA partials (max, sum, acc) go to the workspace; tq_combine_kernel
 // merges splits, un-rotates and casts.
@@ -31,10 +38,11 @@
 
 namespace {
 
-constexpr int kWarps = 4;
-constexpr int kTiles = 4;               // 16-token MMA tiles per warp iteration
-constexpr int kTokIter = 16 * kTiles;   // 64
-constexpr int kSlotWords = 64;          // table slot: 32 key words then 32 value words (256 B)
+constexpr int kWarps = 12;
+constexpr int kStageTok = 32;  // tokens per ring stage (two 16-token MMA tiles)
+constexpr int kStages = 3;
+constexpr int kSlotWords = 64;  // table slot: 32 key words then 32 value words (256 B)
+constexpr uint32_t kSpinLimit = 1u << 22;  // mbarrier polls before a wait gives up
 
 struct Mma4Args {
     const uint8_t *k_codes;
@@ -49,7 +57,52 @@ struct Mma4Args {
     const float *qproj;
     float *part_m, *part_l, *part_acc;
     const float *centers_k, *centers_v;
+    int *error_flag;  // set to 1 when a bounded wait ran out
 };
+
+template <int KB, int VB, bool QJL> struct StageLayout {
+    static constexpr int kK = 0;
+    static constexpr int kV = kK + kStageTok * 16 * KB;
+    static constexpr int kS = kV + kStageTok * 16 * VB;
+    static constexpr int kKN = kS + (QJL ? kStageTok * 16 : 0);
+    static constexpr int kVN = kKN + kStageTok * 2;
+    static constexpr int kRN = kVN + kStageTok * 2;
+    static constexpr int kBytes = (kRN + (QJL ? kStageTok * 2 : 0) + 127) / 128 * 128;
+};
+
+// ---- mbarrier / TMA bulk-copy wrappers (shared::cta addresses) ----
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and the caller flags an error) instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// Global -> shared bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned),
+// completion counted on `bar`.
+__device__ __forceinline__ void tma_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
 
 // Byte offset of this lane's copy of the table slot selected by the WIDTH-bit field at bit
 // `off` of the little-endian word array `w`: slot * 256 + lane_bits, where lane_bits < 256
@@ -70,30 +123,28 @@ template <int WIDTH> __device__ __forceinline__ uint32_t slot_offset(const uint3
     return (x & kMask) | lane_bits;
 }
 
-// The 16*VB-bit value chunk of lane group g of one token row (row = VB*16 bytes).
-template <int VB> __device__ __forceinline__ uint64_t load_v_chunk(const uint8_t *row, int g) {
+// The 16*VB-bit value chunk of lane group g of one staged token row (row = VB*16 bytes).
+template <int VB> __device__ __forceinline__ uint64_t lds_v_chunk(const uint8_t *row, int g) {
     if (VB == 4) {
-        return __ldg((const unsigned long long *)(row + 8 * g));
+        return *reinterpret_cast<const unsigned long long *>(row + 8 * g);
     } else if (VB == 2) {
-        return __ldg((const unsigned int *)(row + 4 * g));
-    } else {  // 3 bits: 6 bytes at byte 6g; read the aligned 8-byte windows that cover it
-        const int off = 6 * g, base = off & ~7, sh = (off & 7) * 8;
-        unsigned long long v = __ldg((const unsigned long long *)(row + base)) >> sh;
-        if (sh > 16) v |= __ldg((const unsigned long long *)(row + base + 8)) << (64 - sh);
-        return v & 0xffffffffffffull;
+        return *reinterpret_cast<const unsigned int *>(row + 4 * g);
+    } else {  // 3 bits: 6 bytes at byte 6g, as three 16-bit reads
+        const uint16_t *p = reinterpret_cast<const uint16_t *>(row + 6 * g);
+        return (uint64_t)p[0] | ((uint64_t)p[1] << 16) | ((uint64_t)p[2] << 32);
     }
 }
 
-__device__ __forceinline__ float2 half2_bits_to_float2(uint32_t u) {
-    return __half22float2(*reinterpret_cast<const __half2 *>(&u));
-}
-
 template <int KB, int VB, bool QJL>
-__global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args a) {
-    extern __shared__ __align__(16) uint8_t smem[];
+__global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args a) {
+    using L = StageLayout<KB, VB, QJL>;
+    extern __shared__ __align__(128) uint8_t smem[];
     constexpr int kKEntries = 1 << (2 * KB), kVEntries = 1 << (2 * VB);
     constexpr int kEntries = kKEntries > kVEntries ? kKEntries : kVEntries;
+    constexpr int kTableBytes = kEntries * kSlotWords * 4;
     uint32_t *table = reinterpret_cast<uint32_t *>(smem);
+    uint8_t *rings = smem + kTableBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(rings + kWarps * kStages * L::kBytes);
 
     const int split = blockIdx.x;
     const int bh = blockIdx.y;
@@ -102,13 +153,59 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int64_t q_row0 = ((int64_t)b * a.Hkv + h) * G;
+    const int64_t row0 = (int64_t)b * a.cache_sb + (int64_t)h * a.cache_sh;
+    const int t_begin = split * a.tok_per_split;
+    const int t_end = min(a.N, t_begin + a.tok_per_split);
+
+    // ---- ring set-up and the first loads (overlap with the table build below)
+    uint8_t *ring = rings + warp * kStages * L::kBytes;
+    const uint32_t ring_u32 = smem_u32(ring);
+    const uint32_t bar_u32 = smem_u32(bars + warp * kStages);
+    const int my_first = t_begin + warp * kStageTok;
+    const int n_iter = my_first < t_end ? (t_end - my_first + kWarps * kStageTok - 1) / (kWarps * kStageTok) : 0;
+
+    auto issue = [&](int it) {  // lane 0 only: fill stage it % kStages with iteration it
+        const int base = my_first + it * kWarps * kStageTok;
+        int n = min(kStageTok, t_end - base);
+        n = (n + 7) & ~7;  // whole 16-byte pieces of the norm streams; rows stay inside the row's stride
+        const int st = it % kStages;
+        const uint32_t dst = ring_u32 + st * L::kBytes, bar = bar_u32 + st * 8;
+        const int64_t r = row0 + base;
+        const uint32_t total = n * (16 * KB + 16 * VB + 4 + (QJL ? 18 : 0));
+        mbar_expect_tx(bar, total);
+        tma_load_1d(dst + L::kK, a.k_codes + r * (16 * KB), n * 16 * KB, bar);
+        tma_load_1d(dst + L::kV, a.v_codes + r * (16 * VB), n * 16 * VB, bar);
+        tma_load_1d(dst + L::kKN, a.k_norms + r, n * 2, bar);
+        tma_load_1d(dst + L::kVN, a.v_norms + r, n * 2, bar);
+        if (QJL) {
+            tma_load_1d(dst + L::kS, a.k_signs + r * 16, n * 16, bar);
+            tma_load_1d(dst + L::kRN, a.k_rnorms + r, n * 2, bar);
+        }
+    };
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(bar_u32 + s * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        for (int it = 0; it < min(n_iter, kStages); ++it) issue(it);
+    }
 
     // ---- per-lane replicated f16x2 centre-pair tables (keys in the low half of each slot);
     // a warp fills one slot at a time, lane l writing words l and 32+l (no bank conflicts)
-    for (int e = warp; e < kEntries; e += kWarps) {
-        uint32_t *slot = table + e * kSlotWords;
-        if (e < kKEntries) slot[lane] = pack_half2(a.centers_k[e & ((1 << KB) - 1)], a.centers_k[e >> KB]);
-        if (e < kVEntries) slot[32 + lane] = pack_half2(a.centers_v[e & ((1 << VB) - 1)], a.centers_v[e >> VB]);
+    {
+        const float ck = a.centers_k[lane & 15], cv = a.centers_v[lane & 15];
+        for (int e = warp; e < kEntries; e += kWarps) {
+            uint32_t *slot = table + e * kSlotWords;
+            if (e < kKEntries) {
+                const float lo = __shfl_sync(0xffffffffu, ck, e & ((1 << KB) - 1));
+                const float hi = __shfl_sync(0xffffffffu, ck, e >> KB);
+                slot[lane] = pack_half2(lo, hi);
+            }
+            if (e < kVEntries) {
+                const float lo = __shfl_sync(0xffffffffu, cv, e & ((1 << VB) - 1));
+                const float hi = __shfl_sync(0xffffffffu, cv, e >> VB);
+                slot[32 + lane] = pack_half2(lo, hi);
+            }
+        }
     }
 
     // ---- B fragments: column g = (head g/2, part g%2)
@@ -160,45 +257,46 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
             isum += __shfl_xor_sync(0xffffffffu, isum, 1);
             isum += __shfl_xor_sync(0xffffffffu, isum, 2);
             // <qp, sign> = scale * (2 * sum_{bit set} x16 - sum x16), and the MMA returns
-            // D = -(256 * hi + lo) summed over set bits
+            // D = -(256 * hi + lo) summed over the set bits
             const float scale = amax > 0.f ? amax / 32000.0f : 0.f;
             const float my_scale = -2.0f * scale, my_bias = -scale * (float)isum;
             sign_scale = __shfl_sync(0xffffffffu, my_scale, (2 * t) * 4);
             sign_bias = __shfl_sync(0xffffffffu, my_bias, (2 * t) * 4);
         }
     }
-    __syncthreads();
+    __syncthreads();  // tables complete
 
-    const int64_t row0 = (int64_t)b * a.cache_sb + (int64_t)h * a.cache_sh;
-    const int t_begin = split * a.tok_per_split;
-    const int t_end = min(a.N, t_begin + a.tok_per_split);
-    const int last = a.N - 1;
     const float kA = 0.08838834764831845f * 1.4426950408889634f;  // (1/sqrt(128)) * log2(e)
     const float kB = kA * (1.2533141373155003f / (float)TQ_D);     // ... * sqrt(pi/2)/D
     const uint8_t *lk = smem;        // key copies: bytes [0, 128) of every slot
     const uint8_t *lv = smem + 128;  // value copies: bytes [128, 256)
     const uint32_t lane_bits = lane * 4;
     const bool head_live = t < G;
+    bool timed_out = false;
 
     float m_run = -INFINITY, l_run = 0.f;
     float o[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-    for (int base = t_begin + warp * kTokIter; base < t_end; base += kWarps * kTokIter) {
-        const bool tail = base + kTokIter > t_end;
+    for (int it = 0; it < n_iter; ++it) {
+        const int base = my_first + it * kWarps * kStageTok;
+        const int st = it % kStages;
+        const uint8_t *sp = ring + st * L::kBytes;
+        if (!mbar_wait(bar_u32 + st * 8, (it / kStages) & 1)) timed_out = true;
+        const bool tail = base + kStageTok > t_end;
+
         // ------------------------------------------------------------ logits
-        float lg[kTiles][2];
+        float lg[2][2];
 #pragma unroll
-        for (int i = 0; i < kTiles; ++i) {
-            int tokA = base + 16 * i + 2 * g;
-            if (tail) tokA = min(tokA, last & ~1);  // stay on an even token inside the row
-            const int64_t rA = row0 + tokA;
+        for (int i = 0; i < 2; ++i) {
+            const int slotA = 16 * i + g, slotB = slotA + 8;
             uint32_t wa[KB + 1], wb[KB + 1];
             {
-                const uint32_t *pa = reinterpret_cast<const uint32_t *>(a.k_codes + rA * (16 * KB)) + KB * t;
+                const uint32_t *pa = reinterpret_cast<const uint32_t *>(sp + L::kK + slotA * (16 * KB)) + KB * t;
+                const uint32_t *pb = reinterpret_cast<const uint32_t *>(sp + L::kK + slotB * (16 * KB)) + KB * t;
 #pragma unroll
-                for (int w = 0; w < KB; ++w) wa[w] = __ldg(pa + w), wb[w] = __ldg(pa + 4 * KB + w);
+                for (int w = 0; w < KB; ++w) wa[w] = pa[w], wb[w] = pb[w];
                 wa[KB] = wb[KB] = 0;
             }
             float d1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -212,12 +310,12 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
                 const uint32_t a3 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wb, o1, lane_bits));
                 mma_f16(d1, a0, a1, a2, a3, bq[s][0], bq[s][1]);
             }
-            const float2 kn = half2_bits_to_float2(__ldg(reinterpret_cast<const uint32_t *>(a.k_norms + rA)));
-            float lgA = kn.x * kA * (d1[0] + d1[1]);
-            float lgB = kn.y * kA * (d1[2] + d1[3]);
+            const uint16_t *kn = reinterpret_cast<const uint16_t *>(sp + L::kKN);
+            float lgA = tq_half_bits_to_float(kn[slotA]) * kA * (d1[0] + d1[1]);
+            float lgB = tq_half_bits_to_float(kn[slotB]) * kA * (d1[2] + d1[3]);
             if (QJL) {
-                const uint32_t *ps = reinterpret_cast<const uint32_t *>(a.k_signs + rA * 16) + t;
-                const uint32_t sa = __ldg(ps), sb = __ldg(ps + 4);
+                const uint32_t sa = reinterpret_cast<const uint32_t *>(sp + L::kS + slotA * 16)[t];
+                const uint32_t sb = reinterpret_cast<const uint32_t *>(sp + L::kS + slotB * 16)[t];
                 int d2[4] = {0, 0, 0, 0};
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
@@ -227,24 +325,21 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
                     const uint32_t a3 = prmt(sb << (2 * n + 1), 0u, 0xBA98u);
                     mma_s8(d2, a0, a1, a2, a3, bp[n][0], bp[n][1]);
                 }
-                const float2 rn = half2_bits_to_float2(__ldg(reinterpret_cast<const uint32_t *>(a.k_rnorms + rA)));
+                const uint16_t *rn = reinterpret_cast<const uint16_t *>(sp + L::kRN);
                 const float sA = fmaf((float)(d2[0] * 256 + d2[1]), sign_scale, sign_bias);
                 const float sB = fmaf((float)(d2[2] * 256 + d2[3]), sign_scale, sign_bias);
-                lgA = fmaf(rn.x * kB, sA, lgA);
-                lgB = fmaf(rn.y * kB, sB, lgB);
+                lgA = fmaf(tq_half_bits_to_float(rn[slotA]) * kB, sA, lgA);
+                lgB = fmaf(tq_half_bits_to_float(rn[slotB]) * kB, sB, lgB);
             }
-            if (tail) {
-                const int real = base + 16 * i + 2 * g;
-                if (real >= t_end) lgA = -INFINITY;
-                if (real + 1 >= t_end) lgB = -INFINITY;
+            if (tail) {  // rows past the range hold stale bytes
+                if (base + slotA >= t_end) lgA = -INFINITY;
+                if (base + slotB >= t_end) lgB = -INFINITY;
             }
             lg[i][0] = head_live ? lgA : -INFINITY;
             lg[i][1] = head_live ? lgB : -INFINITY;
         }
         // ------------------------------------------------------------ online softmax (base 2), head t
-        float mx = lg[0][0];
-#pragma unroll
-        for (int i = 0; i < kTiles; ++i) mx = fmaxf(mx, fmaxf(lg[i][0], lg[i][1]));
+        float mx = fmaxf(fmaxf(lg[0][0], lg[0][1]), fmaxf(lg[1][0], lg[1][1]));
 #pragma unroll
         for (int sft = 4; sft <= 16; sft <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
         const float nm = fmaxf(m_run, mx);
@@ -256,41 +351,35 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
             m_run = nm;
         }
         const float sub = (m_run == -INFINITY) ? 0.f : m_run;
-        uint32_t pb[kTiles][2];
+        uint32_t pb[2][2];
 #pragma unroll
-        for (int i = 0; i < kTiles; ++i) {
-            int tokA = base + 16 * i + 2 * g;
-            if (tail) tokA = min(tokA, last & ~1);
-            const float2 vn = half2_bits_to_float2(__ldg(reinterpret_cast<const uint32_t *>(a.v_norms + row0 + tokA)));
+        for (int i = 0; i < 2; ++i) {
+            const uint16_t *vn = reinterpret_cast<const uint16_t *>(sp + L::kVN);
+            const float vnA = tq_half_bits_to_float(vn[16 * i + g]), vnB = tq_half_bits_to_float(vn[16 * i + g + 8]);
             const float pA = fast_exp2(lg[i][0] - sub), pB = fast_exp2(lg[i][1] - sub);
             l_run += pA + pB;
-            // rows = token slots, cols = (head t, unused)  ->  transpose to rows = columns
-            // (a masked token may sit on an unwritten row whose norm is not finite)
-            pb[i][0] = movmatrix_trans(pack_half2(pA > 0.f ? pA * vn.x : 0.f, 0.f));
-            pb[i][1] = movmatrix_trans(pack_half2(pB > 0.f ? pB * vn.y : 0.f, 0.f));
+            // rows = token slots, cols = (head t, unused) -> transpose to rows = columns.
+            // (a masked token's staged norm may be stale and not finite)
+            pb[i][0] = movmatrix_trans(pack_half2(pA > 0.f ? pA * vnA : 0.f, 0.f));
+            pb[i][1] = movmatrix_trans(pack_half2(pB > 0.f ? pB * vnB : 0.f, 0.f));
         }
         // ------------------------------------------------------------ values
 #pragma unroll
-        for (int i = 0; i < kTiles; ++i) {
-            const int tk = base + 16 * i + 4 * t;
-            const uint8_t *vrow = a.v_codes + (row0 + (tail ? min(tk, last) : tk)) * (16 * VB);
-            const int step1 = tail ? (min(tk + 1, last) - min(tk, last)) * (16 * VB) : 16 * VB;
-            const int step2 = tail ? (min(tk + 2, last) - min(tk, last)) * (16 * VB) : 32 * VB;
-            const int step3 = tail ? (min(tk + 3, last) - min(tk, last)) * (16 * VB) : 48 * VB;
-            const uint64_t w0 = load_v_chunk<VB>(vrow, g);
-            const uint64_t w1 = load_v_chunk<VB>(vrow + step1, g);
-            const uint64_t w2 = load_v_chunk<VB>(vrow + step2, g);
-            const uint64_t w3 = load_v_chunk<VB>(vrow + step3, g);
+        for (int i = 0; i < 2; ++i) {
+            const uint8_t *vrow = sp + L::kV + (16 * i + 2 * t) * (16 * VB);
+            const uint64_t w0 = lds_v_chunk<VB>(vrow, g);                   // token 2t     (k-slot 2t)
+            const uint64_t w1 = lds_v_chunk<VB>(vrow + 16 * VB, g);         // token 2t+1   (k-slot 2t+1)
+            const uint64_t w2 = lds_v_chunk<VB>(vrow + 8 * 16 * VB, g);     // token 2t+8   (k-slot 2t+8)
+            const uint64_t w3 = lds_v_chunk<VB>(vrow + 9 * 16 * VB, g);     // token 2t+9   (k-slot 2t+9)
             constexpr uint64_t me = even_field_mask<VB>();
-            // k-slots (2t, 2t+1) hold tokens (4t, 4t+2); k-slots (2t+8, 2t+9) hold (4t+1, 4t+3)
-            const uint64_t x02 = (w0 & me) | ((w2 << VB) & (me << VB));
-            const uint64_t y02 = ((w0 >> VB) & me) | (w2 & (me << VB));
-            const uint64_t x13 = (w1 & me) | ((w3 << VB) & (me << VB));
-            const uint64_t y13 = ((w1 >> VB) & me) | (w3 & (me << VB));
-            const uint32_t xa[3] = {(uint32_t)x02, (uint32_t)(x02 >> 32), 0u};
-            const uint32_t ya[3] = {(uint32_t)y02, (uint32_t)(y02 >> 32), 0u};
-            const uint32_t xb[3] = {(uint32_t)x13, (uint32_t)(x13 >> 32), 0u};
-            const uint32_t yb[3] = {(uint32_t)y13, (uint32_t)(y13 >> 32), 0u};
+            const uint64_t x01 = (w0 & me) | ((w1 << VB) & (me << VB));
+            const uint64_t y01 = ((w0 >> VB) & me) | (w1 & (me << VB));
+            const uint64_t x23 = (w2 & me) | ((w3 << VB) & (me << VB));
+            const uint64_t y23 = ((w2 >> VB) & me) | (w3 & (me << VB));
+            const uint32_t xa[3] = {(uint32_t)x01, (uint32_t)(x01 >> 32), 0u};
+            const uint32_t ya[3] = {(uint32_t)y01, (uint32_t)(y01 >> 32), 0u};
+            const uint32_t xb[3] = {(uint32_t)x23, (uint32_t)(x23 >> 32), 0u};
+            const uint32_t yb[3] = {(uint32_t)y23, (uint32_t)(y23 >> 32), 0u};
 #pragma unroll
             for (int mt = 0; mt < 8; ++mt) {
                 constexpr int W = 2 * VB;
@@ -301,10 +390,14 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
                 mma_f16(o[mt], a0, a1, a2, a3, pb[i][0], pb[i][1]);
             }
         }
+        // ------------------------------------------------------------ refill this stage
+        __syncwarp();
+        if (lane == 0 && it + kStages < n_iter) issue(it + kStages);
     }
+    if (timed_out && lane == 0) atomicExch(a.error_flag, 1);
 
     // ---- merge the warps of the CTA, write the split partial
-    __syncthreads();  // the tables are dead; reuse shared memory
+    __syncthreads();  // tables and rings are dead; reuse shared memory
     float *s_acc = reinterpret_cast<float *>(smem);   // [kWarps][4][128]
     float *s_m = s_acc + kWarps * 4 * TQ_D;           // [kWarps][4]
     float *s_l = s_m + kWarps * 4;
@@ -317,34 +410,37 @@ __global__ void __launch_bounds__(kWarps * 32, 3) tq_decode_mma4_kernel(Mma4Args
         r[0] = o[mt][0], r[1] = o[mt][2];
     }
     __syncthreads();
-    const int d = threadIdx.x;
-    for (int hh = 0; hh < G; ++hh) {
+    for (int idx = threadIdx.x; idx < G * TQ_D; idx += blockDim.x) {
+        const int hh = idx / TQ_D, d = idx % TQ_D;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w * 4 + hh]);
-        float L = 0.f, A = 0.f;
+        float Lsum = 0.f, A = 0.f;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
             const float mw = s_m[w * 4 + hh];
             const float sc = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-            L += s_l[w * 4 + hh] * sc;
+            Lsum += s_l[w * 4 + hh] * sc;
             A += s_acc[(w * 4 + hh) * TQ_D + d] * sc;
         }
         const int64_t prow = (q_row0 + hh) * a.n_splits + split;
         a.part_acc[prow * TQ_D + d] = A;
-        if (d == 0) a.part_m[prow] = M * 0.6931471805599453f, a.part_l[prow] = L;  // natural-log units
+        if (d == 0) a.part_m[prow] = M * 0.6931471805599453f, a.part_l[prow] = Lsum;  // natural-log units
     }
 }
 
-template <int KB, int VB> size_t mma4_smem_bytes() {
+template <int KB, int VB, bool QJL> size_t mma4_smem_bytes() {
     const int kk = 1 << (2 * KB), kv = 1 << (2 * VB);
     const size_t lut = (size_t)(kk > kv ? kk : kv) * kSlotWords * 4;
+    const size_t rings = (size_t)kWarps * kStages * StageLayout<KB, VB, QJL>::kBytes;
+    const size_t bars = (size_t)kWarps * kStages * 8;
     const size_t merge = ((size_t)kWarps * 4 * TQ_D + 2 * kWarps * 4) * sizeof(float);
-    return lut > merge ? lut : merge;
+    const size_t main = lut + rings + bars;
+    return main > merge ? main : merge;
 }
 
 template <int KB, int VB, bool QJL> cudaError_t launch_mma4(const Mma4Args &a, dim3 grid, cudaStream_t stream) {
-    const size_t smem = mma4_smem_bytes<KB, VB>();
+    const size_t smem = mma4_smem_bytes<KB, VB, QJL>();
     static bool configured = false;  // per instantiation
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(tq_decode_mma4_kernel<KB, VB, QJL>,
@@ -357,6 +453,8 @@ template <int KB, int VB, bool QJL> cudaError_t launch_mma4(const Mma4Args &a, d
 }
 
 }  // namespace
+
+int tq_mma4_tokens_per_cta_step() { return kWarps * kStageTok; }
 
 int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
                               const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
@@ -373,12 +471,13 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     a.v_codes = cache->v_codes, a.v_norms = cache->v_norms;
     a.cache_sb = cache->stride_b, a.cache_sh = cache->stride_h;
     a.Hkv = cache->kv_heads, a.G = q_heads / cache->kv_heads, a.N = seq_len, a.n_splits = n_splits;
-    const int per_iter = kWarps * kTokIter;
+    const int per_iter = kWarps * kStageTok;
     a.tok_per_split = ((seq_len + n_splits - 1) / n_splits + per_iter - 1) / per_iter * per_iter;
     if (a.tok_per_split < per_iter) a.tok_per_split = per_iter;
     a.qrot = w.qrot, a.qproj = w.qproj;
     a.part_m = w.part_m, a.part_l = w.part_l, a.part_acc = w.part_acc;
     a.centers_k = ctx->centers_k, a.centers_v = ctx->centers_v;
+    a.error_flag = ctx->error_flag;
     dim3 grid(n_splits, cache->batch * cache->kv_heads);
     const int mode = ctx->use_qjl * 10 + ctx->bits;
     tq_prof_count(ctx, 3);

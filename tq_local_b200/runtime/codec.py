@@ -118,6 +118,12 @@ class Codec:
                   "tq_profile_read")
         return ms.value, n_main.value, n_all.value
 
+    def device_status(self) -> int:
+        """0 unless a kernel's bounded wait ever ran out (synchronises with the device)."""
+        v = C.c_int32()
+        ffi.check(ffi.lib().tq_device_status(self.handle, C.byref(v)), "tq_device_status")
+        return v.value
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             ffi.lib().tq_ctx_destroy(self.handle)

@@ -19,7 +19,7 @@ TQ_MAX_GROUPS = 8
 EXPORTS = (
     "tq_abi_version", "tq_last_cuda_error", "tq_ctx_create", "tq_ctx_destroy", "tq_pack",
     "tq_decode_workspace_bytes", "tq_decode_suggest_splits", "tq_decode_attn", "tq_dequant",
-    "tq_key_norm_sum", "tq_profile_enable", "tq_profile_read",
+    "tq_key_norm_sum", "tq_profile_enable", "tq_profile_read", "tq_device_status",
 )
 
 _ERRORS = {-1: "bad argument", -2: "unsupported shape or mode", -3: "CUDA error", -4: "workspace too small"}
@@ -94,6 +94,8 @@ def lib() -> C.CDLL:
     L.tq_profile_enable.restype = C.c_int32
     L.tq_profile_read.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
     L.tq_profile_read.restype = C.c_int32
+    L.tq_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+    L.tq_device_status.restype = C.c_int32
     _lib = L
     return L
 

@@ -331,6 +331,7 @@ def run_gpu_arm(args) -> None:
                 "value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(all_launches),
+            "device_status": codec.device_status(),
             "clocks": clocks,
             "pack": {"seconds": pack_s, "vectors_per_s": 2 * batch * hkv * n_ctx / pack_s},
         }

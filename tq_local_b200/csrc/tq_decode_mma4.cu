@@ -104,15 +104,26 @@ __device__ __forceinline__ void tma_load_1d(uint32_t dst, const void *src, uint3
                  : "memory");
 }
 
-// Byte offset of this lane's copy of the table slot selected by the WIDTH-bit field at bit
-// `off` of the little-endian word array `w`: slot * 256 + lane_bits, where lane_bits < 256
-// is the lane's offset inside a slot.  `off` is a compile-time constant after unrolling.
-// A byte-aligned 8-bit field takes one byte permute (field -> byte 1, lane_bits -> byte 0);
-// any other field takes a shift and one three-input logic op (or a funnel shift first when
-// it straddles two words; w[off/32+1] must exist).
+// The centre-pair table sits at shared-memory address kTableAddr, a multiple of 65536, so
+// that a complete address can be assembled without an add: bits 16+ are the table base,
+// byte 1 is the slot index (slot stride 256 B) and byte 0 the lane's offset inside the slot.
+constexpr uint32_t kTableAddr = 65536;
+
+__device__ __forceinline__ uint32_t lds_abs(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// Shared-memory address of this lane's copy of the table slot selected by the WIDTH-bit
+// field at bit `off` of the little-endian word array `w`.  `lane_bits` = kTableAddr + the
+// lane's offset inside a slot (< 256).  `off` is a compile-time constant after unrolling.
+// A byte-aligned 8-bit field takes one byte permute (field -> byte 1, the rest from
+// lane_bits); any other field takes a shift and one three-input logic op (or a funnel shift
+// first when it straddles two words; w[off/32+1] must exist).
 template <int WIDTH> __device__ __forceinline__ uint32_t slot_offset(const uint32_t *w, int off, uint32_t lane_bits) {
     const int wi = off >> 5, s = off & 31;
-    if (WIDTH == 8 && (s & 7) == 0) return prmt(w[wi], lane_bits, 0x5504u | ((uint32_t)(s >> 3) << 4));
+    if (WIDTH == 8 && (s & 7) == 0) return prmt(w[wi], lane_bits, 0x7604u | ((uint32_t)(s >> 3) << 4));
     constexpr uint32_t kMask = ((1u << WIDTH) - 1u) << 8;
     uint32_t x;
     if (s + WIDTH <= 32) {
@@ -142,9 +153,23 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     constexpr int kKEntries = 1 << (2 * KB), kVEntries = 1 << (2 * VB);
     constexpr int kEntries = kKEntries > kVEntries ? kKEntries : kVEntries;
     constexpr int kTableBytes = kEntries * kSlotWords * 4;
-    uint32_t *table = reinterpret_cast<uint32_t *>(smem);
-    uint8_t *rings = smem + kTableBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(rings + kWarps * kStages * L::kBytes);
+    static_assert(kTableBytes <= 65536, "table must fit between two 64 KB boundaries");
+    // Shared-memory map (absolute shared addresses): [dynamic base, 65536) the first rings,
+    // [65536, 65536 + table) the centre-pair table, then the remaining rings and the mbarriers.
+    const uint32_t dyn_base = smem_u32(smem);
+    constexpr int kRingBytes = kStages * L::kBytes;
+    const int rings_low = dyn_base <= kTableAddr ? min(kWarps, (int)((kTableAddr - dyn_base) / kRingBytes)) : 0;
+    const uint32_t high_base = kTableAddr + ((kTableBytes + 127) / 128) * 128;
+    const uint32_t bars_addr = high_base + (kWarps - rings_low) * kRingBytes;
+    {
+        uint32_t dyn_size;
+        asm("mov.u32 %0, %%dynamic_smem_size;\n" : "=r"(dyn_size));
+        if (dyn_base > kTableAddr || bars_addr + kWarps * kStages * 8 > dyn_base + dyn_size) {
+            if (threadIdx.x == 0) atomicExch(a.error_flag, 2);  // layout does not fit: refuse to run
+            return;
+        }
+    }
+    uint32_t *table = reinterpret_cast<uint32_t *>(smem + (kTableAddr - dyn_base));
 
     const int split = blockIdx.x;
     const int bh = blockIdx.y;
@@ -158,9 +183,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     const int t_end = min(a.N, t_begin + a.tok_per_split);
 
     // ---- ring set-up and the first loads (overlap with the table build below)
-    uint8_t *ring = rings + warp * kStages * L::kBytes;
-    const uint32_t ring_u32 = smem_u32(ring);
-    const uint32_t bar_u32 = smem_u32(bars + warp * kStages);
+    const uint32_t ring_u32 = warp < rings_low ? dyn_base + warp * kRingBytes
+                                               : high_base + (warp - rings_low) * kRingBytes;
+    const uint8_t *ring = smem + (ring_u32 - dyn_base);
+    const uint32_t bar_u32 = bars_addr + warp * kStages * 8;
     const int my_first = t_begin + warp * kStageTok;
     const int n_iter = my_first < t_end ? (t_end - my_first + kWarps * kStageTok - 1) / (kWarps * kStageTok) : 0;
 
@@ -268,9 +294,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
 
     const float kA = 0.08838834764831845f * 1.4426950408889634f;  // (1/sqrt(128)) * log2(e)
     const float kB = kA * (1.2533141373155003f / (float)TQ_D);     // ... * sqrt(pi/2)/D
-    const uint8_t *lk = smem;        // key copies: bytes [0, 128) of every slot
-    const uint8_t *lv = smem + 128;  // value copies: bytes [128, 256)
-    const uint32_t lane_bits = lane * 4;
+    const uint32_t lane_k = kTableAddr + lane * 4;        // key copies: bytes [0, 128) of every slot
+    const uint32_t lane_v = kTableAddr + 128 + lane * 4;  // value copies: bytes [128, 256)
     const bool head_live = t < G;
     bool timed_out = false;
 
@@ -304,10 +329,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
             for (int s = 0; s < 8; ++s) {
                 constexpr int W = 2 * KB;
                 const int o0 = (2 * s) * W, o1 = (2 * s + 1) * W;
-                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wa, o0, lane_bits));
-                const uint32_t a1 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wb, o0, lane_bits));
-                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wa, o1, lane_bits));
-                const uint32_t a3 = *reinterpret_cast<const uint32_t *>(lk + slot_offset<W>(wb, o1, lane_bits));
+                const uint32_t a0 = lds_abs(slot_offset<W>(wa, o0, lane_k));
+                const uint32_t a1 = lds_abs(slot_offset<W>(wb, o0, lane_k));
+                const uint32_t a2 = lds_abs(slot_offset<W>(wa, o1, lane_k));
+                const uint32_t a3 = lds_abs(slot_offset<W>(wb, o1, lane_k));
                 mma_f16(d1, a0, a1, a2, a3, bq[s][0], bq[s][1]);
             }
             const uint16_t *kn = reinterpret_cast<const uint16_t *>(sp + L::kKN);
@@ -383,10 +408,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
 #pragma unroll
             for (int mt = 0; mt < 8; ++mt) {
                 constexpr int W = 2 * VB;
-                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(xa, mt * W, lane_bits));
-                const uint32_t a1 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(ya, mt * W, lane_bits));
-                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(xb, mt * W, lane_bits));
-                const uint32_t a3 = *reinterpret_cast<const uint32_t *>(lv + slot_offset<W>(yb, mt * W, lane_bits));
+                const uint32_t a0 = lds_abs(slot_offset<W>(xa, mt * W, lane_v));
+                const uint32_t a1 = lds_abs(slot_offset<W>(ya, mt * W, lane_v));
+                const uint32_t a2 = lds_abs(slot_offset<W>(xb, mt * W, lane_v));
+                const uint32_t a3 = lds_abs(slot_offset<W>(yb, mt * W, lane_v));
                 mma_f16(o[mt], a0, a1, a2, a3, pb[i][0], pb[i][1]);
             }
         }
@@ -429,15 +454,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     }
 }
 
-template <int KB, int VB, bool QJL> size_t mma4_smem_bytes() {
-    const int kk = 1 << (2 * KB), kv = 1 << (2 * VB);
-    const size_t lut = (size_t)(kk > kv ? kk : kv) * kSlotWords * 4;
-    const size_t rings = (size_t)kWarps * kStages * StageLayout<KB, VB, QJL>::kBytes;
-    const size_t bars = (size_t)kWarps * kStages * 8;
-    const size_t merge = ((size_t)kWarps * 4 * TQ_D + 2 * kWarps * 4) * sizeof(float);
-    const size_t main = lut + rings + bars;
-    return main > merge ? main : merge;
-}
+// The kernel lays its rings around a table pinned at a 64 KB boundary and checks the fit
+// itself, so it is always given the largest dynamic allocation a CTA can have.
+template <int KB, int VB, bool QJL> size_t mma4_smem_bytes() { return 227 * 1024; }
 
 template <int KB, int VB, bool QJL> cudaError_t launch_mma4(const Mma4Args &a, dim3 grid, cudaStream_t stream) {
     const size_t smem = mma4_smem_bytes<KB, VB, QJL>();

@@ -67,7 +67,7 @@ template <int KB, int VB, bool QJL> struct StageLayout {
     static constexpr int kKN = kS + (QJL ? kStageTok * 16 : 0);
     static constexpr int kVN = kKN + kStageTok * 2;
     static constexpr int kRN = kVN + kStageTok * 2;
-    static constexpr int kBytes = (kRN + (QJL ? kStageTok * 2 : 0) + 127) / 128 * 128;
+    static constexpr int kBytes = (kRN + (QJL ? kStageTok * 2 : 0) + 15) / 16 * 16;
 };
 
 // ---- mbarrier / TMA bulk-copy wrappers (shared::cta addresses) ----

@@ -3,6 +3,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <algorithm>
+#include <queue>
 #include <vector>
 
 #include "tq_common.cuh"
@@ -222,23 +224,38 @@ extern "C" size_t tq_decode_workspace_bytes(int32_t batch, int32_t q_heads, int3
 
 extern "C" int32_t tq_decode_suggest_splits(tq_ctx *ctx, int32_t batch, int32_t kv_heads, int32_t seq_len) {
     if (!ctx || batch <= 0 || kv_heads <= 0 || seq_len <= 0) return 1;
-    // The decode kernel runs one 12-warp CTA per SM and walks tokens 384 at a time per CTA.
-    // Pick the tokens-per-split (a multiple of 384) that best balances two effects:
-    // the last partial wave of CTAs, and the fixed per-CTA cost (table build, pipeline
-    // fill, partial write-back), taken as the time of about 256 tokens.
+    // The decode kernel runs one CTA per SM; a CTA costs its tokens plus a fixed part (table
+    // build, pipeline fill, partial write-back) worth about 256 tokens.  For every candidate
+    // tokens-per-split (a multiple of the kernel's step) replay the hardware's in-order
+    // assignment of CTAs to SMs and keep the candidate with the shortest makespan.
     const int rows = batch * kv_heads;
-    const double slots = (double)ctx->sm_count;
-    const int step = 384;
-    double best_score = -1.0;
+    const int step = tq_mma4_tokens_per_cta_step();
+    const int64_t key = ((int64_t)rows << 32) | (uint32_t)((seq_len + step - 1) / step);
+    if (ctx->splits_cache_key == key) return ctx->splits_cache_val;
+    const int slots = ctx->sm_count;
+    const double fixed = 256.0;
+    double best = 1e300;
     int best_splits = 1;
+    std::vector<double> free_at(slots);
     for (int tok = step; tok < seq_len + step; tok += step) {
         const int splits = (seq_len + tok - 1) / tok;
-        if (splits > 1024) continue;
-        const double waves = rows * (double)splits / slots;
-        const double eff = waves / ceil(waves);
-        const double score = eff * tok / (tok + 256.0);
-        if (score > best_score + 1e-9) best_score = score, best_splits = splits;
+        if (splits > 256 || (int64_t)rows * splits > 65536) continue;
+        std::priority_queue<double, std::vector<double>, std::greater<double>> pq;
+        for (int i = 0; i < slots; ++i) pq.push(0.0);
+        double makespan = 0.0;
+        for (int r = 0; r < rows; ++r)
+            for (int sidx = 0; sidx < splits; ++sidx) {
+                const int n = std::min(tok, seq_len - sidx * tok);
+                const double t0 = pq.top();
+                pq.pop();
+                const double t1 = t0 + fixed + n;
+                pq.push(t1);
+                if (t1 > makespan) makespan = t1;
+            }
+        if (makespan < best - 1e-9) best = makespan, best_splits = splits;
     }
+    ctx->splits_cache_key = key;
+    ctx->splits_cache_val = best_splits;
     return best_splits;
 }
 

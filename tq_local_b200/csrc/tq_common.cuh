@@ -38,6 +38,8 @@ struct tq_ctx {
     size_t base_bytes;
     struct tq_prof *prof;  // measurement hooks, see tq_profile_enable
     int *error_flag;       // device word, set by a kernel whose bounded wait ran out
+    int64_t splits_cache_key;  // last (rows, length bucket) asked of tq_decode_suggest_splits
+    int splits_cache_val;
 };
 
 // Measurement hooks: bracket the main decode kernel with events, count launches.
@@ -100,6 +102,7 @@ int32_t tq_launch_decode_mma(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_
                              const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
                              const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
                              void *workspace, void *out, cudaStream_t stream);
+int tq_mma4_tokens_per_cta_step();
 int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
                               const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
                               const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,

@@ -21,10 +21,10 @@
 //   values   O^T[128 x (4 heads x {P, 0})] += Vdeq^T[128 x 16 tok] * P                   f16 m16n8k16
 // A operands are built in registers from the packed words.  The contraction order of an
 // MMA is free, so every lane gets codes that sit together in memory:
-//   keys    lane (g, t): dims [32t, 32t+32) of tokens g and g+8 of a 16-token tile; two
+//   keys    lane (g, t): dims [32t, 32t+32) of two tokens of a 16-token tile; two
 //           neighbouring codes index a per-lane-replicated shared-memory table of f16x2
 //           centre pairs (slot e, lane l -> bank l: no bank conflicts);
-//   values  lane (g, t): dims [16g, 16g+16) of tokens 2t, 2t+1, 2t+8, 2t+9; the codes of two
+//   values  lane (g, t): dims [16g, 16g+16) of tokens t, t+4, t+8, t+12; the codes of two
 //           tokens are interleaved with bit-selects so one look-up yields the (token a,
 //           token b) f16x2 that the MMA wants along its K axis.
 // Softmax is online, base 2, in registers; P*|v| goes to f16 and is transposed with
@@ -38,9 +38,9 @@
 
 namespace {
 
-constexpr int kWarps = 12;
+constexpr int kWarps = 16;
 constexpr int kStageTok = 32;  // tokens per ring stage (two 16-token MMA tiles)
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr int kSlotWords = 64;  // table slot: 32 key words then 32 value words (256 B)
 constexpr uint32_t kSpinLimit = 1u << 22;  // mbarrier polls before a wait gives up
 
@@ -315,7 +315,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         float lg[2][2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const int slotA = 16 * i + g, slotB = slotA + 8;
+            // token slot s of the tile holds token pi(s): pi(2j) = j, pi(2j+1) = j+4, pi(s+8) = pi(s)+8,
+            // which lets the value reads below touch four consecutive rows per instruction
+            const int slotA = 16 * i + (g >> 1) + 4 * (g & 1), slotB = slotA + 8;
             uint32_t wa[KB + 1], wb[KB + 1];
             {
                 const uint32_t *pa = reinterpret_cast<const uint32_t *>(sp + L::kK + slotA * (16 * KB)) + KB * t;
@@ -380,7 +382,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const uint16_t *vn = reinterpret_cast<const uint16_t *>(sp + L::kVN);
-            const float vnA = tq_half_bits_to_float(vn[16 * i + g]), vnB = tq_half_bits_to_float(vn[16 * i + g + 8]);
+            const int slotA = 16 * i + (g >> 1) + 4 * (g & 1);
+            const float vnA = tq_half_bits_to_float(vn[slotA]), vnB = tq_half_bits_to_float(vn[slotA + 8]);
             const float pA = fast_exp2(lg[i][0] - sub), pB = fast_exp2(lg[i][1] - sub);
             l_run += pA + pB;
             // rows = token slots, cols = (head t, unused) -> transpose to rows = columns.
@@ -391,11 +394,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         // ------------------------------------------------------------ values
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const uint8_t *vrow = sp + L::kV + (16 * i + 2 * t) * (16 * VB);
-            const uint64_t w0 = lds_v_chunk<VB>(vrow, g);                   // token 2t     (k-slot 2t)
-            const uint64_t w1 = lds_v_chunk<VB>(vrow + 16 * VB, g);         // token 2t+1   (k-slot 2t+1)
-            const uint64_t w2 = lds_v_chunk<VB>(vrow + 8 * 16 * VB, g);     // token 2t+8   (k-slot 2t+8)
-            const uint64_t w3 = lds_v_chunk<VB>(vrow + 9 * 16 * VB, g);     // token 2t+9   (k-slot 2t+9)
+            const uint8_t *vrow = sp + L::kV + (16 * i + t) * (16 * VB);
+            const uint64_t w0 = lds_v_chunk<VB>(vrow, g);                    // token t      (k-slot 2t)
+            const uint64_t w1 = lds_v_chunk<VB>(vrow + 4 * 16 * VB, g);      // token t+4    (k-slot 2t+1)
+            const uint64_t w2 = lds_v_chunk<VB>(vrow + 8 * 16 * VB, g);      // token t+8    (k-slot 2t+8)
+            const uint64_t w3 = lds_v_chunk<VB>(vrow + 12 * 16 * VB, g);     // token t+12   (k-slot 2t+9)
             constexpr uint64_t me = even_field_mask<VB>();
             const uint64_t x01 = (w0 & me) | ((w1 << VB) & (me << VB));
             const uint64_t y01 = ((w0 >> VB) & me) | (w1 & (me << VB));

@@ -1,0 +1,209 @@
+"""Greedy generation over a packed prefill cache.
+
+Mirror of the reference's ``src/turboquant/runtime/generation.py``
+(``greedy_decode_with_prefill_cache``, ``GenerationMetrics``, ``GenerationOutput``): dense
+prefill with the model's own attention, pack the prefill cache, switch the model to the
+``"turboquant"`` attention backend, then one forward pass per new token.  Differences, all
+on the host side of the hot path:
+
+* the packed cache is allocated once with room for ``max_new_tokens`` (no per-token
+  ``torch.cat``);
+* only the last position's logits are requested from the prefill;
+* the EOS test reads the device every few steps instead of every step and the result is
+  trimmed afterwards, so the returned text is the same;
+* all batch rows are kept (``GenerationOutput.completion_ids``); ``text`` is row 0 as in
+  the reference.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import asdict, dataclass
+from typing import Any
+
+from tq_local_b200.runtime.memory_accounting import (
+    gpu_current_memory_bytes,
+    gpu_peak_memory_bytes,
+    past_key_values_memory_breakdown,
+    turboquant_mse_packed_bytes,
+)
+from tq_local_b200.runtime.packed_qmse_cache import (
+    build_packed_mse_cache,
+    packed_cache_storage_breakdown,
+    verify_packed_reconstruction,
+)
+
+_EOS_POLL_STEPS = 8
+
+
+@dataclass(frozen=True)
+class GenerationMetrics:
+    variant: str
+    qmse_bits: int | None
+    quantization_seconds: float
+    generation_seconds: float
+    prompt_tokens: int
+    completion_tokens: int
+    prefill_cache: dict[str, Any]
+    turboquant_mse_packed_estimate: dict[str, Any] | None
+    turboquant_mse_packed_actual: dict[str, Any] | None
+    post_cache_setup_gpu_memory: dict[str, Any] | None
+    gpu_peak_memory: dict[str, Any] | None
+    reconstruction_quality: list[dict[str, Any]] | None = None
+
+    def to_dict(self) -> dict[str, Any]:
+        return asdict(self)
+
+
+@dataclass(frozen=True)
+class GenerationOutput:
+    text: str
+    metrics: GenerationMetrics
+    completion_ids: Any = None  # LongTensor [batch, new_tokens]; rows padded with EOS after their end
+
+
+def validate_generation_variant(variant: str) -> None:
+    if variant not in {"baseline", "qmse", "qmse_packed"}:
+        raise ValueError(
+            f"Unsupported generation variant={variant!r}. Choose from ['baseline', 'qmse', 'qmse_packed']."
+        )
+    if variant == "qmse":
+        raise NotImplementedError("the unpacked 'qmse' variant is not provided; use 'qmse_packed'")
+
+
+def eos_token_ids(model, tokenizer) -> set[int]:
+    eos = getattr(getattr(model, "generation_config", None), "eos_token_id", None)
+    if eos is None:
+        eos = getattr(tokenizer, "eos_token_id", None)
+    if eos is None:
+        return set()
+    return {int(eos)} if isinstance(eos, int) else {int(x) for x in eos}
+
+
+def _prefill(model, inputs):
+    """Dense prefill; ask for the last position's logits only when the model supports it."""
+    try:
+        return model(**inputs, use_cache=True, logits_to_keep=1)
+    except TypeError:
+        return model(**inputs, use_cache=True)
+
+
+def greedy_decode_with_prefill_cache(
+    *,
+    model,
+    tokenizer,
+    inputs,
+    max_new_tokens: int,
+    variant: str,
+    qmse_bits: int,
+    rotation_seed: int = 0,
+    num_outlier_channels: int = 0,
+    outlier_extra_bits: int = 1,
+    use_qjl_keys: bool = False,
+    quantize_decode: bool = False,
+    norm_guard: bool = True,
+    verify: bool = True,
+    shard=None,
+) -> GenerationOutput:
+    import torch
+
+    validate_generation_variant(variant)
+    if max_new_tokens <= 0:
+        raise ValueError("max_new_tokens must be positive.")
+
+    started = time.monotonic()
+    quant_seconds = 0.0
+    eos_ids = eos_token_ids(model, tokenizer)
+    packed_cache = None
+    old_impl = None
+
+    with torch.inference_mode():
+        outputs = _prefill(model, inputs)
+        cache = outputs.past_key_values
+        next_token = torch.argmax(outputs.logits[:, -1, :], dim=-1, keepdim=True)
+        del outputs
+        dense_breakdown = past_key_values_memory_breakdown(cache)
+        estimate = actual = recon = None
+        if variant == "qmse_packed":
+            estimate = turboquant_mse_packed_bytes(
+                num_vectors_per_kind=dense_breakdown["num_key_value_vectors_per_kind"],
+                vector_dimension=dense_breakdown["vector_dimension"],
+                bits=qmse_bits,
+            )
+            t0 = time.monotonic()
+            packed_cache = build_packed_mse_cache(
+                cache, bits=qmse_bits, seed=rotation_seed, num_outlier_channels=num_outlier_channels,
+                outlier_extra_bits=outlier_extra_bits, use_qjl_keys=use_qjl_keys, quantize_decode=quantize_decode,
+                norm_guard=norm_guard, reserve_tokens=max_new_tokens, shard=shard, release_dense=not verify,
+            )
+            if verify:
+                recon = verify_packed_reconstruction(cache, packed_cache)
+            actual = packed_cache_storage_breakdown(packed_cache)
+            cache = packed_cache
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            quant_seconds += time.monotonic() - t0
+
+            from tq_local_b200.adapters.transformers import enable_turboquant_attention
+
+            old_impl = enable_turboquant_attention(model, packed_cache)
+
+        try:
+            if torch.cuda.is_available():
+                torch.cuda.empty_cache()
+            post_setup = gpu_current_memory_bytes()
+            if torch.cuda.is_available():
+                torch.cuda.reset_peak_memory_stats()
+
+            eos_tensor = (torch.tensor(sorted(eos_ids), device=next_token.device) if eos_ids else None)
+            generated = [next_token]
+            mask = inputs.get("attention_mask")
+            for step in range(max_new_tokens - 1):
+                if eos_tensor is not None and step % _EOS_POLL_STEPS == 0:
+                    seen = torch.isin(torch.cat(generated, dim=-1), eos_tensor).any(dim=-1)
+                    if bool(seen.all()):
+                        break
+                if mask is not None:
+                    mask = torch.cat((mask, mask.new_ones((mask.shape[0], 1))), dim=-1)
+                out = model(input_ids=next_token, attention_mask=mask, past_key_values=cache, use_cache=True)
+                cache = out.past_key_values
+                next_token = torch.argmax(out.logits[:, -1, :], dim=-1, keepdim=True)
+                generated.append(next_token)
+        finally:
+            if packed_cache is not None:
+                from tq_local_b200.adapters.transformers import disable_turboquant_attention
+
+                disable_turboquant_attention(model, packed_cache, old_impl)
+
+        completion = torch.cat(generated, dim=-1)
+        if eos_tensor is not None:
+            # Cut every row after its first EOS (which is kept, as in the reference); the batch
+            # is as long as its longest row and shorter rows are padded with their EOS.
+            hit = torch.isin(completion, eos_tensor)
+            steps = torch.arange(completion.shape[1], device=completion.device).expand_as(completion)
+            first = torch.where(hit, steps, torch.full_like(steps, completion.shape[1] - 1)).min(dim=-1).values
+            keep = int(first.max().item()) + 1
+            completion = completion[:, :keep].clone()
+            for row in range(completion.shape[0]):
+                end = int(first[row])
+                completion[row, end + 1:] = completion[row, end]
+            row0_len = int(first[0]) + 1
+        else:
+            row0_len = completion.shape[1]
+
+    text = tokenizer.decode(completion[0, :row0_len], skip_special_tokens=True).strip()
+    metrics = GenerationMetrics(
+        variant=variant,
+        qmse_bits=qmse_bits if variant == "qmse_packed" else None,
+        quantization_seconds=round(quant_seconds, 4),
+        generation_seconds=round(time.monotonic() - started, 4),
+        prompt_tokens=int(inputs["input_ids"].shape[-1]),
+        completion_tokens=int(row0_len),
+        prefill_cache=dense_breakdown,
+        turboquant_mse_packed_estimate=estimate,
+        turboquant_mse_packed_actual=actual,
+        post_cache_setup_gpu_memory=post_setup,
+        gpu_peak_memory=gpu_peak_memory_bytes(),
+        reconstruction_quality=recon,
+    )
+    return GenerationOutput(text=text, metrics=metrics, completion_ids=completion)

@@ -1,0 +1,454 @@
+"""Packed TurboQuant cache layer backed by the sm_100a kernels.
+
+Host-side mirror of the reference's ``src/turboquant/runtime/packed_qmse_cache.py``:
+the same class / function names, constructor arguments, attributes and error behaviour,
+so code written against the reference (its attention backend, its generation loop, its
+telemetry) works unchanged — but every tensor operation of the hot path is one call into
+``libtq_b200.so``:
+
+===========================================  ==========================================
+reference                                    here
+===========================================  ==========================================
+``_encode_group`` / ``_encode_keys_qjl_group``  ``tq_pack`` (rotate, quantise, bit-pack, QJL)
+``PackedTensorMSE.append`` (``torch.cat``)      in-place write at the current length
+``_decode_group`` / ``triton_decode_group``     ``tq_dequant``
+``fused_attention`` / chunked fallback          ``tq_decode_attn`` (:meth:`PackedMSELayer.attend`)
+===========================================  ==========================================
+
+Outlier-channel splitting (``num_outlier_channels > 0``) is not part of this library.
+"""
+
+from __future__ import annotations
+
+import sys
+from dataclasses import dataclass
+from math import sqrt
+from typing import Any
+
+import torch
+from transformers.cache_utils import Cache, CacheLayerMixin
+
+from tq_local_b200.runtime.codec import Codec
+from tq_local_b200.runtime.packed_store import PackedStore, key_norm_mean
+from tq_local_b200.runtime.sharding import HeadShard
+
+
+@dataclass
+class PackedTensorMSE:
+    """View of the stored tokens of one packed stream pair (reference: packed_qmse_cache.py:58-92)."""
+
+    packed_indices: torch.Tensor  # uint8 [B, H, N, 16*bits]
+    norms: torch.Tensor           # fp16  [B, H, N]
+    original_shape: tuple[int, int, int, int]
+    original_dtype: torch.dtype
+    bits: int
+
+    @property
+    def num_vectors(self) -> int:
+        b, h, n, _ = self.original_shape
+        return int(b * h * n)
+
+    @property
+    def dimension(self) -> int:
+        return int(self.original_shape[-1])
+
+    def storage_bytes(self) -> int:
+        return int(self.packed_indices.numel() * self.packed_indices.element_size()
+                   + self.norms.numel() * self.norms.element_size())
+
+
+@dataclass
+class PackedQJL:
+    """View of the 1-bit QJL sign sketch and residual norms (packed_qmse_cache.py:121-140)."""
+
+    packed_signs: torch.Tensor    # uint8 [B, H, N, 16]
+    residual_norms: torch.Tensor  # fp16  [B, H, N]
+    dimension: int
+
+    def storage_bytes(self) -> int:
+        return int(self.packed_signs.numel() * self.packed_signs.element_size()
+                   + self.residual_norms.numel() * self.residual_norms.element_size())
+
+
+class _GrowingDense:
+    """Dense [B, H, T, D] buffer with spare capacity: amortised O(1) append along T."""
+
+    def __init__(self) -> None:
+        self.buf: torch.Tensor | None = None
+        self.length = 0
+
+    def append(self, x: torch.Tensor, reserve: int = 0) -> torch.Tensor:
+        n = int(x.shape[2])
+        if self.buf is None:
+            cap = max(self.length + n + reserve, 16)
+            self.buf = torch.empty(x.shape[0], x.shape[1], cap, x.shape[3], dtype=x.dtype, device=x.device)
+        elif self.length + n > self.buf.shape[2]:
+            cap = max(2 * self.buf.shape[2], self.length + n + reserve)
+            grown = torch.empty(*self.buf.shape[:2], cap, self.buf.shape[3], dtype=self.buf.dtype,
+                                device=self.buf.device)
+            grown[:, :, :self.length] = self.buf[:, :, :self.length]
+            self.buf = grown
+        self.buf[:, :, self.length:self.length + n] = x
+        self.length += n
+        return self.view()
+
+    def view(self) -> torch.Tensor | None:
+        return None if self.buf is None else self.buf[:, :, :self.length]
+
+
+class PackedMSELayer(CacheLayerMixin):
+    """One layer of the packed cache (reference: packed_qmse_cache.py:163-885)."""
+
+    is_sliding = False
+
+    def __init__(
+        self,
+        bits: int,
+        seed: int = 0,
+        grid_size: int = 32769,
+        num_outlier_channels: int = 0,
+        outlier_extra_bits: int = 1,
+        use_qjl_keys: bool = False,
+        quantize_decode: bool = False,
+        reserve_tokens: int = 0,
+        shard: HeadShard | None = None,
+    ):
+        super().__init__()
+        if num_outlier_channels:
+            raise NotImplementedError("outlier-channel splitting is not provided by the B200 kernels")
+        self.is_initialized = False
+        self.bits = bits
+        self.seed = seed
+        self.grid_size = grid_size
+        self.num_outlier_channels = num_outlier_channels
+        self.outlier_extra_bits = outlier_extra_bits
+        self.use_qjl_keys = use_qjl_keys
+        self.quantize_decode = quantize_decode
+        self.reserve_tokens = int(reserve_tokens)
+        self.shard = shard or HeadShard()
+
+        self.device: torch.device | None = None
+        self.dtype: torch.dtype | None = None
+        self.codec: Codec | None = None
+        self.store: PackedStore | None = None
+        self._force_dense = False
+        self._lazy_update = False
+        self._dense_k = _GrowingDense()
+        self._dense_v = _GrowingDense()
+        self._kv_heads_total: int | None = None
+
+    # ---------------------------------------------------------------- reference attributes
+    @property
+    def _outlier_enabled(self) -> bool:
+        return False
+
+    @property
+    def rotation(self):
+        return self.codec.table("rot_v") if self.codec else None
+
+    @property
+    def centers(self):
+        return self.codec.table("cen_v") if self.codec else None
+
+    @property
+    def boundaries(self):
+        return self.codec.table("bnd_v") if self.codec else None
+
+    @property
+    def _key_rotation(self):
+        return self.codec.table("rot_k") if self.codec and self.use_qjl_keys else None
+
+    @property
+    def _key_centers(self):
+        return self.codec.table("cen_k") if self.codec and self.use_qjl_keys else None
+
+    @property
+    def _key_boundaries(self):
+        return self.codec.table("bnd_k") if self.codec and self.use_qjl_keys else None
+
+    @property
+    def _qjl_matrix(self):
+        return self.codec.table("qjl") if self.codec and self.use_qjl_keys else None
+
+    @property
+    def _dense_keys(self):
+        return self._dense_k.view()
+
+    @property
+    def _dense_values(self):
+        return self._dense_v.view()
+
+    def _shape(self) -> tuple[int, int, int, int]:
+        s = self.store
+        return (s.batch, s.kv_heads, s.length, 128)
+
+    @property
+    def keys_packed(self) -> PackedTensorMSE | None:
+        s = self.store
+        if s is None or s.length == 0:
+            return None
+        n = s.length
+        return PackedTensorMSE(s.k_codes[:, :, :n], s.k_norms[:, :, :n], self._shape(), self.dtype, s.codec.key_bits)
+
+    @property
+    def values_packed(self) -> PackedTensorMSE | None:
+        s = self.store
+        if s is None or s.length == 0:
+            return None
+        n = s.length
+        return PackedTensorMSE(s.v_codes[:, :, :n], s.v_norms[:, :, :n], self._shape(), self.dtype, s.codec.bits)
+
+    @property
+    def _keys_qjl(self) -> PackedQJL | None:
+        s = self.store
+        if s is None or s.length == 0 or not self.use_qjl_keys:
+            return None
+        n = s.length
+        return PackedQJL(s.k_signs[:, :, :n], s.k_rnorms[:, :, :n], 128)
+
+    # ---------------------------------------------------------------- set-up
+    def lazy_initialization(self, key_states: torch.Tensor, value_states: torch.Tensor) -> None:
+        """Bind to the tensors' device and dtype and fetch the shared codec context
+        (reference: packed_qmse_cache.py:237-283)."""
+        self.dtype = key_states.dtype
+        self.device = key_states.device
+        self.codec = Codec.get(self.device, self.bits, self.use_qjl_keys, self.seed, self.grid_size,
+                               int(key_states.shape[-1]))
+        self.is_initialized = True
+
+    def _ensure_store(self, key_states: torch.Tensor) -> None:
+        if self.store is None:
+            local = self.shard.local_kv(key_states)
+            cap = int(key_states.shape[2]) + self.reserve_tokens
+            self.store = PackedStore(self.codec, int(local.shape[0]), int(local.shape[1]), cap)
+            self._kv_heads_total = int(key_states.shape[1])
+
+    def initialize_from_dense(self, key_states: torch.Tensor, value_states: torch.Tensor, *,
+                              force_dense: bool = False) -> None:
+        """Pack a dense prefill cache (reference: packed_qmse_cache.py:332-374)."""
+        if force_dense:
+            self.device, self.dtype = key_states.device, key_states.dtype
+            self._dense_k.append(key_states, self.reserve_tokens)
+            self._dense_v.append(value_states, self.reserve_tokens)
+            self._force_dense = True
+            self.is_initialized = True
+            return
+        if not self.is_initialized:
+            self.lazy_initialization(key_states, value_states)
+        self._ensure_store(key_states)
+        self.store.pack(self.shard.local_kv(key_states), self.shard.local_kv(value_states))
+
+    # ---------------------------------------------------------------- decode-time update
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor,
+               cache_kwargs: dict[str, Any] | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """HF cache hook (reference: packed_qmse_cache.py:600-624)."""
+        if not self.is_initialized:
+            self.lazy_initialization(key_states, value_states)
+        if self._force_dense:
+            return self._update_dense_decode(key_states, value_states)
+        if self._lazy_update:
+            return self._update_lazy(key_states, value_states)
+        if not self.quantize_decode:
+            return self._update_dense_decode(key_states, value_states)
+        # Eager path: hand back the dequantised history plus the new token, then store it.
+        prev_k, prev_v = self._decode_keys_full(), self._decode_values_full()
+        self._ensure_store(key_states)
+        self.store.pack(self.shard.local_kv(key_states), self.shard.local_kv(value_states))
+        if prev_k is None:
+            return key_states, value_states
+        return (torch.cat((prev_k, self.shard.local_kv(key_states)), dim=-2),
+                torch.cat((prev_v, self.shard.local_kv(value_states)), dim=-2))
+
+    def _update_lazy(self, key_states, value_states):
+        """Store the new token without touching history (reference: packed_qmse_cache.py:626-679):
+        quantised in place when ``quantize_decode``, otherwise appended to the dense tail."""
+        if self.quantize_decode:
+            self._ensure_store(key_states)
+            self.store.pack(self.shard.local_kv(key_states), self.shard.local_kv(value_states))
+        else:
+            self._dense_k.append(self.shard.local_kv(key_states), self.reserve_tokens)
+            self._dense_v.append(self.shard.local_kv(value_states), self.reserve_tokens)
+        return key_states, value_states
+
+    def _update_dense_decode(self, key_states, value_states):
+        """Keep generated tokens dense and return the full K/V (packed_qmse_cache.py:681-705)."""
+        if not self._force_dense:
+            key_states, value_states = self.shard.local_kv(key_states), self.shard.local_kv(value_states)
+        dk = self._dense_k.append(key_states, self.reserve_tokens)
+        dv = self._dense_v.append(value_states, self.reserve_tokens)
+        pk, pv = self._decode_keys_full(), self._decode_values_full()
+        if pk is None:
+            return dk, dv
+        return torch.cat((pk, dk), dim=-2), torch.cat((pv, dv), dim=-2)
+
+    # ---------------------------------------------------------------- attention
+    def attend(self, query_states: torch.Tensor) -> torch.Tensor:
+        """Decode attention of ``query_states`` [B, Hq, Sq, D] over this layer's cache, returning
+        [B, Hq, Sq, D] in the query dtype.  ``Sq > 1`` is served one query position at a
+        time with causal visibility (the new tokens were appended before attention)."""
+        if self.store is None or self._force_dense:
+            raise RuntimeError("attend() needs a packed (non-dense) layer")
+        b, hq, sq, d = query_states.shape
+        q_local = self.shard.local_q(query_states, self._kv_heads_total)
+        tail_k, tail_v = self._dense_k.view(), self._dense_v.view()
+        n_tail = 0 if tail_k is None else int(tail_k.shape[2])
+        outs = []
+        for i in range(sq):
+            behind = sq - 1 - i  # tokens of this very call that position i must not see
+            if self.quantize_decode or n_tail == 0:
+                out = self.store.decode_attn(q_local[:, :, i:i + 1], seq_len=self.store.length - behind,
+                                             tail_k=tail_k, tail_v=tail_v)
+            else:
+                out = self.store.decode_attn(q_local[:, :, i:i + 1], tail_k=tail_k[:, :, :n_tail - behind],
+                                             tail_v=tail_v[:, :, :n_tail - behind])
+            outs.append(out)
+        out = outs[0] if sq == 1 else torch.cat(outs, dim=2)
+        return self.shard.gather_heads(out)
+
+    # ---------------------------------------------------------------- dequantisation
+    def _decode_keys_full(self) -> torch.Tensor | None:
+        if self.store is None or self.store.length == 0:
+            return None
+        return self.store.dequant("keys", dtype=self.dtype)
+
+    def _decode_values_full(self) -> torch.Tensor | None:
+        if self.store is None or self.store.length == 0:
+            return None
+        return self.store.dequant("values", dtype=self.dtype)
+
+    def _decode_keys_range(self, start: int, end: int) -> torch.Tensor:
+        return self.store.dequant("keys", start, end, dtype=self.dtype)
+
+    def _decode_values_range(self, start: int, end: int) -> torch.Tensor:
+        return self.store.dequant("values", start, end, dtype=self.dtype)
+
+    # ---------------------------------------------------------------- bookkeeping
+    def packed_seq_length(self) -> int:
+        return 0 if self.store is None else int(self.store.length)
+
+    def get_seq_length(self) -> int:
+        return self.packed_seq_length() + self._dense_k.length
+
+    def get_mask_sizes(self, cache_position) -> tuple[int, int]:
+        """(kv_length, kv_offset); newer ``transformers`` pass the query length as an int,
+        older ones a position tensor (reference: packed_qmse_cache.py:860-864)."""
+        q_len = cache_position if isinstance(cache_position, int) else int(cache_position.shape[0])
+        return self.get_seq_length() + q_len, 0
+
+    def get_max_cache_shape(self) -> int:
+        return -1
+
+    def storage_bytes(self) -> int:
+        """Bytes held for the stored tokens (reference: packed_qmse_cache.py:874-885)."""
+        total = 0 if self.store is None else self.store.storage_bytes()
+        for dense in (self._dense_k.view(), self._dense_v.view()):
+            if dense is not None:
+                total += dense.numel() * dense.element_size()
+        return int(total)
+
+
+_APPROX_DMSE_UNIT: dict[int, float] = {2: 0.079, 3: 0.030, 4: 0.009, 5: 0.003, 6: 0.0008, 7: 0.0002, 8: 0.00005}
+
+
+def _auto_norm_threshold(bits: int, head_dim: int, mse_budget: float = 1.0) -> float:
+    """Largest mean key norm a layer may have before it is kept dense:
+    ``norm^2 * D_mse(bits) / head_dim < mse_budget`` (reference: packed_qmse_cache.py:888-900)."""
+    return sqrt(mse_budget * head_dim / _APPROX_DMSE_UNIT.get(bits, 0.03))
+
+
+def _layer_kv(layer) -> tuple[torch.Tensor, torch.Tensor]:
+    if isinstance(layer, (tuple, list)):
+        return layer[0], layer[1]
+    return layer.keys, layer.values
+
+
+def build_packed_mse_cache(
+    past_key_values,
+    bits: int,
+    seed: int = 0,
+    grid_size: int = 32769,
+    num_outlier_channels: int = 0,
+    outlier_extra_bits: int = 1,
+    use_qjl_keys: bool = False,
+    quantize_decode: bool = False,
+    norm_guard: bool = True,
+    reserve_tokens: int = 0,
+    shard: HeadShard | None = None,
+    release_dense: bool = False,
+) -> Cache:
+    """Pack every layer of a dense prefill cache (reference: packed_qmse_cache.py:903-951).
+
+    A layer whose MEAN key norm exceeds ``sqrt(head_dim / D_mse(bits))`` stays dense when
+    ``norm_guard`` is on.  The per-layer means are computed on the device and fetched with a
+    single host synchronisation.  ``release_dense`` drops each dense layer from a
+    ``DynamicCache`` right after it has been packed, so peak memory is one dense layer.
+    """
+    source_layers = past_key_values.layers if hasattr(past_key_values, "layers") else list(past_key_values)
+    pairs = [_layer_kv(layer) for layer in source_layers]
+    head_dim = int(pairs[0][0].shape[-1]) if pairs else 128
+    threshold = _auto_norm_threshold(bits, head_dim) if norm_guard else float("inf")
+    if norm_guard and pairs:
+        means = torch.stack([key_norm_mean(k) for k, _ in pairs]).tolist()
+    else:
+        means = [0.0] * len(pairs)
+
+    layers: list[PackedMSELayer] = []
+    for idx, (k, v) in enumerate(pairs):
+        layer = PackedMSELayer(bits=bits, seed=seed, grid_size=grid_size, num_outlier_channels=num_outlier_channels,
+                               outlier_extra_bits=outlier_extra_bits, use_qjl_keys=use_qjl_keys,
+                               quantize_decode=quantize_decode, reserve_tokens=reserve_tokens, shard=shard)
+        layer.initialize_from_dense(k, v, force_dense=means[idx] > threshold)
+        layers.append(layer)
+        if release_dense and hasattr(source_layers[idx], "keys") and not layer._force_dense:
+            source_layers[idx].keys = source_layers[idx].values = None
+    dense_ids = [i for i, m in enumerate(means) if m > threshold]
+    if dense_ids:
+        print(f"[TurboQuant] norm_guard: {len(dense_ids)}/{len(layers)} layers kept dense "
+              f"(threshold={threshold:.1f}, layers={dense_ids})", file=sys.stderr)
+    return Cache(layers=layers)
+
+
+def verify_packed_reconstruction(original_cache, packed_cache: Cache) -> list[dict[str, Any]]:
+    """Per-layer reconstruction quality against the dense cache (reference:
+    packed_qmse_cache.py:954-1009; same keys, same rounding)."""
+    source_layers = original_cache.layers if hasattr(original_cache, "layers") else list(original_cache)
+    report: list[dict[str, Any]] = []
+    for idx, src in enumerate(source_layers):
+        k0, v0 = _layer_kv(src)
+        layer: PackedMSELayer = packed_cache.layers[idx]
+        dense = layer._force_dense
+        if dense:
+            k1, v1 = layer._dense_keys, layer._dense_values
+        else:
+            k0, v0 = layer.shard.local_kv(k0), layer.shard.local_kv(v0)
+            k1, v1 = layer._decode_keys_full(), layer._decode_values_full()
+        k0, v0, k1, v1 = k0.float(), v0.float(), k1.float(), v1.float()
+        dk, dv = k0 - k1, v0 - v1
+        cos = torch.nn.functional.cosine_similarity
+        stats = torch.stack([
+            (dk ** 2).mean(), cos(k0.reshape(-1, k0.shape[-1]), k1.reshape(-1, k1.shape[-1]), dim=-1).mean(),
+            dk.abs().max(), k0.norm(dim=-1).mean(),
+            (dv ** 2).mean(), cos(v0.reshape(-1, v0.shape[-1]), v1.reshape(-1, v1.shape[-1]), dim=-1).mean(),
+            dv.abs().max(), v0.norm(dim=-1).mean(),
+        ]).tolist()
+        report.append({
+            "layer": idx, "dense": dense,
+            "key_mse": round(stats[0], 6), "key_cosine_sim": round(stats[1], 6),
+            "key_max_abs_error": round(stats[2], 6), "key_mean_norm": round(stats[3], 4),
+            "val_mse": round(stats[4], 6), "val_cosine_sim": round(stats[5], 6),
+            "val_max_abs_error": round(stats[6], 6), "val_mean_norm": round(stats[7], 4),
+        })
+    return report
+
+
+def packed_cache_storage_bytes(cache: Cache) -> int:
+    return int(sum(layer.storage_bytes() for layer in cache.layers if hasattr(layer, "storage_bytes")))
+
+
+def packed_cache_storage_breakdown(cache: Cache) -> dict[str, int]:
+    per_layer = [int(layer.storage_bytes()) for layer in cache.layers if hasattr(layer, "storage_bytes")]
+    return {
+        "packed_total_bytes": int(sum(per_layer)),
+        "packed_layer_mean_bytes": int(sum(per_layer) / len(per_layer)) if per_layer else 0,
+        "packed_num_layers": len(per_layer),
+    }

@@ -162,6 +162,8 @@ def key_norm_mean(k: torch.Tensor) -> torch.Tensor:
     """Mean L2 norm over all vectors of ``k`` [B, H, T, 128] as a 0-dim float64 device tensor
     (no host sync); the norm-guard statistic of ``build_packed_mse_cache``
     (packed_qmse_cache.py:918-920)."""
+    if k.device.type != "cuda":
+        raise ffi.TQError("TurboQuant-B200 runs on CUDA devices only; there is no CPU path")
     acc = torch.zeros((), dtype=torch.float64, device=k.device)
     if k.stride(-1) != 1:
         k = k.contiguous()

@@ -145,6 +145,20 @@ int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32
 int32_t tq_key_norm_sum(const tq_dense_desc *k, int32_t batch, int32_t heads, int32_t n_tokens,
                         double *sum_out, tq_stream stream);
 
+/* Decode attention for callers that cannot allocate (no counterpart in the reference).
+ * Same computation and arguments as tq_decode_attn without a dense tail, but the scratch
+ * lives in an 8 MiB array built into the library instead of a caller workspace: use it from
+ * hosts that are not allowed to call an allocator while running (a server that owns all
+ * device memory through its own pool, a plug-in hook barred from allocating).  Shapes that
+ * need more than tq_static_scratch_bytes() of scratch return TQ_ERR_WORKSPACE.  The first
+ * call on a device resolves the array's address and should happen before any stream capture.
+ * All calls share the array: calls that overlap on the GPU race and must be serialised.
+ * The context's device must be current. */
+size_t tq_static_scratch_bytes(void);
+int32_t tq_decode_attn_static(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                              const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits, void *out,
+                              tq_stream stream);
+
 /* Device-side status (no reference counterpart).  Kernels never spin without a limit: a
  * wait on an asynchronous copy that runs out sets a status word instead of hanging.  This
  * call synchronises with the device and returns that word (0 = no kernel ever gave up). */

@@ -224,39 +224,15 @@ extern "C" size_t tq_decode_workspace_bytes(int32_t batch, int32_t q_heads, int3
 
 extern "C" int32_t tq_decode_suggest_splits(tq_ctx *ctx, int32_t batch, int32_t kv_heads, int32_t seq_len) {
     if (!ctx || batch <= 0 || kv_heads <= 0 || seq_len <= 0) return 1;
-    // The decode kernel runs one CTA per SM; a CTA costs its tokens plus a fixed part (table
-    // build, pipeline fill, partial write-back) worth about 256 tokens.  For every candidate
-    // tokens-per-split (a multiple of the kernel's step) replay the hardware's in-order
-    // assignment of CTAs to SMs and keep the candidate with the shortest makespan.
-    const int rows = batch * kv_heads;
+    // The decode kernel cuts the rows, laid end to end, into one equal chunk per SM; a row then
+    // spans at most ceil(row / chunk) + 1 chunks, which is the number of partial slots to provide.
     const int step = tq_mma4_tokens_per_cta_step();
-    const int64_t key = ((int64_t)rows << 32) | (uint32_t)((seq_len + step - 1) / step);
-    if (ctx->splits_cache_key == key) return ctx->splits_cache_val;
-    const int slots = ctx->sm_count;
-    const double fixed = 256.0;
-    double best = 1e300;
-    int best_splits = 1;
-    std::vector<double> free_at(slots);
-    for (int tok = step; tok < seq_len + step; tok += step) {
-        const int splits = (seq_len + tok - 1) / tok;
-        if (splits > 256 || (int64_t)rows * splits > 65536) continue;
-        std::priority_queue<double, std::vector<double>, std::greater<double>> pq;
-        for (int i = 0; i < slots; ++i) pq.push(0.0);
-        double makespan = 0.0;
-        for (int r = 0; r < rows; ++r)
-            for (int sidx = 0; sidx < splits; ++sidx) {
-                const int n = std::min(tok, seq_len - sidx * tok);
-                const double t0 = pq.top();
-                pq.pop();
-                const double t1 = t0 + fixed + n;
-                pq.push(t1);
-                if (t1 > makespan) makespan = t1;
-            }
-        if (makespan < best - 1e-9) best = makespan, best_splits = splits;
-    }
-    ctx->splits_cache_key = key;
-    ctx->splits_cache_val = best_splits;
-    return best_splits;
+    const int64_t n_pad = (seq_len + step - 1) / step * step;
+    const int64_t total = (int64_t)batch * kv_heads * n_pad;
+    const int64_t chunk = ((total + ctx->sm_count - 1) / ctx->sm_count + step - 1) / step * step;
+    int64_t splits = (n_pad + chunk - 1) / chunk + 1;
+    if (chunk >= n_pad && total % chunk == 0 && chunk % n_pad == 0) splits = 1;  // whole rows per CTA
+    return (int32_t)(splits > 1024 ? 1024 : splits);
 }
 
 extern "C" int32_t tq_device_status(tq_ctx *ctx, int32_t *status_out) {

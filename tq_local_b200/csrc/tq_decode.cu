@@ -232,8 +232,13 @@ __global__ void __launch_bounds__(TQ_D) tq_combine_kernel(CombineArgs a) {
     const int b = (int)(row / a.Hq), hq = (int)(row % a.Hq);
     const float hs = 0.08838834764831845f;
 
+    int n_valid = a.n_splits;
+    if (a.seg_chunk > 0) {
+        const int64_t lo = (row / a.G) * (int64_t)a.seg_npad;
+        n_valid = (int)((lo + a.seg_npad - 1) / a.seg_chunk - lo / a.seg_chunk) + 1;
+    }
     float M = -INFINITY;
-    for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, a.part_m[row * a.n_splits + s]);
+    for (int s = 0; s < n_valid; ++s) M = fmaxf(M, a.part_m[row * a.n_splits + s]);
 
     // dense tail logits (quantize_decode = False buffer)
     const T *tk = nullptr, *tv = nullptr;
@@ -259,7 +264,7 @@ __global__ void __launch_bounds__(TQ_D) tq_combine_kernel(CombineArgs a) {
     }
 
     float L = 0.f, o = 0.f;
-    for (int s = 0; s < a.n_splits; ++s) {
+    for (int s = 0; s < n_valid; ++s) {
         const float ms = a.part_m[row * a.n_splits + s];
         const float w = (ms == -INFINITY) ? 0.f : expf(ms - M);
         L += a.part_l[row * a.n_splits + s] * w;
@@ -360,6 +365,7 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
     CombineArgs c;
     c.part_m = w.part_m, c.part_l = w.part_l, c.part_acc = w.part_acc;
     c.n_splits = n_splits, c.Hq = q_heads, c.G = a.G;
+    c.seg_chunk = 0, c.seg_npad = 0;
     c.rot_v = ctx->rot_v;
     c.q = q, c.out = out;
     c.n_tail = n_tail;

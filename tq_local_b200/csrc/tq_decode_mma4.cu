@@ -1,10 +1,12 @@
 // Decode attention over the packed cache: tensor-core kernel for fp16 / bf16 queries
 // with at most 4 query heads per KV head (Llama-3.1-8B: 32 / 8).
 //
-// One CTA (12 warps, one per SM) owns one (batch, KV head) row and one contiguous token
-// range and serves all G <= 4 query heads, so packed bytes are read from HBM once.
+// Persistent CTAs, one per SM: the (batch, KV head) rows are laid end to end and cut into
+// equal token chunks, one per CTA, so every SM streams the same number of bytes; a CTA emits
+// one partial (max, sum, acc) per row it touches.  Each CTA serves all G <= 4 query heads of
+// a row, so packed bytes are read from HBM once.
 //
-// Data movement: every warp runs its own 3-stage ring of 32-token stages in shared
+// Data movement: every warp runs its own ring of 32-token stages in shared
 // memory.  Lane 0 fills a stage with six TMA bulk copies (cp.async.bulk: key codes, QJL
 // signs, value codes and the three fp16 norm streams are each contiguous in HBM) that
 // complete on an mbarrier; the warp waits on it with a bounded spin.  No registers and no
@@ -52,7 +54,10 @@ struct Mma4Args {
     const uint8_t *v_codes;
     const uint16_t *v_norms;
     int64_t cache_sb, cache_sh;
-    int Hkv, G, N, n_splits, tok_per_split;
+    int Hkv, G, N, n_splits;
+    int rows;    // batch * kv_heads
+    int n_pad;   // N rounded up to the CTA step: rows are laid end to end in units of n_pad tokens
+    int chunk;   // tokens of that flattened (row, token) space per CTA
     const float *qrot;
     const float *qproj;
     float *part_m, *part_l, *part_acc;
@@ -171,49 +176,25 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     }
     uint32_t *table = reinterpret_cast<uint32_t *>(smem + (kTableAddr - dyn_base));
 
-    const int split = blockIdx.x;
-    const int bh = blockIdx.y;
-    const int b = bh / a.Hkv, h = bh % a.Hkv;
     const int G = a.G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int64_t q_row0 = ((int64_t)b * a.Hkv + h) * G;
-    const int64_t row0 = (int64_t)b * a.cache_sb + (int64_t)h * a.cache_sh;
-    const int t_begin = split * a.tok_per_split;
-    const int t_end = min(a.N, t_begin + a.tok_per_split);
 
-    // ---- ring set-up and the first loads (overlap with the table build below)
+    // ---- this CTA's contiguous piece of the flattened (row, token) space
+    const int64_t flat_begin = (int64_t)blockIdx.x * a.chunk;
+    const int64_t flat_end = min(flat_begin + a.chunk, (int64_t)a.rows * a.n_pad);
+
+    // ---- ring set-up
     const uint32_t ring_u32 = warp < rings_low ? dyn_base + warp * kRingBytes
                                                : high_base + (warp - rings_low) * kRingBytes;
     const uint8_t *ring = smem + (ring_u32 - dyn_base);
     const uint32_t bar_u32 = bars_addr + warp * kStages * 8;
-    const int my_first = t_begin + warp * kStageTok;
-    const int n_iter = my_first < t_end ? (t_end - my_first + kWarps * kStageTok - 1) / (kWarps * kStageTok) : 0;
-
-    auto issue = [&](int it) {  // lane 0 only: fill stage it % kStages with iteration it
-        const int base = my_first + it * kWarps * kStageTok;
-        int n = min(kStageTok, t_end - base);
-        n = (n + 7) & ~7;  // whole 16-byte pieces of the norm streams; rows stay inside the row's stride
-        const int st = it % kStages;
-        const uint32_t dst = ring_u32 + st * L::kBytes, bar = bar_u32 + st * 8;
-        const int64_t r = row0 + base;
-        const uint32_t total = n * (16 * KB + 16 * VB + 4 + (QJL ? 18 : 0));
-        mbar_expect_tx(bar, total);
-        tma_load_1d(dst + L::kK, a.k_codes + r * (16 * KB), n * 16 * KB, bar);
-        tma_load_1d(dst + L::kV, a.v_codes + r * (16 * VB), n * 16 * VB, bar);
-        tma_load_1d(dst + L::kKN, a.k_norms + r, n * 2, bar);
-        tma_load_1d(dst + L::kVN, a.v_norms + r, n * 2, bar);
-        if (QJL) {
-            tma_load_1d(dst + L::kS, a.k_signs + r * 16, n * 16, bar);
-            tma_load_1d(dst + L::kRN, a.k_rnorms + r, n * 2, bar);
-        }
-    };
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(bar_u32 + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        for (int it = 0; it < min(n_iter, kStages); ++it) issue(it);
     }
+    uint32_t ring_pos = 0;  // stages this warp has consumed since the kernel began
 
     // ---- per-lane replicated f16x2 centre-pair tables (keys in the low half of each slot);
     // a warp fills one slot at a time, lane l writing words l and 32+l (no bank conflicts)
@@ -232,6 +213,54 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                 slot[32 + lane] = pack_half2(lo, hi);
             }
         }
+    }
+
+    __syncthreads();  // tables complete
+
+    const float kA = 0.08838834764831845f * 1.4426950408889634f;  // (1/sqrt(128)) * log2(e)
+    const float kB = kA * (1.2533141373155003f / (float)TQ_D);     // ... * sqrt(pi/2)/D
+    const uint32_t lane_k = kTableAddr + lane * 4;        // key copies: bytes [0, 128) of every slot
+    const uint32_t lane_v = kTableAddr + 128 + lane * 4;  // value copies: bytes [128, 256)
+    const bool head_live = t < G;
+    bool timed_out = false;
+
+    // ---- one segment per row this CTA touches
+    for (int64_t flat = flat_begin; flat < flat_end;) {
+    const int bh = (int)(flat / a.n_pad);
+    const int seg_lo = (int)(flat - (int64_t)bh * a.n_pad);
+    const int seg_len = (int)min((int64_t)(a.n_pad - seg_lo), flat_end - flat);
+    flat += seg_len;
+    const int split = blockIdx.x - (int)(((int64_t)bh * a.n_pad) / a.chunk);  // partial slot inside the row
+    const int b = bh / a.Hkv, h = bh % a.Hkv;
+    const int64_t q_row0 = ((int64_t)b * a.Hkv + h) * G;
+    const int64_t row0 = (int64_t)b * a.cache_sb + (int64_t)h * a.cache_sh;
+    const int t_begin = seg_lo;
+    const int t_end = min(a.N, seg_lo + seg_len);
+    const int my_first = t_begin + warp * kStageTok;
+    const int n_iter = my_first < t_end ? (t_end - my_first + kWarps * kStageTok - 1) / (kWarps * kStageTok) : 0;
+
+    auto issue = [&](int it) {  // lane 0 only: fill the ring stage of local iteration `it`
+        const int base = my_first + it * kWarps * kStageTok;
+        int n = min(kStageTok, t_end - base);
+        n = (n + 7) & ~7;  // whole 16-byte pieces of the norm streams; rows stay inside the row's stride
+        const int st = (ring_pos + it) % kStages;
+        const uint32_t dst = ring_u32 + st * L::kBytes, bar = bar_u32 + st * 8;
+        const int64_t r = row0 + base;
+        const uint32_t total = n * (16 * KB + 16 * VB + 4 + (QJL ? 18 : 0));
+        mbar_expect_tx(bar, total);
+        tma_load_1d(dst + L::kK, a.k_codes + r * (16 * KB), n * 16 * KB, bar);
+        tma_load_1d(dst + L::kV, a.v_codes + r * (16 * VB), n * 16 * VB, bar);
+        tma_load_1d(dst + L::kKN, a.k_norms + r, n * 2, bar);
+        tma_load_1d(dst + L::kVN, a.v_norms + r, n * 2, bar);
+        if (QJL) {
+            tma_load_1d(dst + L::kS, a.k_signs + r * 16, n * 16, bar);
+            tma_load_1d(dst + L::kRN, a.k_rnorms + r, n * 2, bar);
+        }
+    };
+    if (lane == 0) {
+        // the ring area was last touched through ordinary loads/stores (previous segment's merge)
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        for (int it = 0; it < min(n_iter, kStages); ++it) issue(it);
     }
 
     // ---- B fragments: column g = (head g/2, part g%2)
@@ -290,15 +319,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
             sign_bias = __shfl_sync(0xffffffffu, my_bias, (2 * t) * 4);
         }
     }
-    __syncthreads();  // tables complete
-
-    const float kA = 0.08838834764831845f * 1.4426950408889634f;  // (1/sqrt(128)) * log2(e)
-    const float kB = kA * (1.2533141373155003f / (float)TQ_D);     // ... * sqrt(pi/2)/D
-    const uint32_t lane_k = kTableAddr + lane * 4;        // key copies: bytes [0, 128) of every slot
-    const uint32_t lane_v = kTableAddr + 128 + lane * 4;  // value copies: bytes [128, 256)
-    const bool head_live = t < G;
-    bool timed_out = false;
-
     float m_run = -INFINITY, l_run = 0.f;
     float o[8][4];
 #pragma unroll
@@ -306,9 +326,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
 
     for (int it = 0; it < n_iter; ++it) {
         const int base = my_first + it * kWarps * kStageTok;
-        const int st = it % kStages;
+        const int st = (ring_pos + it) % kStages;
         const uint8_t *sp = ring + st * L::kBytes;
-        if (!mbar_wait(bar_u32 + st * 8, (it / kStages) & 1)) timed_out = true;
+        if (!mbar_wait(bar_u32 + st * 8, ((ring_pos + it) / kStages) & 1)) timed_out = true;
         const bool tail = base + kStageTok > t_end;
 
         // ------------------------------------------------------------ logits
@@ -422,10 +442,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         __syncwarp();
         if (lane == 0 && it + kStages < n_iter) issue(it + kStages);
     }
-    if (timed_out && lane == 0) atomicExch(a.error_flag, 1);
+    ring_pos += n_iter;
 
-    // ---- merge the warps of the CTA, write the split partial
-    __syncthreads();  // tables and rings are dead; reuse shared memory
+    // ---- merge the warps of the CTA and write this segment's partial.  The merge buffer
+    // reuses the first rings' memory, which is idle here: every issued stage was consumed.
+    __syncthreads();
     float *s_acc = reinterpret_cast<float *>(smem);   // [kWarps][4][128]
     float *s_m = s_acc + kWarps * 4 * TQ_D;           // [kWarps][4]
     float *s_l = s_m + kWarps * 4;
@@ -455,10 +476,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         a.part_acc[prow * TQ_D + d] = A;
         if (d == 0) a.part_m[prow] = M * 0.6931471805599453f, a.part_l[prow] = Lsum;  // natural-log units
     }
+    __syncthreads();  // the merge buffer is free again before the next segment refills the rings
+    }  // segment loop
+    if (timed_out && lane == 0) atomicExch(a.error_flag, 1);
 }
 
-// The kernel lays its rings around a table pinned at a 64 KB boundary and checks the fit
-// itself, so it is always given the largest dynamic allocation a CTA can have.
 template <int KB, int VB, bool QJL> size_t mma4_smem_bytes() { return 227 * 1024; }
 
 template <int KB, int VB, bool QJL> cudaError_t launch_mma4(const Mma4Args &a, dim3 grid, cudaStream_t stream) {
@@ -493,14 +515,26 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     a.v_codes = cache->v_codes, a.v_norms = cache->v_norms;
     a.cache_sb = cache->stride_b, a.cache_sh = cache->stride_h;
     a.Hkv = cache->kv_heads, a.G = q_heads / cache->kv_heads, a.N = seq_len, a.n_splits = n_splits;
-    const int per_iter = kWarps * kStageTok;
-    a.tok_per_split = ((seq_len + n_splits - 1) / n_splits + per_iter - 1) / per_iter * per_iter;
-    if (a.tok_per_split < per_iter) a.tok_per_split = per_iter;
+    // Rows are laid end to end (each padded to the CTA step) and cut into equal chunks, one per
+    // CTA, at most one CTA per SM; a row then has at most ceil(n_pad / chunk) + 1 partials,
+    // which must fit the n_splits slots the caller's workspace provides.
+    const int step = kWarps * kStageTok;
+    a.rows = cache->batch * cache->kv_heads;
+    a.n_pad = (seq_len + step - 1) / step * step;
+    const int64_t total = (int64_t)a.rows * a.n_pad;
+    int64_t chunk = ((total + ctx->sm_count - 1) / ctx->sm_count + step - 1) / step * step;
+    if (n_splits == 1) {
+        chunk = a.n_pad;
+    } else {
+        const int64_t floor_chunk = ((a.n_pad + n_splits - 2) / (n_splits - 1) + step - 1) / step * step;
+        if (chunk < floor_chunk) chunk = floor_chunk;
+    }
+    a.chunk = (int)chunk;
     a.qrot = w.qrot, a.qproj = w.qproj;
     a.part_m = w.part_m, a.part_l = w.part_l, a.part_acc = w.part_acc;
     a.centers_k = ctx->centers_k, a.centers_v = ctx->centers_v;
     a.error_flag = ctx->error_flag;
-    dim3 grid(n_splits, cache->batch * cache->kv_heads);
+    dim3 grid((unsigned)((total + chunk - 1) / chunk));
     const int mode = ctx->use_qjl * 10 + ctx->bits;
     tq_prof_count(ctx, 3);
     tq_prof_begin(ctx, stream);
@@ -520,6 +554,7 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     CombineArgs c;
     c.part_m = w.part_m, c.part_l = w.part_l, c.part_acc = w.part_acc;
     c.n_splits = n_splits, c.Hq = q_heads, c.G = a.G;
+    c.seg_chunk = a.chunk, c.seg_npad = a.n_pad;
     c.rot_v = ctx->rot_v;
     c.q = q, c.out = out;
     c.n_tail = n_tail;

@@ -6,6 +6,9 @@
 struct CombineArgs {
     const float *part_m, *part_l, *part_acc;
     int n_splits, Hq, G;
+    // When seg_chunk > 0 the partials of KV row r are those of the CTAs whose chunk of the
+    // flattened (row * seg_npad + token) space overlaps the row; otherwise all n_splits are valid.
+    int seg_chunk, seg_npad;
     const float *rot_v;  // R_v[d][e]
     const void *q;       // original-dtype query, for the dense tail
     void *out;

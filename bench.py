@@ -204,6 +204,8 @@ def run_gpu_arm(args) -> None:
     w = dict(WORKLOAD)
     if args.batch_per_gpu:
         w["batch_per_gpu"] = args.batch_per_gpu
+    if args.context:
+        w["context"] = args.context
     if w["kv_heads"] % world:
         raise SystemExit(f"{w['kv_heads']} KV heads do not shard over {world} ranks")
     dtype = getattr(torch, w["dtype"])
@@ -353,6 +355,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch-per-gpu", type=int, default=None,
                     help="override the workload's batch (profiling captures use a smaller one)")
+    ap.add_argument("--context", type=int, default=None, help="override the context length (profiling captures)")
     ap.add_argument("--splits", type=int, default=None, help="override the library's split choice")
     ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling captures)")
     args = ap.parse_args()

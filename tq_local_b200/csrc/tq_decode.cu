@@ -283,8 +283,178 @@ __global__ void __launch_bounds__(TQ_D) tq_combine_kernel(CombineArgs a) {
     ((T *)a.out)[row * TQ_D + e] = tq_from_float<T>(out / fmaxf(L, 1e-8f));
 }
 
+// Query preparation for the G <= 4 tensor-core kernel: one block per (batch, KV head) row
+// rotates and projects all G query heads (each matrix element is read once for the G heads)
+// and emits, per head, the ready-made MMA B-fragment words of all eight (part, t) lane
+// variants: 16 words of the rotated query split in two f16 terms, 8 words of the projected
+// query as 16-bit fixed point in two s8 terms, the fixed-point scale and bias (26 words).
+// Row stride of the fragment area: TQ_FRAG_ROW_WORDS words per query head.
+template <typename T>
+__global__ void __launch_bounds__(4 * TQ_D) tq_qprep_frag_kernel(const T *q, const float *rot_k_t, const float *qjl_t,
+                                                                uint32_t *frag, int G, int use_qjl) {
+    __shared__ float s_q[4][TQ_D], s_r[4][TQ_D], s_p[4][TQ_D];
+    __shared__ float s_part[4][2][4][TQ_D];  // [quarter of d][rot / proj][head][column]
+    __shared__ int s_x[4][TQ_D];
+    __shared__ float s_scale[4], s_bias[4];
+    const int64_t R = blockIdx.x;
+    const int tid = threadIdx.x, j = tid & (TQ_D - 1), dq = tid >> 7;
+    const int warp = tid >> 5, lane = tid & 31;
+    if (dq < G) s_q[dq][j] = tq_to_float<T>(q[(R * G + dq) * TQ_D + j]);
+    __syncthreads();
+    {   // thread (j, dq) covers rows d in [32 dq, 32 dq + 32) of both matrices for all heads
+        float r[4] = {0.f, 0.f, 0.f, 0.f}, p[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+            const int d = 32 * dq + i;
+            const float rk = __ldg(rot_k_t + d * TQ_D + j);
+            const float sk = use_qjl ? __ldg(qjl_t + d * TQ_D + j) : 0.f;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const float qv = g < G ? s_q[g][d] : 0.f;
+                r[g] = fmaf(qv, rk, r[g]);
+                p[g] = fmaf(qv, sk, p[g]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) s_part[dq][0][g][j] = r[g], s_part[dq][1][g][j] = p[g];
+    }
+    __syncthreads();
+    {   // thread (j, dq) finishes head dq
+        const int g = dq;
+        s_r[g][j] = (s_part[0][0][g][j] + s_part[1][0][g][j]) + (s_part[2][0][g][j] + s_part[3][0][g][j]);
+        s_p[g][j] = (s_part[0][1][g][j] + s_part[1][1][g][j]) + (s_part[2][1][g][j] + s_part[3][1][g][j]);
+    }
+    __syncthreads();
+    if (warp < G) {  // warp w quantises the projected query of head w to 16-bit fixed point
+        float amax = 0.f;
+        for (int i = lane; i < TQ_D; i += 32) amax = fmaxf(amax, fabsf(s_p[warp][i]));
+        amax = tq_warp_max(amax);
+        const float inv = amax > 0.f ? 32000.0f / amax : 0.f;
+        int isum = 0;
+        for (int i = lane; i < TQ_D; i += 32) {
+            const int x = __float2int_rn(s_p[warp][i] * inv);
+            s_x[warp][i] = x;
+            isum += x;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
+        if (lane == 0) {
+            // <qp, sign> = scale * (2 * sum_{bit set} x - sum x); the MMA yields -(sum over set bits)
+            const float scale = amax > 0.f ? amax / 32000.0f : 0.f;
+            s_scale[warp] = -2.0f * scale;
+            s_bias[warp] = -scale * (float)isum;
+        }
+    }
+    __syncthreads();
+    if (tid < G * 8) {
+        const int hcol = tid >> 3, part = (tid >> 2) & 1, t = tid & 3;
+        uint32_t *out = frag + (R * G + hcol) * TQ_FRAG_ROW_WORDS + (part * 4 + t) * 26;
+        for (int s8 = 0; s8 < 8; ++s8) {
+            float x[4];
+            for (int i = 0; i < 4; ++i) {
+                const float v = s_r[hcol][32 * t + 4 * s8 + i];
+                const float hi = __half2float(__float2half_rn(v));
+                x[i] = part ? (v - hi) : hi;
+            }
+            const __half2 a = __floats2half2_rn(x[0], x[1]), b = __floats2half2_rn(x[2], x[3]);
+            out[2 * s8] = *reinterpret_cast<const uint32_t *>(&a);
+            out[2 * s8 + 1] = *reinterpret_cast<const uint32_t *>(&b);
+        }
+        for (int n = 0; n < 4; ++n)
+            for (int rr = 0; rr < 2; ++rr) {
+                uint32_t word = 0;
+                for (int k = 0; k < 4; ++k) {
+                    const int x16 = use_qjl ? s_x[hcol][32 * t + (7 - 2 * n - rr) + 8 * k] : 0;
+                    const int hi8 = (x16 + 128) >> 8;
+                    const int lo8 = x16 - (hi8 << 8);
+                    word |= (uint32_t)((part ? lo8 : hi8) & 0xff) << (8 * k);
+                }
+                out[16 + 2 * n + rr] = word;
+            }
+        out[24] = __float_as_uint(use_qjl ? s_scale[hcol] : 0.f);
+        out[25] = __float_as_uint(use_qjl ? s_bias[hcol] : 0.f);
+    }
+}
+
+// Split combine for all G <= 4 heads of one (batch, KV head) row per block (no dense tail):
+// the un-rotation matrix is read once for the G heads.
+template <typename T>
+__global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs a) {
+    __shared__ float s_o[4][TQ_D];
+    __shared__ float s_part[4][4][TQ_D];  // [quarter of d][head][column]
+    __shared__ float s_L[4];
+    const int64_t R = blockIdx.x;
+    const int tid = threadIdx.x, e = tid & (TQ_D - 1), dq = tid >> 7;
+    int n_valid = a.n_splits;
+    if (a.seg_chunk > 0) {
+        const int64_t lo = R * (int64_t)a.seg_npad;
+        n_valid = (int)((lo + a.seg_npad - 1) / a.seg_chunk - lo / a.seg_chunk) + 1;
+    }
+    {   // thread (e, dq) merges the splits of head dq
+        const int g = dq;
+        float o = 0.f, L = 0.f;
+        if (g < a.G) {
+            const int64_t row = R * a.G + g;
+            float M = -INFINITY;
+            for (int s = 0; s < n_valid; ++s) M = fmaxf(M, a.part_m[row * a.n_splits + s]);
+            for (int s = 0; s < n_valid; ++s) {
+                const float ms = a.part_m[row * a.n_splits + s];
+                const float w = (ms == -INFINITY) ? 0.f : expf(ms - M);
+                L += a.part_l[row * a.n_splits + s] * w;
+                o += a.part_acc[(row * a.n_splits + s) * TQ_D + e] * w;
+            }
+        }
+        s_o[g][e] = o;
+        if (e == 0) s_L[g] = L;
+    }
+    __syncthreads();
+    {   // thread (e, dq) un-rotates rows d in [32 dq, 32 dq + 32) for all heads
+        float out[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+            const int d = 32 * dq + i;
+            const float rv = __ldg(a.rot_v + d * TQ_D + e);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) out[g] = fmaf(s_o[g][d], rv, out[g]);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) s_part[dq][g][e] = out[g];
+    }
+    __syncthreads();
+    if (dq < a.G) {
+        const int g = dq;
+        const float v = (s_part[0][g][e] + s_part[1][g][e]) + (s_part[2][g][e] + s_part[3][g][e]);
+        ((T *)a.out)[(R * a.G + g) * TQ_D + e] = tq_from_float<T>(v / fmaxf(s_L[g], 1e-8f));
+    }
+}
+
+// The decode kernels run with the largest shared-memory carve-out.  The small kernels around
+// them ask for the same carve-out, so the SMs are not reconfigured (and drained) between the
+// launches of one decode step.
+template <typename K> static void prefer_max_shared(K kernel) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+static void configure_small_kernels() {
+    static bool done = false;
+    if (done) return;
+    done = true;
+    prefer_max_shared(tq_qprep_kernel<float>);
+    prefer_max_shared(tq_qprep_kernel<__half>);
+    prefer_max_shared(tq_qprep_kernel<__nv_bfloat16>);
+    prefer_max_shared(tq_combine_kernel<float>);
+    prefer_max_shared(tq_combine_kernel<__half>);
+    prefer_max_shared(tq_combine_kernel<__nv_bfloat16>);
+    prefer_max_shared(tq_qprep_frag_kernel<float>);
+    prefer_max_shared(tq_qprep_frag_kernel<__half>);
+    prefer_max_shared(tq_qprep_frag_kernel<__nv_bfloat16>);
+    prefer_max_shared(tq_combine_group_kernel<float>);
+    prefer_max_shared(tq_combine_group_kernel<__half>);
+    prefer_max_shared(tq_combine_group_kernel<__nv_bfloat16>);
+}
+
 int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
                         cudaStream_t stream) {
+    configure_small_kernels();
     if (q_dtype == TQ_DTYPE_F32)
         tq_qprep_kernel<float><<<(unsigned)rows, TQ_D, 0, stream>>>((const float *)q, ctx->rot_k_t, ctx->qjl_t, qrot,
                                                                     qproj, ctx->use_qjl);
@@ -298,7 +468,35 @@ int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t row
     return TQ_OK;
 }
 
+int32_t tq_launch_qprep_frag(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t kv_rows, int G, uint32_t *frag,
+                             cudaStream_t stream) {
+    configure_small_kernels();
+    if (G > 4) return TQ_ERR_UNSUPPORTED;
+    if (q_dtype == TQ_DTYPE_F32)
+        tq_qprep_frag_kernel<float><<<(unsigned)kv_rows, 4 * TQ_D, 0, stream>>>((const float *)q, ctx->rot_k_t, ctx->qjl_t,
+                                                                            frag, G, ctx->use_qjl);
+    else if (q_dtype == TQ_DTYPE_F16)
+        tq_qprep_frag_kernel<__half><<<(unsigned)kv_rows, 4 * TQ_D, 0, stream>>>((const __half *)q, ctx->rot_k_t,
+                                                                             ctx->qjl_t, frag, G, ctx->use_qjl);
+    else
+        tq_qprep_frag_kernel<__nv_bfloat16><<<(unsigned)kv_rows, 4 * TQ_D, 0, stream>>>(
+            (const __nv_bfloat16 *)q, ctx->rot_k_t, ctx->qjl_t, frag, G, ctx->use_qjl);
+    TQ_CUDA_CHECK(cudaGetLastError());
+    return TQ_OK;
+}
+
 int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, cudaStream_t stream) {
+    if (a.n_tail == 0 && a.G <= 4) {  // grouped variant: one block per KV row
+        const unsigned kv_rows = (unsigned)(rows / a.G);
+        if (q_dtype == TQ_DTYPE_F32)
+            tq_combine_group_kernel<float><<<kv_rows, 4 * TQ_D, 0, stream>>>(a);
+        else if (q_dtype == TQ_DTYPE_F16)
+            tq_combine_group_kernel<__half><<<kv_rows, 4 * TQ_D, 0, stream>>>(a);
+        else
+            tq_combine_group_kernel<__nv_bfloat16><<<kv_rows, 4 * TQ_D, 0, stream>>>(a);
+        TQ_CUDA_CHECK(cudaGetLastError());
+        return TQ_OK;
+    }
     const size_t dyn = (size_t)a.n_tail * sizeof(float);
     if (dyn > 40 * 1024) return TQ_ERR_UNSUPPORTED;
     if (q_dtype == TQ_DTYPE_F32)

@@ -58,8 +58,7 @@ struct Mma4Args {
     int rows;    // batch * kv_heads
     int n_pad;   // N rounded up to the CTA step: rows are laid end to end in units of n_pad tokens
     int chunk;   // tokens of that flattened (row, token) space per CTA
-    const float *qrot;
-    const float *qproj;
+    const uint32_t *frag;  // per query head: TQ_FRAG_ROW_WORDS words, see tq_qprep_frag_kernel
     float *part_m, *part_l, *part_acc;
     const float *centers_k, *centers_v;
     int *error_flag;  // set to 1 when a bounded wait ran out
@@ -120,23 +119,17 @@ __device__ __forceinline__ uint32_t lds_abs(uint32_t addr) {
     return v;
 }
 
-// Shared-memory address of this lane's copy of the table slot selected by the WIDTH-bit
-// field at bit `off` of the little-endian word array `w`.  `lane_bits` = kTableAddr + the
-// lane's offset inside a slot (< 256).  `off` is a compile-time constant after unrolling.
-// A byte-aligned 8-bit field takes one byte permute (field -> byte 1, the rest from
-// lane_bits); any other field takes a shift and one three-input logic op (or a funnel shift
-// first when it straddles two words; w[off/32+1] must exist).
-template <int WIDTH> __device__ __forceinline__ uint32_t slot_offset(const uint32_t *w, int off, uint32_t lane_bits) {
-    const int wi = off >> 5, s = off & 31;
-    if (WIDTH == 8 && (s & 7) == 0) return prmt(w[wi], lane_bits, 0x7604u | ((uint32_t)(s >> 3) << 4));
-    constexpr uint32_t kMask = ((1u << WIDTH) - 1u) << 8;
-    uint32_t x;
-    if (s + WIDTH <= 32) {
-        x = s >= 8 ? (w[wi] >> (s - 8)) : (w[wi] << (8 - s));
-    } else {
-        x = __funnelshift_r(w[wi], w[wi + 1], s) << 8;
-    }
-    return (x & kMask) | lane_bits;
+// Shared-memory address of this lane's copy of the table slot selected by the BYTE that
+// starts at bit `off` of the little-endian word array `w` (w[off/32+1] must exist).  Every
+// table has 256 slots and ignores the bits of the byte beyond the field it encodes, so a
+// field never needs masking.  `lane_bits` = kTableAddr + the lane's offset inside a slot.
+// `off` is a compile-time constant after unrolling: a byte-aligned field costs one byte
+// permute; otherwise the word is first funnel-shifted by off % 8 (the shifted copies are
+// shared by all fields with the same word and remainder).
+__device__ __forceinline__ uint32_t slot_addr(const uint32_t *w, int off, uint32_t lane_bits) {
+    const int wi = off >> 5, sh = off & 7, byte = (off & 31) >> 3;
+    const uint32_t x = sh == 0 ? w[wi] : __funnelshift_r(w[wi], w[wi + 1], sh);
+    return prmt(x, lane_bits, 0x7604u | ((uint32_t)byte << 4));
 }
 
 // The 16*VB-bit value chunk of lane group g of one staged token row (row = VB*16 bytes).
@@ -155,8 +148,7 @@ template <int KB, int VB, bool QJL>
 __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args a) {
     using L = StageLayout<KB, VB, QJL>;
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int kKEntries = 1 << (2 * KB), kVEntries = 1 << (2 * VB);
-    constexpr int kEntries = kKEntries > kVEntries ? kKEntries : kVEntries;
+    constexpr int kEntries = 256;  // indexed by a whole byte; bits beyond the field are ignored
     constexpr int kTableBytes = kEntries * kSlotWords * 4;
     static_assert(kTableBytes <= 65536, "table must fit between two 64 KB boundaries");
     // Shared-memory map (absolute shared addresses): [dynamic base, 65536) the first rings,
@@ -200,18 +192,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     // a warp fills one slot at a time, lane l writing words l and 32+l (no bank conflicts)
     {
         const float ck = a.centers_k[lane & 15], cv = a.centers_v[lane & 15];
+        constexpr int mk = (1 << KB) - 1, mv = (1 << VB) - 1;
         for (int e = warp; e < kEntries; e += kWarps) {
             uint32_t *slot = table + e * kSlotWords;
-            if (e < kKEntries) {
-                const float lo = __shfl_sync(0xffffffffu, ck, e & ((1 << KB) - 1));
-                const float hi = __shfl_sync(0xffffffffu, ck, e >> KB);
-                slot[lane] = pack_half2(lo, hi);
-            }
-            if (e < kVEntries) {
-                const float lo = __shfl_sync(0xffffffffu, cv, e & ((1 << VB) - 1));
-                const float hi = __shfl_sync(0xffffffffu, cv, e >> VB);
-                slot[32 + lane] = pack_half2(lo, hi);
-            }
+            const float klo = __shfl_sync(0xffffffffu, ck, e & mk), khi = __shfl_sync(0xffffffffu, ck, (e >> KB) & mk);
+            const float vlo = __shfl_sync(0xffffffffu, cv, e & mv), vhi = __shfl_sync(0xffffffffu, cv, (e >> VB) & mv);
+            slot[lane] = pack_half2(klo, khi);
+            slot[32 + lane] = pack_half2(vlo, vhi);
         }
     }
 
@@ -221,7 +208,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     const float kB = kA * (1.2533141373155003f / (float)TQ_D);     // ... * sqrt(pi/2)/D
     const uint32_t lane_k = kTableAddr + lane * 4;        // key copies: bytes [0, 128) of every slot
     const uint32_t lane_v = kTableAddr + 128 + lane * 4;  // value copies: bytes [128, 256)
-    const bool head_live = t < G;
     bool timed_out = false;
 
     // ---- one segment per row this CTA touches
@@ -270,53 +256,22 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     uint32_t bp[QJL ? 4 : 1][2];
     float sign_scale = 0.f, sign_bias = 0.f;  // for the head this lane owns in the softmax (head t)
     {
-        const float *qr = a.qrot + (q_row0 + (live ? hcol : 0)) * TQ_D + 32 * t;
+        const uint2 *fr = reinterpret_cast<const uint2 *>(a.frag + (q_row0 + (live ? hcol : 0)) * TQ_FRAG_ROW_WORDS +
+                                                          (part * 4 + t) * 26);
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-            const float4 v = *reinterpret_cast<const float4 *>(qr + 4 * s);
-            float x[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float hi = __half2float(__float2half_rn(x[i]));
-                x[i] = part ? (x[i] - hi) : hi;
-            }
-            bq[s][0] = live ? pack_half2(x[0], x[1]) : 0u;
-            bq[s][1] = live ? pack_half2(x[2], x[3]) : 0u;
+            const uint2 v = __ldg(fr + s);
+            bq[s][0] = live ? v.x : 0u, bq[s][1] = live ? v.y : 0u;
         }
         if (QJL) {
-            const float *qp = a.qproj + (q_row0 + (live ? hcol : 0)) * TQ_D + 32 * t;
-            float amax = 0.f;
-#pragma unroll
-            for (int d = 0; d < 32; ++d) amax = fmaxf(amax, fabsf(qp[d]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            const float inv = amax > 0.f ? 32000.0f / amax : 0.f;
-            int isum = 0;
 #pragma unroll
             for (int n = 0; n < 4; ++n) {
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    uint32_t word = 0;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int d = (7 - 2 * n - r) + 8 * j;  // bit of the sign word behind k-slot j
-                        const int x16 = __float2int_rn(qp[d] * inv);
-                        const int hi8 = (x16 + 128) >> 8;
-                        const int lo8 = x16 - (hi8 << 8);
-                        isum += x16;
-                        word |= (uint32_t)((part ? lo8 : hi8) & 0xff) << (8 * j);
-                    }
-                    bp[n][r] = live ? word : 0u;
-                }
+                const uint2 v = __ldg(fr + 8 + n);
+                bp[n][0] = live ? v.x : 0u, bp[n][1] = live ? v.y : 0u;
             }
-            isum += __shfl_xor_sync(0xffffffffu, isum, 1);
-            isum += __shfl_xor_sync(0xffffffffu, isum, 2);
-            // <qp, sign> = scale * (2 * sum_{bit set} x16 - sum x16), and the MMA returns
-            // D = -(256 * hi + lo) summed over the set bits
-            const float scale = amax > 0.f ? amax / 32000.0f : 0.f;
-            const float my_scale = -2.0f * scale, my_bias = -scale * (float)isum;
-            sign_scale = __shfl_sync(0xffffffffu, my_scale, (2 * t) * 4);
-            sign_bias = __shfl_sync(0xffffffffu, my_bias, (2 * t) * 4);
+            const uint32_t *mine = a.frag + (q_row0 + (t < G ? t : 0)) * TQ_FRAG_ROW_WORDS;
+            sign_scale = __uint_as_float(__ldg(mine + 24));
+            sign_bias = __uint_as_float(__ldg(mine + 25));
         }
     }
     float m_run = -INFINITY, l_run = 0.f;
@@ -351,10 +306,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
             for (int s = 0; s < 8; ++s) {
                 constexpr int W = 2 * KB;
                 const int o0 = (2 * s) * W, o1 = (2 * s + 1) * W;
-                const uint32_t a0 = lds_abs(slot_offset<W>(wa, o0, lane_k));
-                const uint32_t a1 = lds_abs(slot_offset<W>(wb, o0, lane_k));
-                const uint32_t a2 = lds_abs(slot_offset<W>(wa, o1, lane_k));
-                const uint32_t a3 = lds_abs(slot_offset<W>(wb, o1, lane_k));
+                const uint32_t a0 = lds_abs(slot_addr(wa, o0, lane_k));
+                const uint32_t a1 = lds_abs(slot_addr(wb, o0, lane_k));
+                const uint32_t a2 = lds_abs(slot_addr(wa, o1, lane_k));
+                const uint32_t a3 = lds_abs(slot_addr(wb, o1, lane_k));
                 mma_f16(d1, a0, a1, a2, a3, bq[s][0], bq[s][1]);
             }
             const uint16_t *kn = reinterpret_cast<const uint16_t *>(sp + L::kKN);
@@ -382,8 +337,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                 if (base + slotA >= t_end) lgA = -INFINITY;
                 if (base + slotB >= t_end) lgB = -INFINITY;
             }
-            lg[i][0] = head_live ? lgA : -INFINITY;
-            lg[i][1] = head_live ? lgB : -INFINITY;
+            // (lanes whose head t >= G see a zero query: their state is never read)
+            lg[i][0] = lgA, lg[i][1] = lgB;
         }
         // ------------------------------------------------------------ online softmax (base 2), head t
         float mx = fmaxf(fmaxf(lg[0][0], lg[0][1]), fmaxf(lg[1][0], lg[1][1]));
@@ -391,13 +346,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         for (int sft = 4; sft <= 16; sft <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
         const float nm = fmaxf(m_run, mx);
         if (__any_sync(0xffffffffu, nm > m_run)) {
-            const float sc = (nm == -INFINITY) ? 1.f : fast_exp2(m_run - nm);
+            // every iteration holds at least one real token, so nm is finite; exp2(-inf) = 0
+            const float sc = fast_exp2(m_run - nm);
             l_run *= sc;
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i][0] *= sc, o[i][2] *= sc;
             m_run = nm;
         }
-        const float sub = (m_run == -INFINITY) ? 0.f : m_run;
+        const float sub = m_run;
         uint32_t pb[2][2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -408,8 +364,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
             l_run += pA + pB;
             // rows = token slots, cols = (head t, unused) -> transpose to rows = columns.
             // (a masked token's staged norm may be stale and not finite)
-            pb[i][0] = movmatrix_trans(pack_half2(pA > 0.f ? pA * vnA : 0.f, 0.f));
-            pb[i][1] = movmatrix_trans(pack_half2(pB > 0.f ? pB * vnB : 0.f, 0.f));
+            float wA = pA * vnA, wB = pB * vnB;
+            if (tail) wA = pA > 0.f ? wA : 0.f, wB = pB > 0.f ? wB : 0.f;
+            pb[i][0] = movmatrix_trans(pack_half2(wA, 0.f));
+            pb[i][1] = movmatrix_trans(pack_half2(wB, 0.f));
         }
         // ------------------------------------------------------------ values
 #pragma unroll
@@ -431,10 +389,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
 #pragma unroll
             for (int mt = 0; mt < 8; ++mt) {
                 constexpr int W = 2 * VB;
-                const uint32_t a0 = lds_abs(slot_offset<W>(xa, mt * W, lane_v));
-                const uint32_t a1 = lds_abs(slot_offset<W>(ya, mt * W, lane_v));
-                const uint32_t a2 = lds_abs(slot_offset<W>(xb, mt * W, lane_v));
-                const uint32_t a3 = lds_abs(slot_offset<W>(yb, mt * W, lane_v));
+                const uint32_t a0 = lds_abs(slot_addr(xa, mt * W, lane_v));
+                const uint32_t a1 = lds_abs(slot_addr(ya, mt * W, lane_v));
+                const uint32_t a2 = lds_abs(slot_addr(xb, mt * W, lane_v));
+                const uint32_t a3 = lds_abs(slot_addr(yb, mt * W, lane_v));
                 mma_f16(o[mt], a0, a1, a2, a3, pb[i][0], pb[i][1]);
             }
         }
@@ -506,7 +464,10 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
                               void *out, cudaStream_t stream) {
     const int64_t rows = (int64_t)cache->batch * q_heads;
     DecodeWorkspace w = tq_carve_workspace(workspace, rows, n_splits);
-    int rc = tq_launch_qprep(ctx, q, q_dtype, rows, w.qrot, w.qproj, stream);
+    // the fragment area overlays the rotated / projected query rows of the workspace
+    uint32_t *frag = reinterpret_cast<uint32_t *>(w.qrot);
+    const int groups = q_heads / cache->kv_heads;
+    int rc = tq_launch_qprep_frag(ctx, q, q_dtype, rows / groups, groups, frag, stream);
     if (rc) return rc;
 
     Mma4Args a;
@@ -530,7 +491,7 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
         if (chunk < floor_chunk) chunk = floor_chunk;
     }
     a.chunk = (int)chunk;
-    a.qrot = w.qrot, a.qproj = w.qproj;
+    a.frag = frag;
     a.part_m = w.part_m, a.part_l = w.part_l, a.part_acc = w.part_acc;
     a.centers_k = ctx->centers_k, a.centers_v = ctx->centers_v;
     a.error_flag = ctx->error_flag;

@@ -26,7 +26,13 @@ struct DecodeWorkspace {
     float *part_acc;  // [rows][splits][128]
 };
 
+// Words per query head in the fragment area written by tq_qprep_frag_kernel (8 lane variants of
+// 26 words, padded to the size of the rotated + projected query rows it overlays).
+#define TQ_FRAG_ROW_WORDS (2 * TQ_D + 8)
+
 DecodeWorkspace tq_carve_workspace(void *workspace, int64_t rows, int n_splits);
 int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
                         cudaStream_t stream);
+int32_t tq_launch_qprep_frag(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t kv_rows, int G, uint32_t *frag,
+                             cudaStream_t stream);
 int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, cudaStream_t stream);

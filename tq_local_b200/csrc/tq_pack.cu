@@ -319,6 +319,16 @@ int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc 
     a.rot_k = ctx->rot_k, a.qjl_t = ctx->qjl_t;
     a.centers_k = ctx->centers_k;
     a.bounds[0] = ctx->bounds_k, a.bounds[1] = ctx->bounds_v;
+    static bool configured = false;
+    if (!configured) {  // same shared-memory carve-out as the decode kernels: no SM reconfiguration between them
+        configured = true;
+        cudaFuncSetAttribute(tq_pack_rows_kernel<float, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaFuncSetAttribute(tq_pack_rows_kernel<float, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaFuncSetAttribute(tq_pack_rows_kernel<__half, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaFuncSetAttribute(tq_pack_rows_kernel<__half, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaFuncSetAttribute(tq_pack_rows_kernel<__nv_bfloat16, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaFuncSetAttribute(tq_pack_rows_kernel<__nv_bfloat16, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    }
     const int64_t items = 2 * (int64_t)a.B * a.H * a.S;
     const int grid = grid_for(items, ctx->sm_count);
     const int threads = kWarpsPerBlock * 32;

@@ -346,33 +346,34 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_qprep_frag_kernel(const T *q, con
         }
     }
     __syncthreads();
-    if (tid < G * 8) {
-        const int hcol = tid >> 3, part = (tid >> 2) & 1, t = tid & 3;
-        uint32_t *out = frag + (R * G + hcol) * TQ_FRAG_ROW_WORDS + (part * 4 + t) * 26;
-        for (int s8 = 0; s8 < 8; ++s8) {
-            float x[4];
-            for (int i = 0; i < 4; ++i) {
-                const float v = s_r[hcol][32 * t + 4 * s8 + i];
+    // one thread per output word: G heads x 8 lane variants x 26 words
+    for (int w = tid; w < G * 8 * 26; w += blockDim.x) {
+        const int variant = w / 26, k = w % 26;
+        const int hcol = variant >> 3, part = (variant >> 2) & 1, t = variant & 3;
+        uint32_t word;
+        if (k < 16) {  // rotated query, f16 hi / lo terms: dims 32t + 4*(k/2) + 2*(k%2) + {0, 1}
+            const int d0 = 32 * t + 4 * (k >> 1) + 2 * (k & 1);
+            float x[2];
+            for (int i = 0; i < 2; ++i) {
+                const float v = s_r[hcol][d0 + i];
                 const float hi = __half2float(__float2half_rn(v));
                 x[i] = part ? (v - hi) : hi;
             }
-            const __half2 a = __floats2half2_rn(x[0], x[1]), b = __floats2half2_rn(x[2], x[3]);
-            out[2 * s8] = *reinterpret_cast<const uint32_t *>(&a);
-            out[2 * s8 + 1] = *reinterpret_cast<const uint32_t *>(&b);
-        }
-        for (int n = 0; n < 4; ++n)
-            for (int rr = 0; rr < 2; ++rr) {
-                uint32_t word = 0;
-                for (int k = 0; k < 4; ++k) {
-                    const int x16 = use_qjl ? s_x[hcol][32 * t + (7 - 2 * n - rr) + 8 * k] : 0;
-                    const int hi8 = (x16 + 128) >> 8;
-                    const int lo8 = x16 - (hi8 << 8);
-                    word |= (uint32_t)((part ? lo8 : hi8) & 0xff) << (8 * k);
-                }
-                out[16 + 2 * n + rr] = word;
+            const __half2 hh = __floats2half2_rn(x[0], x[1]);
+            word = *reinterpret_cast<const uint32_t *>(&hh);
+        } else if (k < 24) {  // projected query, s8 hi / lo terms behind sign bits (7 - 2n - rr) + 8j
+            const int n = (k - 16) >> 1, rr = (k - 16) & 1;
+            word = 0;
+            for (int jj = 0; jj < 4; ++jj) {
+                const int x16 = use_qjl ? s_x[hcol][32 * t + (7 - 2 * n - rr) + 8 * jj] : 0;
+                const int hi8 = (x16 + 128) >> 8;
+                const int lo8 = x16 - (hi8 << 8);
+                word |= (uint32_t)((part ? lo8 : hi8) & 0xff) << (8 * jj);
             }
-        out[24] = __float_as_uint(use_qjl ? s_scale[hcol] : 0.f);
-        out[25] = __float_as_uint(use_qjl ? s_bias[hcol] : 0.f);
+        } else {
+            word = __float_as_uint(use_qjl ? (k == 24 ? s_scale[hcol] : s_bias[hcol]) : 0.f);
+        }
+        frag[(R * G + hcol) * TQ_FRAG_ROW_WORDS + variant % 8 * 26 + k] = word;
     }
 }
 

@@ -71,26 +71,6 @@ extern "C" int32_t tq_profile_read(tq_ctx *ctx, double *main_ms, int64_t *main_l
 }
 extern "C" int32_t tq_abi_version(void) { return 1; }
 
-namespace {
-
-// Split a float into a TF32-representable high part (10 explicit mantissa bits,
-// truncated) and the remainder, so that hi + lo == x exactly in fp32.
-inline void split_tf32(float x, float *hi, float *lo) {
-    uint32_t u;
-    memcpy(&u, &x, 4);
-    u &= 0xffffe000u;
-    float h;
-    memcpy(&h, &u, 4);
-    *hi = h;
-    float r = x - h;
-    memcpy(&u, &r, 4);
-    u &= 0xffffe000u;
-    memcpy(&r, &u, 4);
-    *lo = r;
-}
-
-}  // namespace
-
 extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_desc *c) {
     if (!out || !c || !c->rot_k || !c->rot_v || !c->centers_k || !c->bounds_k || !c->centers_v || !c->bounds_v)
         return TQ_ERR_ARG;
@@ -100,16 +80,13 @@ extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_de
 
     const int kb = c->use_qjl ? c->bits - 1 : c->bits;
     const size_t M = (size_t)TQ_D * TQ_D;
-    // 6 plain matrices + 8 split matrices + 4 tables of 16 floats.
+    // 6 plain matrices + 8 matrix-sized slots holding four 96 KB operand images + 4 tables of 16 floats.
     const size_t n_float = 14 * M + 4 * 16 + 4;  // + the device status word
     std::vector<float> h(n_float, 0.0f);
     auto mat = [&](int i) { return h.data() + (size_t)i * M; };
     auto transpose = [&](const float *src, float *dst) {
         for (int r = 0; r < TQ_D; ++r)
             for (int cc = 0; cc < TQ_D; ++cc) dst[(size_t)cc * TQ_D + r] = src[(size_t)r * TQ_D + cc];
-    };
-    auto split = [&](const float *src, float *hi, float *lo) {
-        for (size_t i = 0; i < M; ++i) split_tf32(src[i], hi + i, lo + i);
     };
     memcpy(mat(0), c->rot_k, M * 4);
     transpose(c->rot_k, mat(1));
@@ -119,10 +96,13 @@ extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_de
         memcpy(mat(4), c->qjl, M * 4);
         transpose(c->qjl, mat(5));
     }
-    split(mat(0), mat(6), mat(7));    // R_k
-    split(mat(2), mat(8), mat(9));    // R_v
-    split(mat(1), mat(10), mat(11));  // R_k^T
-    split(mat(4), mat(12), mat(13));  // S
+    // operand images (49152 bf16 = 24576 floats each) in the 8 matrix-sized slots after the plain matrices
+    uint16_t *img = reinterpret_cast<uint16_t *>(mat(6));
+    const size_t kImg = 3 * M;  // bf16 elements per image
+    tq_build_operand_image(mat(0), img);             // R_k
+    tq_build_operand_image(mat(2), img + kImg);      // R_v
+    tq_build_operand_image(mat(1), img + 2 * kImg);  // R_k^T
+    tq_build_operand_image(mat(4), img + 3 * kImg);  // S
     float *tab = h.data() + 14 * M;
     for (int i = 0; i < 16; ++i) {
         tab[i] = i < (1 << kb) ? c->centers_k[i] : 0.0f;
@@ -162,14 +142,11 @@ extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_de
     ctx->rot_v_t = dm(3);
     ctx->qjl = dm(4);
     ctx->qjl_t = dm(5);
-    ctx->rot_k_hi = dm(6);
-    ctx->rot_k_lo = dm(7);
-    ctx->rot_v_hi = dm(8);
-    ctx->rot_v_lo = dm(9);
-    ctx->rot_kT_hi = dm(10);
-    ctx->rot_kT_lo = dm(11);
-    ctx->qjl_hi = dm(12);
-    ctx->qjl_lo = dm(13);
+    uint16_t *dimg = reinterpret_cast<uint16_t *>(dm(6));
+    ctx->img_rot_k = dimg;
+    ctx->img_rot_v = dimg + 3 * M;
+    ctx->img_rot_kt = dimg + 6 * M;
+    ctx->img_qjl = dimg + 9 * M;
     ctx->centers_k = d + 14 * M;
     ctx->bounds_k = ctx->centers_k + 16;
     ctx->centers_v = ctx->centers_k + 32;

@@ -29,11 +29,12 @@ struct tq_ctx {
     float *bounds_k;   // [16] (padded with +inf)
     float *centers_v;
     float *bounds_v;
-    // Split-precision copies for the tensor-core pack kernel (TF32 hi/lo parts).
-    float *rot_k_hi, *rot_k_lo;   // R_k      as [j][d] (B operand of u @ R_k^T, K-major)
-    float *rot_v_hi, *rot_v_lo;
-    float *rot_kT_hi, *rot_kT_lo; // R_k^T    as [d][j] (B operand of c @ R_k)
-    float *qjl_hi, *qjl_lo;       // S        as [i][d]
+    // Shared-memory images for the tensor-core encoder: each [128][128] K-major operand split
+    // into three bf16 terms, two 64-wide slabs per term, 128-byte swizzle (96 KB per matrix).
+    uint16_t *img_rot_k;   // rows j, k = d:  R_k[j][d]      (B operand of u @ R_k^T)
+    uint16_t *img_rot_v;
+    uint16_t *img_rot_kt;  // rows d, k = j:  R_k[j][d]      (B operand of c @ R_k)
+    uint16_t *img_qjl;     // rows i, k = d:  S[i][d]        (B operand of r @ S^T)
     void *base;       // one allocation holding everything above
     size_t base_bytes;
     struct tq_prof *prof;  // measurement hooks, see tq_profile_enable
@@ -107,5 +108,8 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
                               const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
                               const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
                               void *workspace, void *out, cudaStream_t stream);
+void tq_build_operand_image(const float *m, uint16_t *image);
+int32_t tq_launch_pack_tc(tq_ctx *ctx, const tq_dense_desc *x, int which, int32_t n_tokens,
+                          const tq_cache_desc *cache, int32_t pos0, cudaStream_t stream);
 int32_t tq_launch_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,
                           int32_t n_tokens, const tq_dense_desc *out, cudaStream_t stream);

@@ -27,6 +27,7 @@ struct PackArgs {
     const float *qjl_t;      // S^T[d][i]
     const float *centers_k;
     const float *bounds[2];
+    int first_kind, n_kinds;  // which of {keys, values} this launch encodes
 };
 
 // Assemble 32-bit word `w` of the LSB-first bitstream from one-code-per-byte storage.
@@ -58,15 +59,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) tq_pack_rows_kernel(PackA
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t n_vec = (int64_t)a.B * a.H * a.S;
-    const int64_t n_items = 2 * n_vec;
+    const int64_t n_items = a.n_kinds * n_vec;
     float *vec = s_vec[warp];
     float *cq = s_cq[warp];
     uint8_t *code = s_code[warp];
 
     for (int64_t item = (int64_t)blockIdx.x * kWarpsPerBlock + warp; item < n_items;
          item += (int64_t)gridDim.x * kWarpsPerBlock) {
-        const int kind = item >= n_vec ? 1 : 0;
-        const int64_t vid = item - (kind ? n_vec : 0);
+        const int kind = a.first_kind + (item >= n_vec ? 1 : 0);
+        const int64_t vid = item >= n_vec ? item - n_vec : item;
         const int t = (int)(vid % a.S);
         const int h = (int)((vid / a.S) % a.H);
         const int b = (int)(vid / ((int64_t)a.S * a.H));
@@ -329,7 +330,16 @@ int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc 
         cudaFuncSetAttribute(tq_pack_rows_kernel<__nv_bfloat16, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaFuncSetAttribute(tq_pack_rows_kernel<__nv_bfloat16, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     }
-    const int64_t items = 2 * (int64_t)a.B * a.H * a.S;
+    // Large encodes go to the tensor-core kernel: values always, keys when they are plain Q_mse.
+    // Q_prod keys (three chained mat-vecs) and small appends stay on this kernel.
+    a.first_kind = 0, a.n_kinds = 2;
+    const int64_t n_vec = (int64_t)a.B * a.H * a.S;
+    if (n_vec >= 2048) {
+        if (tq_launch_pack_tc(ctx, v, 1, n_tokens, cache, pos0, stream) == TQ_OK) a.n_kinds = 1;
+        if (a.n_kinds == 1 && !ctx->use_qjl && tq_launch_pack_tc(ctx, k, 0, n_tokens, cache, pos0, stream) == TQ_OK)
+            return TQ_OK;
+    }
+    const int64_t items = a.n_kinds * n_vec;
     const int grid = grid_for(items, ctx->sm_count);
     const int threads = kWarpsPerBlock * 32;
 #define TQ_LAUNCH_PACK(T)                                                          \

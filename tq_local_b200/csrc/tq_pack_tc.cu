@@ -1,0 +1,371 @@
+// Prefill encoder on the 5th-generation tensor cores: rotate 128 vectors at a time with
+// tcgen05.mma, quantise and bit-pack in the epilogue.
+//
+//   z[128 tok x 128] = u[128 tok x 128] * R^T          (u = x / |x|, fp32 accuracy)
+//
+// fp32 accuracy on bf16 tensor cores: both operands are split into three bf16 terms
+// (x = x1 + x2 + x3 exactly to 24 bits) and the six products down to 2^-16 relative weight
+// are accumulated in the fp32 TMEM accumulator:  x1*r1 + x1*r2 + x2*r1 + x2*r2 + x1*r3 + x3*r1.
+// bf16 x bf16 products are exact in fp32, so the only rounding is the accumulation.
+//
+// One CTA per SM, persistent over 128-vector tiles:
+//   * the rotation's three bf16 terms (96 KB, already in the 128-byte-swizzled K-major image
+//     the MMA wants) are fetched once with TMA bulk copies onto an mbarrier;
+//   * each thread owns one vector: it loads the row, computes the norm, normalises, splits
+//     into three bf16 terms and stores them swizzled into the A tiles (96 KB);
+//   * one thread issues 48 tcgen05.mma (M = N = 128, K = 16, kind::f16, bf16 in / fp32 out)
+//     into 128 TMEM columns and commits to an mbarrier;
+//   * each thread reads its own accumulator row back with tcgen05.ld (32 columns at a time),
+//     finds the Lloyd-Max bin by binary search ("value equal to a boundary -> lower bin"),
+//     builds the LSB-first bitstream in registers and writes codes + fp16 norm.
+// Every mbarrier wait is bounded and reports through the device status word.
+#include <math.h>
+#include <string.h>
+
+#include "tq_common.cuh"
+
+namespace {
+
+constexpr int kTile = 128;                   // vectors per tile == threads per CTA
+constexpr int kTermBytes = kTile * TQ_D * 2;  // one bf16 term of a 128 x 128 operand: 32 KB
+constexpr int kSlabBytes = kTile * 128;       // 128 rows x 64 bf16 (one 128-byte swizzle row each): 16 KB
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct PackTcArgs {
+    const void *x;
+    int64_t sb, sh, st;
+    int B, H, S, pos0;
+    uint8_t *codes;
+    uint16_t *norms;
+    int64_t cache_sb, cache_sh;
+    const uint16_t *b_image;  // 3 terms x 2 slabs x 16 KB, swizzled (see tq_build_operand_image)
+    const float *bounds;      // 16 floats, padded with +inf
+    int *error_flag;
+    int n_tiles;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+// Instruction descriptor: D = f32, A = B = bf16, both K-major, N = 128, M = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(kInstrDesc), "r"(accumulate)
+        : "memory");
+}
+
+// Byte offset of element (row, k) inside one bf16 term image (two 64-wide slabs, 128-B swizzle).
+__host__ __device__ inline int operand_offset(int row, int k) {
+    const int slab = k >> 6, kk = k & 63;
+    return slab * kSlabBytes + (row >> 3) * 1024 + (row & 7) * 128 + (((kk >> 3) ^ (row & 7)) << 4) + (kk & 7) * 2;
+}
+
+__device__ __forceinline__ void split3(float v, __nv_bfloat16 &t1, __nv_bfloat16 &t2, __nv_bfloat16 &t3) {
+    t1 = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(t1);
+    t2 = __float2bfloat16_rn(r1);
+    t3 = __float2bfloat16_rn(r1 - __bfloat162float(t2));
+}
+
+template <typename T> struct RowLoader;
+template <> struct RowLoader<float> {  // 8 floats = two 16-byte loads
+    static __device__ __forceinline__ void load8(const float *p, float (&v)[8]) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    }
+};
+template <> struct RowLoader<__half> {
+    static __device__ __forceinline__ void load8(const __half *p, float (&v)[8]) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4 *>(p));
+        const __half2 *h = reinterpret_cast<const __half2 *>(&a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[2 * i] = __low2float(h[i]), v[2 * i + 1] = __high2float(h[i]);
+    }
+};
+template <> struct RowLoader<__nv_bfloat16> {
+    static __device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8]) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4 *>(p));
+        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[2 * i] = __low2float(h[i]), v[2 * i + 1] = __high2float(h[i]);
+    }
+};
+
+template <typename T, int BITS>
+__global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ float s_bnd[16];
+    __shared__ __align__(8) uint64_t s_bar[2];  // [0] rotation image landed, [1] MMAs of a tile done
+    __shared__ uint32_t s_tmem;
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+    uint8_t *a_tiles = smem_raw + (base - raw);    // three A terms, then three B terms
+    const uint32_t a_addr = base, b_addr = base + 3 * kTermBytes;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t bar_b = smem_u32(&s_bar[0]), bar_mma = smem_u32(&s_bar[1]);
+
+    if (tid < 16) s_bnd[tid] = a.bounds[tid];
+    if (warp == 0) {  // TMEM: 128 columns of fp32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)),
+                     "r"(128));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n");
+    }
+    if (tid == 0) {
+        mbar_init(bar_b, 1);
+        mbar_init(bar_mma, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        mbar_expect_tx(bar_b, 3 * kTermBytes);
+        for (int i = 0; i < 6; ++i)
+            tma_load_1d(b_addr + i * kSlabBytes, reinterpret_cast<const uint8_t *>(a.b_image) + i * kSlabBytes,
+                        kSlabBytes, bar_b);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    bool timed_out = false;
+    bool b_ready = false;
+
+    const int64_t n_vec = (int64_t)a.B * a.H * a.S;
+    uint32_t phase = 0;
+    for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+        // ---------------- load, normalise, split, store swizzled (thread = vector)
+        const int64_t vid = (int64_t)tile * kTile + tid;
+        const bool valid = vid < n_vec;
+        const int64_t v2 = valid ? vid : 0;
+        const int t = (int)(v2 % a.S);
+        const int h = (int)((v2 / a.S) % a.H);
+        const int b = (int)(v2 / ((int64_t)a.S * a.H));
+        const T *src = reinterpret_cast<const T *>(a.x) + b * a.sb + h * a.sh + (int64_t)t * a.st;
+        float ss = 0.f;
+#pragma unroll 4
+        for (int c = 0; c < 16; ++c) {
+            float v[8];
+            RowLoader<T>::load8(src + 8 * c, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+        }
+        const float nrm = sqrtf(ss);
+        const float safe = nrm > 0.0f ? nrm : 1.0f;
+#pragma unroll 2
+        for (int c = 0; c < 16; ++c) {
+            float v[8];
+            RowLoader<T>::load8(src + 8 * c, v);
+            __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) split3(valid ? v[i] / safe : 0.f, t1[i], t2[i], t3[i]);
+            const int off = operand_offset(tid, 8 * c);
+            *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
+            *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
+            *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> tensor-core reads
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncthreads();
+
+        // ---------------- 48 MMAs by one thread
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (!b_ready) {
+                if (!mbar_wait(bar_b, 0)) timed_out = true;
+                b_ready = true;
+            }
+            uint32_t acc = 0;
+#pragma unroll 1
+            for (int s = 0; s < 8; ++s) {
+                const uint32_t koff = (s >> 2) * kSlabBytes + (s & 3) * 32;
+                const uint64_t a1 = umma_desc(a_addr + koff), a2 = umma_desc(a_addr + kTermBytes + koff),
+                               a3 = umma_desc(a_addr + 2 * kTermBytes + koff);
+                const uint64_t b1 = umma_desc(b_addr + koff), b2 = umma_desc(b_addr + kTermBytes + koff),
+                               b3 = umma_desc(b_addr + 2 * kTermBytes + koff);
+                umma_bf16(tmem, a1, b3, acc);
+                umma_bf16(tmem, a3, b1, 1);
+                umma_bf16(tmem, a2, b2, 1);
+                umma_bf16(tmem, a1, b2, 1);
+                umma_bf16(tmem, a2, b1, 1);
+                umma_bf16(tmem, a1, b1, 1);
+                acc = 1;
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_mma)
+                         : "memory");
+        }
+        if (!mbar_wait(bar_mma, phase)) timed_out = true;
+        phase ^= 1;
+        __syncwarp();  // thread 0 took the issue path; tcgen05.ld below is warp-collective
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+
+        // ---------------- epilogue: this thread's accumulator row -> codes
+        uint32_t words[4 * BITS];
+#pragma unroll
+        for (int w = 0; w < 4 * BITS; ++w) words[w] = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + 32 * c;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+                  "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                  "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr));
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float z = __uint_as_float(r[i]);
+                uint32_t idx = 0;  // number of boundaries strictly below z
+#pragma unroll
+                for (int stepw = 1 << (BITS - 1); stepw > 0; stepw >>= 1)
+                    if (s_bnd[idx + stepw - 1] < z) idx += stepw;
+                const int bit = (32 * c + i) * BITS, w = bit >> 5, sh = bit & 31;
+                words[w] |= idx << sh;
+                if (sh + BITS > 32) words[w + 1] |= idx >> (32 - sh);
+            }
+        }
+        if (valid) {
+            const int64_t row = b * a.cache_sb + h * a.cache_sh + a.pos0 + t;
+            uint4 *dst = reinterpret_cast<uint4 *>(a.codes + row * (int64_t)(16 * BITS));
+#pragma unroll
+            for (int w = 0; w < BITS; ++w)
+                dst[w] = make_uint4(words[4 * w], words[4 * w + 1], words[4 * w + 2], words[4 * w + 3]);
+            a.norms[row] = tq_float_to_half_bits(safe);
+        }
+        // all accumulator rows are read before the next tile's MMAs overwrite them
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncthreads();
+    }
+    if (tid == 0 && !b_ready && !mbar_wait(bar_b, 0)) timed_out = true;  // never leave a copy in flight
+    if (timed_out) atomicExch(a.error_flag, 3);
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(128));
+    }
+}
+
+inline uint16_t host_bf16_rn(float v) {
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    const uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7FFFu + lsb;
+    return (uint16_t)(u >> 16);
+}
+inline float host_bf16_to_float(uint16_t h) {
+    uint32_t u = (uint32_t)h << 16;
+    float v;
+    memcpy(&v, &u, 4);
+    return v;
+}
+
+}  // namespace
+
+// Host: the 96 KB shared-memory image of a [128 x 128] K-major operand `m[row][k]` split into
+// three bf16 terms, each stored as two 64-wide slabs with the 128-byte swizzle.
+void tq_build_operand_image(const float *m, uint16_t *image) {
+    for (int row = 0; row < TQ_D; ++row)
+        for (int k = 0; k < TQ_D; ++k) {
+            const float v = m[(size_t)row * TQ_D + k];
+            const uint16_t t1 = host_bf16_rn(v);
+            const float r1 = v - host_bf16_to_float(t1);
+            const uint16_t t2 = host_bf16_rn(r1);
+            const uint16_t t3 = host_bf16_rn(r1 - host_bf16_to_float(t2));
+            const int off = operand_offset(row, k) / 2;
+            image[off] = t1;
+            image[kTermBytes / 2 + off] = t2;
+            image[2 * (kTermBytes / 2) + off] = t3;
+        }
+}
+
+template <typename T, int BITS> static cudaError_t launch_tc(const PackTcArgs &a, int grid, cudaStream_t stream) {
+    const int smem = 6 * kTermBytes + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(tq_pack_tc_kernel<T, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    tq_pack_tc_kernel<T, BITS><<<grid, kTile, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+// Q_mse encode of one dense tensor (keys when which == 0, values when which == 1) on the
+// tensor cores.  Returns TQ_ERR_UNSUPPORTED when the tensor's alignment rules it out.
+int32_t tq_launch_pack_tc(tq_ctx *ctx, const tq_dense_desc *x, int which, int32_t n_tokens,
+                          const tq_cache_desc *cache, int32_t pos0, cudaStream_t stream) {
+    const int esize = x->dtype == TQ_DTYPE_F32 ? 4 : 2;
+    if (((uintptr_t)x->data & 15) || ((x->stride_b * esize) & 15) || ((x->stride_h * esize) & 15) ||
+        ((x->stride_t * esize) & 15))
+        return TQ_ERR_UNSUPPORTED;
+    PackTcArgs a;
+    a.x = x->data, a.sb = x->stride_b, a.sh = x->stride_h, a.st = x->stride_t;
+    a.B = cache->batch, a.H = cache->kv_heads, a.S = n_tokens, a.pos0 = pos0;
+    a.codes = which == 0 ? cache->k_codes : cache->v_codes;
+    a.norms = which == 0 ? cache->k_norms : cache->v_norms;
+    a.cache_sb = cache->stride_b, a.cache_sh = cache->stride_h;
+    a.b_image = which == 0 ? ctx->img_rot_k : ctx->img_rot_v;
+    a.bounds = which == 0 ? ctx->bounds_k : ctx->bounds_v;
+    a.error_flag = ctx->error_flag;
+    const int bits = which == 0 ? ctx->key_bits : ctx->bits;
+    const int64_t n_vec = (int64_t)a.B * a.H * a.S;
+    a.n_tiles = (int)((n_vec + kTile - 1) / kTile);
+    const int grid = a.n_tiles < ctx->sm_count ? a.n_tiles : ctx->sm_count;
+    cudaError_t e = cudaErrorInvalidValue;
+#define TQ_TC_CASE(T)                                          \
+    switch (bits) {                                            \
+        case 1: e = launch_tc<T, 1>(a, grid, stream); break;   \
+        case 2: e = launch_tc<T, 2>(a, grid, stream); break;   \
+        case 3: e = launch_tc<T, 3>(a, grid, stream); break;   \
+        case 4: e = launch_tc<T, 4>(a, grid, stream); break;   \
+        default: return TQ_ERR_UNSUPPORTED;                    \
+    }
+    if (x->dtype == TQ_DTYPE_F32) {
+        TQ_TC_CASE(float)
+    } else if (x->dtype == TQ_DTYPE_F16) {
+        TQ_TC_CASE(__half)
+    } else {
+        TQ_TC_CASE(__nv_bfloat16)
+    }
+#undef TQ_TC_CASE
+    tq_prof_count(ctx, 1);
+    TQ_CUDA_CHECK(e);
+    return TQ_OK;
+}

@@ -167,6 +167,8 @@ def test_dense_tail_attention_matches_reference(setup_golden, case):
     (2, True, torch.bfloat16, 1, 8, 1, 777),
     (2, False, torch.float32, 1, 6, 2, 300),
     (4, True, torch.float32, 1, 16, 2, 640),
+    (2, True, torch.bfloat16, 2, 8, 2, 600),
+    (3, True, torch.float16, 1, 4, 4, 300),
 ])
 def test_seeded_layer_against_oracle(setup_golden, bits, qjl, dtype, B, Hq, Hkv, N):
     """Larger seeded inputs: encode on the GPU, compare codes with the oracle, then

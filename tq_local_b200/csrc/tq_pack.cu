@@ -330,14 +330,13 @@ int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc 
         cudaFuncSetAttribute(tq_pack_rows_kernel<__nv_bfloat16, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaFuncSetAttribute(tq_pack_rows_kernel<__nv_bfloat16, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     }
-    // Large encodes go to the tensor-core kernel: values always, keys when they are plain Q_mse.
-    // Q_prod keys (three chained mat-vecs) and small appends stay on this kernel.
+    // Large encodes go to the tensor-core kernel; small appends (and tensors whose alignment
+    // the tensor-core loader cannot take) stay on this one.
     a.first_kind = 0, a.n_kinds = 2;
     const int64_t n_vec = (int64_t)a.B * a.H * a.S;
-    if (n_vec >= 2048) {
+    if (n_vec >= 1024) {
         if (tq_launch_pack_tc(ctx, v, 1, n_tokens, cache, pos0, stream) == TQ_OK) a.n_kinds = 1;
-        if (a.n_kinds == 1 && !ctx->use_qjl && tq_launch_pack_tc(ctx, k, 0, n_tokens, cache, pos0, stream) == TQ_OK)
-            return TQ_OK;
+        if (a.n_kinds == 1 && tq_launch_pack_tc(ctx, k, 0, n_tokens, cache, pos0, stream) == TQ_OK) return TQ_OK;
     }
     const int64_t items = a.n_kinds * n_vec;
     const int grid = grid_for(items, ctx->sm_count);

@@ -38,7 +38,12 @@ struct PackTcArgs {
     uint8_t *codes;
     uint16_t *norms;
     int64_t cache_sb, cache_sh;
-    const uint16_t *b_image;  // 3 terms x 2 slabs x 16 KB, swizzled (see tq_build_operand_image)
+    const uint16_t *b_image;   // stage 1 operand: 3 terms x 2 slabs x 16 KB, swizzled (see tq_build_operand_image)
+    const uint16_t *b_image2;  // Q_prod: R_k^T image (reconstruction)
+    const uint16_t *b_image3;  // Q_prod: S image (QJL projection)
+    const float *centers;      // 16 floats (key centres), Q_prod only
+    uint8_t *signs;
+    uint16_t *rnorms;
     const float *bounds;      // 16 floats, padded with +inf
     int *error_flag;
     int n_tiles;
@@ -126,11 +131,33 @@ template <> struct RowLoader<__nv_bfloat16> {
     }
 };
 
-template <typename T, int BITS>
+// 32 consecutive fp32 accumulator columns of this thread's TMEM lane (= its vector).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// QJL = false: Q_mse encode (values, or keys without the sketch): one GEMM per tile.
+// QJL = true : Q_prod key encode: three chained GEMMs per tile through the same TMEM columns
+//   1. z     = u @ R_k^T                        -> codes (BITS = key bits), norm
+//   2. recon = centers[codes] @ R_k             -> residual r = x - round_T(recon * fp16(norm)), |r|
+//   3. proj  = (r / |r|) @ S^T                  -> sign bits, fp16 |r|
+// The B operand (96 KB) is swapped between the stages with TMA bulk copies that are issued as
+// soon as the previous stage's MMAs have completed, so they overlap with the epilogues.
+template <typename T, int BITS, bool QJL>
 __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ float s_bnd[16];
-    __shared__ __align__(8) uint64_t s_bar[2];  // [0] rotation image landed, [1] MMAs of a tile done
+    __shared__ __align__(16) __nv_bfloat16 s_cen3[3][16];  // bf16 terms of the key centres
+    __shared__ __align__(8) uint64_t s_bar[2];  // [0] B operand landed, [1] MMAs of a stage done
     __shared__ uint32_t s_tmem;
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -138,8 +165,54 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
     const uint32_t a_addr = base, b_addr = base + 3 * kTermBytes;
     const int tid = threadIdx.x, warp = tid >> 5;
     const uint32_t bar_b = smem_u32(&s_bar[0]), bar_mma = smem_u32(&s_bar[1]);
+    bool timed_out = false;
+    uint32_t b_phase = 0, mma_phase = 0;
 
-    if (tid < 16) s_bnd[tid] = a.bounds[tid];
+    auto load_b = [&](const uint16_t *image) {  // thread 0 only; the B region must be idle
+        mbar_expect_tx(bar_b, 3 * kTermBytes);
+        for (int i = 0; i < 6; ++i)
+            tma_load_1d(b_addr + i * kSlabBytes, reinterpret_cast<const uint8_t *>(image) + i * kSlabBytes, kSlabBytes,
+                        bar_b);
+    };
+    // Everybody has stored its A row: make the stores visible to the tensor core, let thread 0
+    // wait for B and issue the 48 MMAs of one GEMM, then everybody waits for their completion.
+    auto run_gemm = [&]() {
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (!mbar_wait(bar_b, b_phase)) timed_out = true;
+            uint32_t acc = 0;
+#pragma unroll 1
+            for (int s = 0; s < 8; ++s) {
+                const uint32_t koff = (s >> 2) * kSlabBytes + (s & 3) * 32;
+                const uint64_t a1 = umma_desc(a_addr + koff), a2 = umma_desc(a_addr + kTermBytes + koff),
+                               a3 = umma_desc(a_addr + 2 * kTermBytes + koff);
+                const uint64_t b1 = umma_desc(b_addr + koff), b2 = umma_desc(b_addr + kTermBytes + koff),
+                               b3 = umma_desc(b_addr + 2 * kTermBytes + koff);
+                umma_bf16(s_tmem, a1, b3, acc);
+                umma_bf16(s_tmem, a3, b1, 1);
+                umma_bf16(s_tmem, a2, b2, 1);
+                umma_bf16(s_tmem, a1, b2, 1);
+                umma_bf16(s_tmem, a2, b1, 1);
+                umma_bf16(s_tmem, a1, b1, 1);
+                acc = 1;
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_mma)
+                         : "memory");
+        }
+        b_phase ^= 1;
+        if (!mbar_wait(bar_mma, mma_phase)) timed_out = true;
+        mma_phase ^= 1;
+        __syncwarp();  // thread 0 took the issue path; tcgen05.ld is warp-collective
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    };
+
+    if (tid < 16) {
+        s_bnd[tid] = a.bounds[tid];
+        if (QJL) split3(a.centers[tid], s_cen3[0][tid], s_cen3[1][tid], s_cen3[2][tid]);
+    }
     if (warp == 0) {  // TMEM: 128 columns of fp32 accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)),
                      "r"(128));
@@ -150,22 +223,17 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
         mbar_init(bar_mma, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        mbar_expect_tx(bar_b, 3 * kTermBytes);
-        for (int i = 0; i < 6; ++i)
-            tma_load_1d(b_addr + i * kSlabBytes, reinterpret_cast<const uint8_t *>(a.b_image) + i * kSlabBytes,
-                        kSlabBytes, bar_b);
+        if ((int)blockIdx.x < a.n_tiles) load_b(a.b_image);
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = s_tmem;
-    bool timed_out = false;
-    bool b_ready = false;
+    const uint32_t my_tmem = tmem + ((uint32_t)(warp * 32) << 16);
 
     const int64_t n_vec = (int64_t)a.B * a.H * a.S;
-    uint32_t phase = 0;
     for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
-        // ---------------- load, normalise, split, store swizzled (thread = vector)
+        // ---------------- stage 1: load, normalise, split, store swizzled (thread = vector)
         const int64_t vid = (int64_t)tile * kTile + tid;
         const bool valid = vid < n_vec;
         const int64_t v2 = valid ? vid : 0;
@@ -173,6 +241,7 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
         const int h = (int)((v2 / a.S) % a.H);
         const int b = (int)(v2 / ((int64_t)a.S * a.H));
         const T *src = reinterpret_cast<const T *>(a.x) + b * a.sb + h * a.sh + (int64_t)t * a.st;
+        const int64_t row = b * a.cache_sb + h * a.cache_sh + a.pos0 + t;
         float ss = 0.f;
 #pragma unroll 4
         for (int c = 0; c < 16; ++c) {
@@ -195,60 +264,21 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
             *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
             *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
         }
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> tensor-core reads
-        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        __syncthreads();
-
-        // ---------------- 48 MMAs by one thread
+        run_gemm();
+        const bool more = tile + (int)gridDim.x < a.n_tiles;
         if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            if (!b_ready) {
-                if (!mbar_wait(bar_b, 0)) timed_out = true;
-                b_ready = true;
-            }
-            uint32_t acc = 0;
-#pragma unroll 1
-            for (int s = 0; s < 8; ++s) {
-                const uint32_t koff = (s >> 2) * kSlabBytes + (s & 3) * 32;
-                const uint64_t a1 = umma_desc(a_addr + koff), a2 = umma_desc(a_addr + kTermBytes + koff),
-                               a3 = umma_desc(a_addr + 2 * kTermBytes + koff);
-                const uint64_t b1 = umma_desc(b_addr + koff), b2 = umma_desc(b_addr + kTermBytes + koff),
-                               b3 = umma_desc(b_addr + 2 * kTermBytes + koff);
-                umma_bf16(tmem, a1, b3, acc);
-                umma_bf16(tmem, a3, b1, 1);
-                umma_bf16(tmem, a2, b2, 1);
-                umma_bf16(tmem, a1, b2, 1);
-                umma_bf16(tmem, a2, b1, 1);
-                umma_bf16(tmem, a1, b1, 1);
-                acc = 1;
-            }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_mma)
-                         : "memory");
+            if (QJL) load_b(a.b_image2);
+            else if (more) load_b(a.b_image);
         }
-        if (!mbar_wait(bar_mma, phase)) timed_out = true;
-        phase ^= 1;
-        __syncwarp();  // thread 0 took the issue path; tcgen05.ld below is warp-collective
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 
-        // ---------------- epilogue: this thread's accumulator row -> codes
-        uint32_t words[4 * BITS];
+        // ---------------- epilogue 1: this thread's accumulator row -> codes
+        uint32_t words[4 * BITS + 1];
 #pragma unroll
-        for (int w = 0; w < 4 * BITS; ++w) words[w] = 0;
+        for (int w = 0; w <= 4 * BITS; ++w) words[w] = 0;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             uint32_t r[32];
-            const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + 32 * c;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
-                  "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
-                  "=r"(r[30]), "=r"(r[31])
-                : "r"(taddr));
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            tmem_ld32(my_tmem + 32 * c, r);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float z = __uint_as_float(r[i]);
@@ -261,19 +291,96 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
                 if (sh + BITS > 32) words[w + 1] |= idx >> (32 - sh);
             }
         }
+        const uint16_t nh = tq_float_to_half_bits(safe);
         if (valid) {
-            const int64_t row = b * a.cache_sb + h * a.cache_sh + a.pos0 + t;
             uint4 *dst = reinterpret_cast<uint4 *>(a.codes + row * (int64_t)(16 * BITS));
 #pragma unroll
             for (int w = 0; w < BITS; ++w)
                 dst[w] = make_uint4(words[4 * w], words[4 * w + 1], words[4 * w + 2], words[4 * w + 3]);
-            a.norms[row] = tq_float_to_half_bits(safe);
+            a.norms[row] = nh;
         }
-        // all accumulator rows are read before the next tile's MMAs overwrite them
+
+        if (QJL) {
+            // ---------------- stage 2: A = centres[codes] (three bf16 terms from a 2^BITS-entry table)
+#pragma unroll 2
+            for (int c = 0; c < 16; ++c) {
+                __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int bit = (8 * c + i) * BITS, w = bit >> 5, sh = bit & 31;
+                    uint32_t idx = words[w] >> sh;
+                    if (sh + BITS > 32) idx |= words[w + 1] << (32 - sh);
+                    idx &= (1u << BITS) - 1u;
+                    t1[i] = s_cen3[0][idx], t2[i] = s_cen3[1][idx], t3[i] = s_cen3[2][idx];
+                }
+                const int off = operand_offset(tid, 8 * c);
+                *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
+                *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
+                *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
+            }
+            run_gemm();
+            if (tid == 0) load_b(a.b_image3);
+
+            // ---------------- epilogue 2: residual against the dtype-rounded reconstruction
+            const float nf = tq_half_bits_to_float(nh);
+            float rs = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(my_tmem + 32 * c, r);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    float v[8];
+                    RowLoader<T>::load8(src + 32 * c + 8 * q4, v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float res = v[i] - tq_round_through<T>(__uint_as_float(r[8 * q4 + i]) * nf);
+                        rs = fmaf(res, res, rs);
+                    }
+                }
+            }
+            const float rn = sqrtf(rs);
+            const float rsafe = rn > 0.0f ? rn : 1.0f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(my_tmem + 32 * c, r);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    float v[8];
+                    RowLoader<T>::load8(src + 32 * c + 8 * q4, v);
+                    __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float res = v[i] - tq_round_through<T>(__uint_as_float(r[8 * q4 + i]) * nf);
+                        split3(valid ? res / rsafe : 0.f, t1[i], t2[i], t3[i]);
+                    }
+                    const int off = operand_offset(tid, 32 * c + 8 * q4);
+                    *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
+                    *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
+                    *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
+                }
+            }
+            // ---------------- stage 3: projection, sign bits
+            run_gemm();
+            if (tid == 0 && more) load_b(a.b_image);
+            uint32_t sg[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(my_tmem + 32 * c, r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sg[c] |= (__uint_as_float(r[i]) >= 0.0f ? 1u : 0u) << i;
+            }
+            if (valid) {
+                *reinterpret_cast<uint4 *>(a.signs + row * 16) = make_uint4(sg[0], sg[1], sg[2], sg[3]);
+                a.rnorms[row] = tq_float_to_half_bits(rsafe);
+            }
+        }
+        // every accumulator row is read before the next GEMM overwrites the columns
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
         __syncthreads();
     }
-    if (tid == 0 && !b_ready && !mbar_wait(bar_b, 0)) timed_out = true;  // never leave a copy in flight
     if (timed_out) atomicExch(a.error_flag, 3);
     __syncthreads();
     if (warp == 0) {
@@ -315,20 +422,22 @@ void tq_build_operand_image(const float *m, uint16_t *image) {
         }
 }
 
-template <typename T, int BITS> static cudaError_t launch_tc(const PackTcArgs &a, int grid, cudaStream_t stream) {
+template <typename T, int BITS, bool QJL>
+static cudaError_t launch_tc(const PackTcArgs &a, int grid, cudaStream_t stream) {
     const int smem = 6 * kTermBytes + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(tq_pack_tc_kernel<T, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(tq_pack_tc_kernel<T, BITS, QJL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    tq_pack_tc_kernel<T, BITS><<<grid, kTile, smem, stream>>>(a);
+    tq_pack_tc_kernel<T, BITS, QJL><<<grid, kTile, smem, stream>>>(a);
     return cudaGetLastError();
 }
 
-// Q_mse encode of one dense tensor (keys when which == 0, values when which == 1) on the
-// tensor cores.  Returns TQ_ERR_UNSUPPORTED when the tensor's alignment rules it out.
+// Encode one dense tensor on the tensor cores: values (which == 1, Q_mse) or keys (which == 0,
+// Q_mse or, when the context uses QJL, Q_prod with sign sketch and residual norms).  Returns
+// TQ_ERR_UNSUPPORTED when the tensor's alignment rules it out.
 int32_t tq_launch_pack_tc(tq_ctx *ctx, const tq_dense_desc *x, int which, int32_t n_tokens,
                           const tq_cache_desc *cache, int32_t pos0, cudaStream_t stream) {
     const int esize = x->dtype == TQ_DTYPE_F32 ? 4 : 2;
@@ -344,18 +453,22 @@ int32_t tq_launch_pack_tc(tq_ctx *ctx, const tq_dense_desc *x, int which, int32_
     a.b_image = which == 0 ? ctx->img_rot_k : ctx->img_rot_v;
     a.bounds = which == 0 ? ctx->bounds_k : ctx->bounds_v;
     a.error_flag = ctx->error_flag;
+    a.b_image2 = ctx->img_rot_kt, a.b_image3 = ctx->img_qjl;
+    a.centers = ctx->centers_k;
+    a.signs = cache->k_signs, a.rnorms = cache->k_rnorms;
+    const bool qjl = which == 0 && ctx->use_qjl;
     const int bits = which == 0 ? ctx->key_bits : ctx->bits;
     const int64_t n_vec = (int64_t)a.B * a.H * a.S;
     a.n_tiles = (int)((n_vec + kTile - 1) / kTile);
     const int grid = a.n_tiles < ctx->sm_count ? a.n_tiles : ctx->sm_count;
     cudaError_t e = cudaErrorInvalidValue;
-#define TQ_TC_CASE(T)                                          \
-    switch (bits) {                                            \
-        case 1: e = launch_tc<T, 1>(a, grid, stream); break;   \
-        case 2: e = launch_tc<T, 2>(a, grid, stream); break;   \
-        case 3: e = launch_tc<T, 3>(a, grid, stream); break;   \
-        case 4: e = launch_tc<T, 4>(a, grid, stream); break;   \
-        default: return TQ_ERR_UNSUPPORTED;                    \
+#define TQ_TC_CASE(T)                                                                                     \
+    switch (bits) {                                                                                       \
+        case 1: e = qjl ? launch_tc<T, 1, true>(a, grid, stream) : cudaErrorInvalidValue; break;          \
+        case 2: e = qjl ? launch_tc<T, 2, true>(a, grid, stream) : launch_tc<T, 2, false>(a, grid, stream); break; \
+        case 3: e = qjl ? launch_tc<T, 3, true>(a, grid, stream) : launch_tc<T, 3, false>(a, grid, stream); break; \
+        case 4: e = qjl ? cudaErrorInvalidValue : launch_tc<T, 4, false>(a, grid, stream); break;         \
+        default: return TQ_ERR_UNSUPPORTED;                                                               \
     }
     if (x->dtype == TQ_DTYPE_F32) {
         TQ_TC_CASE(float)

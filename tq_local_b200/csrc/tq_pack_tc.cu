@@ -167,12 +167,14 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
     const uint32_t bar_b = smem_u32(&s_bar[0]), bar_mma = smem_u32(&s_bar[1]);
     bool timed_out = false;
     uint32_t b_phase = 0, mma_phase = 0;
+    bool b_pending = false;  // thread 0: a B-operand copy has been issued and not yet waited for
 
     auto load_b = [&](const uint16_t *image) {  // thread 0 only; the B region must be idle
         mbar_expect_tx(bar_b, 3 * kTermBytes);
         for (int i = 0; i < 6; ++i)
             tma_load_1d(b_addr + i * kSlabBytes, reinterpret_cast<const uint8_t *>(image) + i * kSlabBytes, kSlabBytes,
                         bar_b);
+        b_pending = true;
     };
     // Everybody has stored its A row: make the stores visible to the tensor core, let thread 0
     // wait for B and issue the 48 MMAs of one GEMM, then everybody waits for their completion.
@@ -182,7 +184,11 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
         __syncthreads();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            if (!mbar_wait(bar_b, b_phase)) timed_out = true;
+            if (b_pending) {
+                if (!mbar_wait(bar_b, b_phase)) timed_out = true;
+                b_phase ^= 1;
+                b_pending = false;
+            }
             uint32_t acc = 0;
 #pragma unroll 1
             for (int s = 0; s < 8; ++s) {
@@ -202,7 +208,6 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_mma)
                          : "memory");
         }
-        b_phase ^= 1;
         if (!mbar_wait(bar_mma, mma_phase)) timed_out = true;
         mma_phase ^= 1;
         __syncwarp();  // thread 0 took the issue path; tcgen05.ld is warp-collective
@@ -266,10 +271,7 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
         }
         run_gemm();
         const bool more = tile + (int)gridDim.x < a.n_tiles;
-        if (tid == 0) {
-            if (QJL) load_b(a.b_image2);
-            else if (more) load_b(a.b_image);
-        }
+        if (QJL && tid == 0) load_b(a.b_image2);  // (a plain Q_mse encode keeps its one operand resident)
 
         // ---------------- epilogue 1: this thread's accumulator row -> codes
         uint32_t words[4 * BITS + 1];

@@ -287,18 +287,21 @@ def run_gpu_arm(args) -> None:
     h2d = h_q.numel() * h_q.element_size() + h_k.numel() * h_k.element_size() + h_v.numel() * h_v.element_size()
     d2h = (gathered if world > 1 else out).numel() * out.element_size()
 
+    h_out1 = torch.empty(batch, hq, 1, HEAD_DIM, **pin)
+
     def e2e_step():
-        d_q.copy_(h_q, non_blocking=True)
-        d_k.copy_(h_k, non_blocking=True)
-        d_v.copy_(h_v, non_blocking=True)
-        store.pack(d_k, d_v)
-        store.decode_attn(d_q, splits=splits, out=out)
-        if world > 1:
+        if world == 1:
+            # the library's host-buffer entry point: H2D of q / k / v, append, attend, D2H of the output
+            store.decode_step_host(h_q, h_k, h_v, h_out1)
+        else:
+            d_q.copy_(h_q, non_blocking=True)
+            d_k.copy_(h_k, non_blocking=True)
+            d_v.copy_(h_v, non_blocking=True)
+            store.pack(d_k, d_v)
+            store.decode_attn(d_q, splits=splits, out=out)
             dist.all_gather_into_tensor(gathered, out)
             h_out.view(batch, world, hq, HEAD_DIM).copy_(gathered.view(world, batch, hq, HEAD_DIM).transpose(0, 1),
                                                           non_blocking=True)
-        else:
-            h_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the host needs the result before the next token
 
     e2e_steps = 0 if args.skip_e2e else steps

@@ -135,6 +135,20 @@ int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_he
                        const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
                        void *workspace, size_t workspace_bytes, void *out, tq_stream stream);
 
+/* One whole decode step for callers whose tensors live in HOST memory (pinned for the copies
+ * to be asynchronous): copy the query and the new token's key / value to the device, append
+ * the token at position `pos` of every cache row, attend over pos + 1 tokens, copy the
+ * output back.  Replaces, per layer and step, the reference's PackedMSELayer.update +
+ * turboquant_attention_forward (src/turboquant/runtime/packed_qmse_cache.py:600-679,
+ * src/turboquant/runtime/attention.py:28-72).  q_host / out_host: [batch, q_heads, 128];
+ * k_host / v_host: [batch, kv_heads, 128]; all contiguous, of `dtype`.  The work is queued on
+ * `stream`; out_host is valid once the stream has been synchronised. */
+size_t tq_decode_step_workspace_bytes(int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t n_splits);
+int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const void *k_host, const void *v_host,
+                            int32_t dtype, int32_t q_heads, const tq_cache_desc *cache, int32_t pos,
+                            int32_t n_splits, void *workspace, size_t workspace_bytes, void *out_host,
+                            tq_stream stream);
+
 /* Dequantise tokens [pos0, pos0 + n_tokens) of the keys (which = 0) or values (which = 1)
  * into a dense [batch, kv_heads, n_tokens, 128] tensor of dtype out->dtype. */
 int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,

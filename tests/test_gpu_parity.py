@@ -257,3 +257,27 @@ def test_argument_errors(setup_golden):
         store.decode_attn(torch.zeros(1, 18, 1, 128, device="cuda"))
     with pytest.raises(NotImplementedError):
         make_codec(5, False, setup_golden)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_host_buffer_decode_step_matches_device_calls(setup_golden, dtype):
+    """tq_decode_step_host (host tensors in, host tensor out) == append + decode on device tensors."""
+    from tq_local_b200.runtime.packed_store import PackedStore
+
+    codec = make_codec(4, True, setup_golden)
+    k, v, q = O.synth_kvq(2, 8, 2, 130, 128, seed=77, dtype=dtype)
+    a = PackedStore(codec, 2, 2, capacity=160)
+    b = PackedStore(codec, 2, 2, capacity=160)
+    a.pack(k[:, :, :128].cuda(), v[:, :, :128].cuda())
+    b.pack(k[:, :, :128].cuda(), v[:, :, :128].cuda())
+    for t in (128, 129):
+        kn, vn = k[:, :, t:t + 1].contiguous(), v[:, :, t:t + 1].contiguous()
+        out_h = torch.empty(2, 8, 1, 128, dtype=dtype).pin_memory()
+        a.decode_step_host(q.contiguous().pin_memory(), kn.pin_memory(), vn.pin_memory(), out_h)
+        b.pack(kn.cuda(), vn.cuda())
+        want = b.decode_attn(q.cuda())
+        torch.cuda.synchronize()
+        assert a.length == b.length == t + 1
+        assert torch.equal(out_h, want.cpu())
+    for x, y in zip(a.streams(), b.streams()):
+        assert torch.equal(x[:, :, :130], y[:, :, :130])

@@ -245,6 +245,44 @@ extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, i
                                 workspace, out, (cudaStream_t)stream);
 }
 
+extern "C" size_t tq_decode_step_workspace_bytes(int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t n_splits) {
+    const size_t ws = tq_decode_workspace_bytes(batch, q_heads, n_splits);
+    if (!ws || kv_heads <= 0) return 0;
+    // device staging: q and out (batch x q_heads x 128), k and v (batch x kv_heads x 128), fp32-sized
+    const size_t staging = ((size_t)batch * (2 * (size_t)q_heads + 2 * (size_t)kv_heads) * TQ_D * 4 + 255) / 256 * 256;
+    return ws + staging;
+}
+
+extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const void *k_host, const void *v_host,
+                                       int32_t dtype, int32_t q_heads, const tq_cache_desc *cache, int32_t pos,
+                                       int32_t n_splits, void *workspace, size_t workspace_bytes, void *out_host,
+                                       tq_stream stream) {
+    if (!ctx || !q_host || !k_host || !v_host || !out_host || !workspace || !cache) return TQ_ERR_ARG;
+    if (dtype < 0 || dtype > 2 || pos < 0 || pos >= cache->capacity) return TQ_ERR_ARG;
+    if (workspace_bytes < tq_decode_step_workspace_bytes(cache->batch, q_heads, cache->kv_heads, n_splits))
+        return TQ_ERR_WORKSPACE;
+    const size_t es = dtype == TQ_DTYPE_F32 ? 4 : 2;
+    const size_t q_bytes = (size_t)cache->batch * q_heads * TQ_D * es;
+    const size_t kv_bytes = (size_t)cache->batch * cache->kv_heads * TQ_D * es;
+    const size_t ws = tq_decode_workspace_bytes(cache->batch, q_heads, n_splits);
+    uint8_t *stage = (uint8_t *)workspace + ws;
+    const size_t q_slot = (size_t)cache->batch * q_heads * TQ_D * 4, kv_slot = (size_t)cache->batch * cache->kv_heads * TQ_D * 4;
+    void *d_q = stage, *d_out = stage + q_slot, *d_k = stage + 2 * q_slot, *d_v = stage + 2 * q_slot + kv_slot;
+    cudaStream_t s = (cudaStream_t)stream;
+    TQ_CUDA_CHECK(cudaMemcpyAsync(d_q, q_host, q_bytes, cudaMemcpyHostToDevice, s));
+    TQ_CUDA_CHECK(cudaMemcpyAsync(d_k, k_host, kv_bytes, cudaMemcpyHostToDevice, s));
+    TQ_CUDA_CHECK(cudaMemcpyAsync(d_v, v_host, kv_bytes, cudaMemcpyHostToDevice, s));
+    tq_dense_desc kd = {d_k, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
+    tq_dense_desc vd = {d_v, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
+    int32_t rc = tq_pack(ctx, &kd, &vd, 1, cache, pos, stream);
+    if (rc) return rc;
+    rc = tq_decode_attn(ctx, d_q, dtype, q_heads, cache, pos + 1, nullptr, nullptr, 0, n_splits, workspace, ws, d_out,
+                        stream);
+    if (rc) return rc;
+    TQ_CUDA_CHECK(cudaMemcpyAsync(out_host, d_out, q_bytes, cudaMemcpyDeviceToHost, s));
+    return TQ_OK;
+}
+
 extern "C" int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,
                               int32_t n_tokens, const tq_dense_desc *out, tq_stream stream) {
     if (!ctx || !out || !out->data) return TQ_ERR_ARG;

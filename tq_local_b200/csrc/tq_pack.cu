@@ -172,6 +172,84 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) tq_pack_rows_kernel(PackA
     }
 }
 
+// Latency-optimised encoder for a handful of vectors (the per-step append of decoded tokens):
+// one 512-thread block per vector.  Thread (j, dq) accumulates rows [32 dq, 32 dq + 32) of a
+// mat-vec for output column j, so each 128 x 128 mat-vec is 32 dependent steps deep instead
+// of 128, and the three chained mat-vecs of a Q_prod key finish in a few microseconds.
+template <typename T, bool QJL>
+__global__ void __launch_bounds__(4 * TQ_D) tq_pack_small_kernel(PackArgs a) {
+    __shared__ float s_x[TQ_D], s_u[TQ_D], s_part[4][TQ_D], s_red[4];
+    __shared__ uint8_t s_code[TQ_D];
+    __shared__ float s_bnd[16], s_cen[16];
+    const int tid = threadIdx.x, j = tid & (TQ_D - 1), dq = tid >> 7, lane = tid & 31;
+    const int64_t n_vec = (int64_t)a.B * a.H * a.S;
+    const int64_t item = blockIdx.x;
+    const int kind = a.first_kind + (item >= n_vec ? 1 : 0);
+    const int64_t vid = item >= n_vec ? item - n_vec : item;
+    const int t = (int)(vid % a.S);
+    const int h = (int)((vid / a.S) % a.H);
+    const int b = (int)(vid / ((int64_t)a.S * a.H));
+    const T *src = (const T *)a.x[kind] + b * a.sb[kind] + h * a.sh[kind] + (int64_t)t * a.st[kind];
+    const int64_t row = b * a.cache_sb + h * a.cache_sh + a.pos0 + t;
+    const int bits = a.bits[kind];
+    if (tid < 16) s_bnd[tid] = a.bounds[kind][tid], s_cen[tid] = a.centers_k[tid];
+
+    auto block_norm = [&](float v) {  // sqrt of the sum of v*v over the 128 threads with dq == 0
+        float ss = dq == 0 ? v * v : 0.f;
+        ss = tq_warp_sum(ss);
+        if (dq == 0 && lane == 0) s_red[j >> 5] = ss;
+        __syncthreads();
+        const float tot = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
+        __syncthreads();
+        return sqrtf(tot);
+    };
+    // out[j] = sum_d vec[d] * m[d][j], every thread gets the result for its column j
+    auto matvec = [&](const float *vec, const float *m) {
+        float acc = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+            const int d = 32 * dq + i;
+            acc = fmaf(vec[d], __ldg(m + d * TQ_D + j), acc);
+        }
+        s_part[dq][j] = acc;
+        __syncthreads();
+        const float r = (s_part[0][j] + s_part[1][j]) + (s_part[2][j] + s_part[3][j]);
+        __syncthreads();
+        return r;
+    };
+
+    const float x = tq_to_float<T>(src[j]);
+    const float nrm = block_norm(x);
+    const float safe = nrm > 0.0f ? nrm : 1.0f;
+    if (dq == 0) s_x[j] = x, s_u[j] = x / safe;
+    __syncthreads();
+    const float z = matvec(s_u, a.rot_t[kind]);
+    int idx = 0;
+#pragma unroll
+    for (int e = 0; e < 15; ++e) idx += (s_bnd[e] < z) ? 1 : 0;
+    if (dq == 0) s_code[j] = (uint8_t)idx;
+    const uint16_t nh = tq_float_to_half_bits(safe);
+    if (tid == 0) a.norms[kind][row] = nh;
+    __syncthreads();
+    if (tid < 4 * bits) ((uint32_t *)(a.codes[kind] + row * (int64_t)(16 * bits)))[tid] = assemble_word(s_code, tid, bits);
+
+    if (QJL && kind == 0) {
+        __syncthreads();
+        if (dq == 0) s_u[j] = s_cen[idx];
+        __syncthreads();
+        const float rec = matvec(s_u, a.rot_k);  // sum_j c[j] * R_k[j][d], d = this thread's column
+        const float res = s_x[j] - tq_round_through<T>(rec * tq_half_bits_to_float(nh));
+        const float rn = block_norm(res);
+        const float rsafe = rn > 0.0f ? rn : 1.0f;
+        if (dq == 0) s_u[j] = res / rsafe;
+        __syncthreads();
+        const float pr = matvec(s_u, a.qjl_t);
+        const uint32_t m = __ballot_sync(0xffffffffu, pr >= 0.0f);
+        if (dq == 0 && lane == 0) ((uint32_t *)(a.signs + row * 16))[j >> 5] = m;
+        if (tid == 0) a.rnorms[row] = tq_float_to_half_bits(rsafe);
+    }
+}
+
 struct DequantArgs {
     const uint8_t *codes;
     const uint16_t *norms;
@@ -339,6 +417,22 @@ int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc 
         if (a.n_kinds == 1 && tq_launch_pack_tc(ctx, k, 0, n_tokens, cache, pos0, stream) == TQ_OK) return TQ_OK;
     }
     const int64_t items = a.n_kinds * n_vec;
+    if (n_vec < 1024) {  // appends: one block per vector
+#define TQ_LAUNCH_SMALL(T)                                                                   \
+    do {                                                                                     \
+        if (ctx->use_qjl)                                                                    \
+            tq_pack_small_kernel<T, true><<<(unsigned)items, 4 * TQ_D, 0, stream>>>(a);      \
+        else                                                                                 \
+            tq_pack_small_kernel<T, false><<<(unsigned)items, 4 * TQ_D, 0, stream>>>(a);     \
+    } while (0)
+        if (k->dtype == TQ_DTYPE_F32) TQ_LAUNCH_SMALL(float);
+        else if (k->dtype == TQ_DTYPE_F16) TQ_LAUNCH_SMALL(__half);
+        else TQ_LAUNCH_SMALL(__nv_bfloat16);
+#undef TQ_LAUNCH_SMALL
+        tq_prof_count(ctx, 1);
+        TQ_CUDA_CHECK(cudaGetLastError());
+        return TQ_OK;
+    }
     const int grid = grid_for(items, ctx->sm_count);
     const int threads = kWarpsPerBlock * 32;
 #define TQ_LAUNCH_PACK(T)                                                          \

@@ -144,6 +144,31 @@ class PackedStore:
                       "tq_decode_attn")
         return out
 
+    def decode_step_host(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, out: torch.Tensor,
+                         splits: int | None = None) -> torch.Tensor:
+        """One decode step with HOST tensors (pinned memory keeps the copies asynchronous): append
+        ``k_new`` / ``v_new`` [B, Hkv, 1, 128], attend with ``q`` [B, Hq, 1, 128], write ``out``
+        [B, Hq, 1, 128] on the host.  Queued on the current stream; synchronise it before reading
+        ``out``."""
+        for t in (q, k_new, v_new, out):
+            if t.device.type != "cpu" or not t.is_contiguous():
+                raise ValueError("decode_step_host takes contiguous host tensors")
+        b, hq = int(q.shape[0]), int(q.shape[1])
+        if b != self.batch or k_new.shape[1] != self.kv_heads or q.dtype != k_new.dtype or out.dtype != q.dtype:
+            raise ValueError("shape or dtype mismatch")
+        self.reserve(self.length + 1)
+        splits = self.suggest_splits(self.length + 1) if splits is None else int(splits)
+        need = int(ffi.lib().tq_decode_step_workspace_bytes(b, hq, self.kv_heads, splits))
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.codec.device)
+        with torch.cuda.device(self.codec.device):
+            ffi.check(ffi.lib().tq_decode_step_host(self.codec.handle, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+                                                    tq_dtype(q.dtype), hq, C.byref(self._desc), self.length, splits,
+                                                    self._workspace.data_ptr(), self._workspace.numel(),
+                                                    out.data_ptr(), self._stream_ptr()), "tq_decode_step_host")
+        self.length += 1
+        return out
+
     def dequant(self, which: str, lo: int = 0, hi: int | None = None,
                 dtype: torch.dtype = torch.float32) -> torch.Tensor:
         """Dequantise tokens [lo, hi) of ``which`` in {'keys', 'values'} -> [B, Hkv, hi-lo, 128]."""

@@ -46,6 +46,13 @@ def bytes_per_unit(bits: int, use_qjl: bool) -> int:
     return 16 * key_bits + 2 + (16 + 2 if use_qjl else 0) + 16 * bits + 2
 
 
+# DRAM bytes (read + write) per unit of the main decode kernel, from the ncu capture of the
+# batch-4 case summarised in profiles/decode_mma4_persistent_b4_ctx32768.md: 140.74 MB read +
+# 3.6 MB written for 1 048 576 units of 134 B.  Every packed byte is read once, so traffic
+# grows in proportion to the units of a launch.
+NCU_TRAFFIC_BYTES_PER_UNIT = (140.74e6 + 3.6e6) / 1048576
+
+
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -341,7 +348,9 @@ def run_gpu_arm(args) -> None:
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": (achieved / peak) if achieved else None, "peak_source": f"of {peak_src}",
                 "kernel": "tq_decode main kernel (streams the packed cache)",
-                "kernel_ms": main_ms / max(main_n, 1), "traffic": None,
+                "kernel_ms": main_ms / max(main_n, 1),
+                "traffic": NCU_TRAFFIC_BYTES_PER_UNIT * batch * hkv * n_ctx if w["bits"] == 4 else None,
+                "traffic_source": "ncu dram read+write of the batch-4 capture in profiles/, scaled by units",
             },
             "e2e": None if args.skip_e2e else {
                 "value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,

@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "tq_common.cuh"
+#include "tq_step_blocks.cuh"
 
 static thread_local char g_err[256] = "";
 
@@ -253,33 +254,64 @@ extern "C" size_t tq_decode_step_workspace_bytes(int32_t batch, int32_t q_heads,
     return ws + staging;
 }
 
+// Device-side address of a caller buffer the GPU can reach directly (page-locked host memory
+// mapped into the device's address space, managed or device memory), else nullptr.
+static void *device_view(const void *p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    if (at.type == cudaMemoryTypeUnregistered || !at.devicePointer) return nullptr;
+    return ((uintptr_t)at.devicePointer & 15) ? nullptr : at.devicePointer;
+}
+
 extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const void *k_host, const void *v_host,
                                        int32_t dtype, int32_t q_heads, const tq_cache_desc *cache, int32_t pos,
                                        int32_t n_splits, void *workspace, size_t workspace_bytes, void *out_host,
                                        tq_stream stream) {
     if (!ctx || !q_host || !k_host || !v_host || !out_host || !workspace || !cache) return TQ_ERR_ARG;
     if (dtype < 0 || dtype > 2 || pos < 0 || pos >= cache->capacity) return TQ_ERR_ARG;
+    if (cache->batch <= 0 || cache->kv_heads <= 0 || q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
     if (workspace_bytes < tq_decode_step_workspace_bytes(cache->batch, q_heads, cache->kv_heads, n_splits))
         return TQ_ERR_WORKSPACE;
     const size_t es = dtype == TQ_DTYPE_F32 ? 4 : 2;
     const size_t q_bytes = (size_t)cache->batch * q_heads * TQ_D * es;
     const size_t kv_bytes = (size_t)cache->batch * cache->kv_heads * TQ_D * es;
     const size_t ws = tq_decode_workspace_bytes(cache->batch, q_heads, n_splits);
-    uint8_t *stage = (uint8_t *)workspace + ws;
-    const size_t q_slot = (size_t)cache->batch * q_heads * TQ_D * 4, kv_slot = (size_t)cache->batch * cache->kv_heads * TQ_D * 4;
-    void *d_q = stage, *d_out = stage + q_slot, *d_k = stage + 2 * q_slot, *d_v = stage + 2 * q_slot + kv_slot;
     cudaStream_t s = (cudaStream_t)stream;
-    TQ_CUDA_CHECK(cudaMemcpyAsync(d_q, q_host, q_bytes, cudaMemcpyHostToDevice, s));
-    TQ_CUDA_CHECK(cudaMemcpyAsync(d_k, k_host, kv_bytes, cudaMemcpyHostToDevice, s));
-    TQ_CUDA_CHECK(cudaMemcpyAsync(d_v, v_host, kv_bytes, cudaMemcpyHostToDevice, s));
+    // Page-locked, device-mapped host buffers are read and written by the kernels themselves
+    // (no copy engine round trips); anything else is staged through the workspace.
+    void *d_q = device_view(q_host), *d_k = device_view(k_host), *d_v = device_view(v_host);
+    void *d_out = device_view(out_host);
+    const bool direct = d_q && d_k && d_v && d_out;
+    if (!direct) {
+        uint8_t *stage = (uint8_t *)workspace + ws;
+        const size_t q_slot = (size_t)cache->batch * q_heads * TQ_D * 4;
+        const size_t kv_slot = (size_t)cache->batch * cache->kv_heads * TQ_D * 4;
+        d_q = stage, d_out = stage + q_slot, d_k = stage + 2 * q_slot, d_v = stage + 2 * q_slot + kv_slot;
+        TQ_CUDA_CHECK(cudaMemcpyAsync(d_q, q_host, q_bytes, cudaMemcpyHostToDevice, s));
+        TQ_CUDA_CHECK(cudaMemcpyAsync(d_k, k_host, kv_bytes, cudaMemcpyHostToDevice, s));
+        TQ_CUDA_CHECK(cudaMemcpyAsync(d_v, v_host, kv_bytes, cudaMemcpyHostToDevice, s));
+    }
     tq_dense_desc kd = {d_k, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
     tq_dense_desc vd = {d_v, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
-    int32_t rc = tq_pack(ctx, &kd, &vd, 1, cache, pos, stream);
+    int32_t rc = check_cache(ctx, cache);
     if (rc) return rc;
+    TqPackArgs append;
+    if (dtype != TQ_DTYPE_F32 && q_heads / cache->kv_heads <= 4) {
+        // the tensor-core decode path encodes the new token in its own query-preparation launch
+        tq_fill_pack_args(ctx, &kd, &vd, 1, cache, pos, &append);
+        ctx->pending_append = &append;
+    } else {
+        rc = tq_pack(ctx, &kd, &vd, 1, cache, pos, stream);
+        if (rc) return rc;
+    }
     rc = tq_decode_attn(ctx, d_q, dtype, q_heads, cache, pos + 1, nullptr, nullptr, 0, n_splits, workspace, ws, d_out,
                         stream);
+    ctx->pending_append = nullptr;
     if (rc) return rc;
-    TQ_CUDA_CHECK(cudaMemcpyAsync(out_host, d_out, q_bytes, cudaMemcpyDeviceToHost, s));
+    if (!direct) TQ_CUDA_CHECK(cudaMemcpyAsync(out_host, d_out, q_bytes, cudaMemcpyDeviceToHost, s));
     return TQ_OK;
 }
 

@@ -39,6 +39,7 @@ struct tq_ctx {
     size_t base_bytes;
     struct tq_prof *prof;  // measurement hooks, see tq_profile_enable
     int *error_flag;       // device word, set by a kernel whose bounded wait ran out
+    const struct TqPackArgs *pending_append;  // set by the host-step entry point for the next decode launch
     int64_t splits_cache_key;  // last (rows, length bucket) asked of tq_decode_suggest_splits
     int splits_cache_val;
 };
@@ -58,6 +59,21 @@ void tq_set_cuda_error(cudaError_t e, const char *where);
             return TQ_ERR_CUDA;                     \
         }                                           \
     } while (0)
+
+// Kernel launch with the optional "programmatic stream serialization" attribute: the kernel may
+// start while the preceding kernel of the stream is still running and must call
+// griddepcontrol.wait before it touches anything that kernel writes.
+template <typename... KArgs, typename... Args>
+cudaError_t tq_launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             bool programmatic, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 template <typename T> __device__ __forceinline__ float tq_to_float(T x);
 template <> __device__ __forceinline__ float tq_to_float<float>(float x) { return x; }

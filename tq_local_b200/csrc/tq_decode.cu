@@ -283,98 +283,24 @@ __global__ void __launch_bounds__(TQ_D) tq_combine_kernel(CombineArgs a) {
     ((T *)a.out)[row * TQ_D + e] = tq_from_float<T>(out / fmaxf(L, 1e-8f));
 }
 
-// Query preparation for the G <= 4 tensor-core kernel: one block per (batch, KV head) row
-// rotates and projects all G query heads (each matrix element is read once for the G heads)
-// and emits, per head, the ready-made MMA B-fragment words of all eight (part, t) lane
-// variants: 16 words of the rotated query split in two f16 terms, 8 words of the projected
-// query as 16-bit fixed point in two s8 terms, the fixed-point scale and bias (26 words).
-// Row stride of the fragment area: TQ_FRAG_ROW_WORDS words per query head.
+// Query preparation for the G <= 4 tensor-core kernel (see tq_qprep_block): kv_rows blocks
+// rotate, another kv_rows blocks project when the keys carry a QJL sketch.  The blocks let the
+// decode kernel, launched as a programmatic dependent, start its own set-up at once.
 template <typename T>
-__global__ void __launch_bounds__(4 * TQ_D) tq_qprep_frag_kernel(const T *q, const float *rot_k_t, const float *qjl_t,
-                                                                uint32_t *frag, int G, int use_qjl) {
-    __shared__ float s_q[4][TQ_D], s_r[4][TQ_D], s_p[4][TQ_D];
-    __shared__ float s_part[4][2][4][TQ_D];  // [quarter of d][rot / proj][head][column]
-    __shared__ int s_x[4][TQ_D];
-    __shared__ float s_scale[4], s_bias[4];
-    const int64_t R = blockIdx.x;
-    const int tid = threadIdx.x, j = tid & (TQ_D - 1), dq = tid >> 7;
-    const int warp = tid >> 5, lane = tid & 31;
-    if (dq < G) s_q[dq][j] = tq_to_float<T>(q[(R * G + dq) * TQ_D + j]);
-    __syncthreads();
-    {   // thread (j, dq) covers rows d in [32 dq, 32 dq + 32) of both matrices for all heads
-        float r[4] = {0.f, 0.f, 0.f, 0.f}, p[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-        for (int i = 0; i < 32; ++i) {
-            const int d = 32 * dq + i;
-            const float rk = __ldg(rot_k_t + d * TQ_D + j);
-            const float sk = use_qjl ? __ldg(qjl_t + d * TQ_D + j) : 0.f;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const float qv = g < G ? s_q[g][d] : 0.f;
-                r[g] = fmaf(qv, rk, r[g]);
-                p[g] = fmaf(qv, sk, p[g]);
-            }
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) s_part[dq][0][g][j] = r[g], s_part[dq][1][g][j] = p[g];
-    }
-    __syncthreads();
-    {   // thread (j, dq) finishes head dq
-        const int g = dq;
-        s_r[g][j] = (s_part[0][0][g][j] + s_part[1][0][g][j]) + (s_part[2][0][g][j] + s_part[3][0][g][j]);
-        s_p[g][j] = (s_part[0][1][g][j] + s_part[1][1][g][j]) + (s_part[2][1][g][j] + s_part[3][1][g][j]);
-    }
-    __syncthreads();
-    if (warp < G) {  // warp w quantises the projected query of head w to 16-bit fixed point
-        float amax = 0.f;
-        for (int i = lane; i < TQ_D; i += 32) amax = fmaxf(amax, fabsf(s_p[warp][i]));
-        amax = tq_warp_max(amax);
-        const float inv = amax > 0.f ? 32000.0f / amax : 0.f;
-        int isum = 0;
-        for (int i = lane; i < TQ_D; i += 32) {
-            const int x = __float2int_rn(s_p[warp][i] * inv);
-            s_x[warp][i] = x;
-            isum += x;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
-        if (lane == 0) {
-            // <qp, sign> = scale * (2 * sum_{bit set} x - sum x); the MMA yields -(sum over set bits)
-            const float scale = amax > 0.f ? amax / 32000.0f : 0.f;
-            s_scale[warp] = -2.0f * scale;
-            s_bias[warp] = -scale * (float)isum;
-        }
-    }
-    __syncthreads();
-    // one thread per output word: G heads x 8 lane variants x 26 words
-    for (int w = tid; w < G * 8 * 26; w += blockDim.x) {
-        const int variant = w / 26, k = w % 26;
-        const int hcol = variant >> 3, part = (variant >> 2) & 1, t = variant & 3;
-        uint32_t word;
-        if (k < 16) {  // rotated query, f16 hi / lo terms: dims 32t + 4*(k/2) + 2*(k%2) + {0, 1}
-            const int d0 = 32 * t + 4 * (k >> 1) + 2 * (k & 1);
-            float x[2];
-            for (int i = 0; i < 2; ++i) {
-                const float v = s_r[hcol][d0 + i];
-                const float hi = __half2float(__float2half_rn(v));
-                x[i] = part ? (v - hi) : hi;
-            }
-            const __half2 hh = __floats2half2_rn(x[0], x[1]);
-            word = *reinterpret_cast<const uint32_t *>(&hh);
-        } else if (k < 24) {  // projected query, s8 hi / lo terms behind sign bits (7 - 2n - rr) + 8j
-            const int n = (k - 16) >> 1, rr = (k - 16) & 1;
-            word = 0;
-            for (int jj = 0; jj < 4; ++jj) {
-                const int x16 = use_qjl ? s_x[hcol][32 * t + (7 - 2 * n - rr) + 8 * jj] : 0;
-                const int hi8 = (x16 + 128) >> 8;
-                const int lo8 = x16 - (hi8 << 8);
-                word |= (uint32_t)((part ? lo8 : hi8) & 0xff) << (8 * jj);
-            }
-        } else {
-            word = __float_as_uint(use_qjl ? (k == 24 ? s_scale[hcol] : s_bias[hcol]) : 0.f);
-        }
-        frag[(R * G + hcol) * TQ_FRAG_ROW_WORDS + variant % 8 * 26 + k] = word;
-    }
+__global__ void __launch_bounds__(4 * TQ_D, 2) tq_qprep_frag_kernel(TqQprepArgs a) {
+    tq_launch_dependents();
+    tq_qprep_block<T>(a, blockIdx.x);
+}
+
+// The whole latency-bound front of a decode step in one launch: query preparation blocks
+// first, then one block per new key and value vector to append (tq_pack_small_block).
+template <typename T, bool QJL>
+__global__ void __launch_bounds__(4 * TQ_D, 2) tq_step_prologue_kernel(TqQprepArgs qa, TqPackArgs pa, int n_qprep) {
+    tq_launch_dependents();
+    if ((int)blockIdx.x < n_qprep)
+        tq_qprep_block<T>(qa, blockIdx.x);
+    else
+        tq_pack_small_block<T, QJL>(pa, (int64_t)blockIdx.x - n_qprep);
 }
 
 // Split combine for all G <= 4 heads of one (batch, KV head) row per block (no dense tail):
@@ -386,6 +312,9 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
     __shared__ float s_L[4];
     const int64_t R = blockIdx.x;
     const int tid = threadIdx.x, e = tid & (TQ_D - 1), dq = tid >> 7;
+    float rv[32];  // this thread's un-rotation elements, fetched while the decode kernel drains
+    tq_load_column(rv, a.rot_v, dq, e);
+    tq_grid_dependency_wait();
     int n_valid = a.n_splits;
     if (a.seg_chunk > 0) {
         const int64_t lo = R * (int64_t)a.seg_npad;
@@ -411,12 +340,11 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
     __syncthreads();
     {   // thread (e, dq) un-rotates rows d in [32 dq, 32 dq + 32) for all heads
         float out[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
+#pragma unroll
         for (int i = 0; i < 32; ++i) {
             const int d = 32 * dq + i;
-            const float rv = __ldg(a.rot_v + d * TQ_D + e);
 #pragma unroll
-            for (int g = 0; g < 4; ++g) out[g] = fmaf(s_o[g][d], rv, out[g]);
+            for (int g = 0; g < 4; ++g) out[g] = fmaf(s_o[g][d], rv[i], out[g]);
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) s_part[dq][g][e] = out[g];
@@ -451,6 +379,12 @@ static void configure_small_kernels() {
     prefer_max_shared(tq_combine_group_kernel<float>);
     prefer_max_shared(tq_combine_group_kernel<__half>);
     prefer_max_shared(tq_combine_group_kernel<__nv_bfloat16>);
+    prefer_max_shared(tq_step_prologue_kernel<float, true>);
+    prefer_max_shared(tq_step_prologue_kernel<float, false>);
+    prefer_max_shared(tq_step_prologue_kernel<__half, true>);
+    prefer_max_shared(tq_step_prologue_kernel<__half, false>);
+    prefer_max_shared(tq_step_prologue_kernel<__nv_bfloat16, true>);
+    prefer_max_shared(tq_step_prologue_kernel<__nv_bfloat16, false>);
 }
 
 int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
@@ -469,33 +403,41 @@ int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t row
     return TQ_OK;
 }
 
+template <typename T>
+static cudaError_t launch_prologue(tq_ctx *ctx, const TqQprepArgs &qa, const TqPackArgs *append, cudaStream_t stream) {
+    const int n_qprep = (int)qa.kv_rows * (qa.use_qjl ? 2 : 1);
+    if (!append) return tq_launch_kernel(tq_qprep_frag_kernel<T>, dim3(n_qprep), dim3(4 * TQ_D), 0, stream, false, qa);
+    const int n_pack = append->n_kinds * append->B * append->H * append->S;
+    if (ctx->use_qjl)
+        return tq_launch_kernel(tq_step_prologue_kernel<T, true>, dim3(n_qprep + n_pack), dim3(4 * TQ_D), 0, stream,
+                                false, qa, *append, n_qprep);
+    return tq_launch_kernel(tq_step_prologue_kernel<T, false>, dim3(n_qprep + n_pack), dim3(4 * TQ_D), 0, stream, false,
+                            qa, *append, n_qprep);
+}
+
 int32_t tq_launch_qprep_frag(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t kv_rows, int G, uint32_t *frag,
-                             cudaStream_t stream) {
+                             const TqPackArgs *append, cudaStream_t stream) {
     configure_small_kernels();
     if (G > 4) return TQ_ERR_UNSUPPORTED;
-    if (q_dtype == TQ_DTYPE_F32)
-        tq_qprep_frag_kernel<float><<<(unsigned)kv_rows, 4 * TQ_D, 0, stream>>>((const float *)q, ctx->rot_k_t, ctx->qjl_t,
-                                                                            frag, G, ctx->use_qjl);
-    else if (q_dtype == TQ_DTYPE_F16)
-        tq_qprep_frag_kernel<__half><<<(unsigned)kv_rows, 4 * TQ_D, 0, stream>>>((const __half *)q, ctx->rot_k_t,
-                                                                             ctx->qjl_t, frag, G, ctx->use_qjl);
-    else
-        tq_qprep_frag_kernel<__nv_bfloat16><<<(unsigned)kv_rows, 4 * TQ_D, 0, stream>>>(
-            (const __nv_bfloat16 *)q, ctx->rot_k_t, ctx->qjl_t, frag, G, ctx->use_qjl);
-    TQ_CUDA_CHECK(cudaGetLastError());
+    TqQprepArgs qa;
+    qa.q = q, qa.rot_k_t = ctx->rot_k_t, qa.qjl_t = ctx->qjl_t, qa.frag = frag;
+    qa.G = G, qa.use_qjl = ctx->use_qjl, qa.kv_rows = kv_rows;
+    cudaError_t e;
+    if (q_dtype == TQ_DTYPE_F32) e = launch_prologue<float>(ctx, qa, append, stream);
+    else if (q_dtype == TQ_DTYPE_F16) e = launch_prologue<__half>(ctx, qa, append, stream);
+    else e = launch_prologue<__nv_bfloat16>(ctx, qa, append, stream);
+    TQ_CUDA_CHECK(e);
     return TQ_OK;
 }
 
-int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, cudaStream_t stream) {
+int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, cudaStream_t stream, bool programmatic) {
     if (a.n_tail == 0 && a.G <= 4) {  // grouped variant: one block per KV row
-        const unsigned kv_rows = (unsigned)(rows / a.G);
-        if (q_dtype == TQ_DTYPE_F32)
-            tq_combine_group_kernel<float><<<kv_rows, 4 * TQ_D, 0, stream>>>(a);
-        else if (q_dtype == TQ_DTYPE_F16)
-            tq_combine_group_kernel<__half><<<kv_rows, 4 * TQ_D, 0, stream>>>(a);
-        else
-            tq_combine_group_kernel<__nv_bfloat16><<<kv_rows, 4 * TQ_D, 0, stream>>>(a);
-        TQ_CUDA_CHECK(cudaGetLastError());
+        const dim3 grid((unsigned)(rows / a.G)), block(4 * TQ_D);
+        cudaError_t e;
+        if (q_dtype == TQ_DTYPE_F32) e = tq_launch_kernel(tq_combine_group_kernel<float>, grid, block, 0, stream, programmatic, a);
+        else if (q_dtype == TQ_DTYPE_F16) e = tq_launch_kernel(tq_combine_group_kernel<__half>, grid, block, 0, stream, programmatic, a);
+        else e = tq_launch_kernel(tq_combine_group_kernel<__nv_bfloat16>, grid, block, 0, stream, programmatic, a);
+        TQ_CUDA_CHECK(e);
         return TQ_OK;
     }
     const size_t dyn = (size_t)a.n_tail * sizeof(float);

@@ -37,6 +37,7 @@
 #include "tq_common.cuh"
 #include "tq_decode_shared.cuh"
 #include "tq_mma_utils.cuh"
+#include "tq_step_blocks.cuh"
 
 namespace {
 
@@ -58,6 +59,7 @@ struct Mma4Args {
     int rows;    // batch * kv_heads
     int n_pad;   // N rounded up to the CTA step: rows are laid end to end in units of n_pad tokens
     int chunk;   // tokens of that flattened (row, token) space per CTA
+    int stable_len;  // tokens [0, stable_len) of every row were written before the preceding kernel began
     const uint32_t *frag;  // per query head: TQ_FRAG_ROW_WORDS words, see tq_qprep_frag_kernel
     float *part_m, *part_l, *part_acc;
     const float *centers_k, *centers_v;
@@ -209,6 +211,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     const uint32_t lane_k = kTableAddr + lane * 4;        // key copies: bytes [0, 128) of every slot
     const uint32_t lane_v = kTableAddr + 128 + lane * 4;  // value copies: bytes [128, 256)
     bool timed_out = false;
+    bool first_segment = true;
 
     // ---- one segment per row this CTA touches
     for (int64_t flat = flat_begin; flat < flat_end;) {
@@ -243,10 +246,26 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
             tma_load_1d(dst + L::kRN, a.k_rnorms + r, n * 2, bar);
         }
     };
+    // The kernel is launched as a programmatic dependent of the query-preparation kernel, which
+    // may also be appending this step's token: ring stages that hold only older tokens are
+    // requested before the dependency wait, everything else after it.
+    const int n_first = min(n_iter, kStages);
+    uint32_t deferred = 0;
     if (lane == 0) {
         // the ring area was last touched through ordinary loads/stores (previous segment's merge)
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        for (int it = 0; it < min(n_iter, kStages); ++it) issue(it);
+        for (int it = 0; it < n_first; ++it) {
+            if (first_segment && my_first + it * kWarps * kStageTok + kStageTok > a.stable_len)
+                deferred |= 1u << it;
+            else
+                issue(it);
+        }
+    }
+    if (first_segment) {
+        tq_grid_dependency_wait();
+        for (int it = 0; it < n_first; ++it)
+            if (deferred >> it & 1) issue(it);
+        first_segment = false;
     }
 
     // ---- B fragments: column g = (head g/2, part g%2)
@@ -450,8 +469,8 @@ template <int KB, int VB, bool QJL> cudaError_t launch_mma4(const Mma4Args &a, d
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    tq_decode_mma4_kernel<KB, VB, QJL><<<grid, kWarps * 32, smem, stream>>>(a);
-    return cudaGetLastError();
+    return tq_launch_kernel(tq_decode_mma4_kernel<KB, VB, QJL>, grid, dim3(kWarps * 32), smem, stream,
+                            /*programmatic=*/true, a);
 }
 
 }  // namespace
@@ -467,7 +486,9 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     // the fragment area overlays the rotated / projected query rows of the workspace
     uint32_t *frag = reinterpret_cast<uint32_t *>(w.qrot);
     const int groups = q_heads / cache->kv_heads;
-    int rc = tq_launch_qprep_frag(ctx, q, q_dtype, rows / groups, groups, frag, stream);
+    const TqPackArgs *append = ctx->pending_append;  // this step's new token, encoded by the same launch
+    ctx->pending_append = nullptr;
+    int rc = tq_launch_qprep_frag(ctx, q, q_dtype, rows / groups, groups, frag, append, stream);
     if (rc) return rc;
 
     Mma4Args a;
@@ -491,6 +512,7 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
         if (chunk < floor_chunk) chunk = floor_chunk;
     }
     a.chunk = (int)chunk;
+    a.stable_len = append ? append->pos0 : seq_len;
     a.frag = frag;
     a.part_m = w.part_m, a.part_l = w.part_l, a.part_acc = w.part_acc;
     a.centers_k = ctx->centers_k, a.centers_v = ctx->centers_v;
@@ -528,5 +550,5 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     } else {
         c.tk_sb = c.tk_sh = c.tk_st = c.tv_sb = c.tv_sh = c.tv_st = 0;
     }
-    return tq_launch_combine(c, q_dtype, rows, stream);
+    return tq_launch_combine(c, q_dtype, rows, stream, /*programmatic=*/true);
 }

@@ -2,6 +2,7 @@
 #pragma once
 
 #include "tq_common.cuh"
+#include "tq_step_blocks.cuh"
 
 struct CombineArgs {
     const float *part_m, *part_l, *part_acc;
@@ -26,13 +27,14 @@ struct DecodeWorkspace {
     float *part_acc;  // [rows][splits][128]
 };
 
-// Words per query head in the fragment area written by tq_qprep_frag_kernel (8 lane variants of
-// 26 words, padded to the size of the rotated + projected query rows it overlays).
-#define TQ_FRAG_ROW_WORDS (2 * TQ_D + 8)
-
 DecodeWorkspace tq_carve_workspace(void *workspace, int64_t rows, int n_splits);
 int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
                         cudaStream_t stream);
+// Query preparation for the G <= 4 kernel; with `append` the same launch also encodes and
+// appends the step's new key / value vectors.
 int32_t tq_launch_qprep_frag(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t kv_rows, int G, uint32_t *frag,
-                             cudaStream_t stream);
-int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, cudaStream_t stream);
+                             const TqPackArgs *append, cudaStream_t stream);
+// `programmatic`: launch as a programmatic dependent of the preceding kernel (honoured by the
+// grouped variant, which waits for that kernel before it reads the partials).
+int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, cudaStream_t stream,
+                          bool programmatic = false);

@@ -6,42 +6,13 @@
 // reconstruction before the QJL residual.  It serves the O(1) append of decoded
 // tokens and small prefills; large prefills go to the tensor-core kernel.
 #include "tq_common.cuh"
+#include "tq_step_blocks.cuh"
 
 namespace {
 
 constexpr int kWarpsPerBlock = 8;
 
-struct PackArgs {
-    const void *x[2];  // K, V
-    int64_t sb[2], sh[2], st[2];
-    int B, H, S;
-    int pos0;
-    int bits[2];  // key_bits, value bits
-    uint8_t *codes[2];
-    uint16_t *norms[2];
-    uint8_t *signs;
-    uint16_t *rnorms;
-    int64_t cache_sb, cache_sh;
-    const float *rot_t[2];   // R^T[d][j] for the rotation
-    const float *rot_k;      // R_k[j][d] for the reconstruction
-    const float *qjl_t;      // S^T[d][i]
-    const float *centers_k;
-    const float *bounds[2];
-    int first_kind, n_kinds;  // which of {keys, values} this launch encodes
-};
-
-// Assemble 32-bit word `w` of the LSB-first bitstream from one-code-per-byte storage.
-__device__ __forceinline__ uint32_t assemble_word(const uint8_t *codes, int w, int bits) {
-    uint32_t word = 0;
-    const int lo = 32 * w;
-    int j = lo / bits;
-    for (; j < TQ_D && j * bits < lo + 32; ++j) {
-        const int sh = j * bits - lo;
-        const uint32_t c = codes[j];
-        word |= sh >= 0 ? (c << sh) : (c >> (-sh));
-    }
-    return word;
-}
+using PackArgs = TqPackArgs;
 
 template <typename T, bool QJL>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) tq_pack_rows_kernel(PackArgs a) {
@@ -112,7 +83,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) tq_pack_rows_kernel(PackA
         __syncwarp();
         if (lane < 4 * bits) {
             uint32_t *dst = (uint32_t *)(a.codes[kind] + row * (int64_t)(16 * bits));
-            dst[lane] = assemble_word(code, lane, bits);
+            dst[lane] = tq_assemble_word(code, lane, bits);
         }
 
         if (QJL && kind == 0) {
@@ -173,81 +144,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) tq_pack_rows_kernel(PackA
 }
 
 // Latency-optimised encoder for a handful of vectors (the per-step append of decoded tokens):
-// one 512-thread block per vector.  Thread (j, dq) accumulates rows [32 dq, 32 dq + 32) of a
-// mat-vec for output column j, so each 128 x 128 mat-vec is 32 dependent steps deep instead
-// of 128, and the three chained mat-vecs of a Q_prod key finish in a few microseconds.
+// one 512-thread block per vector, see tq_pack_small_block.
 template <typename T, bool QJL>
-__global__ void __launch_bounds__(4 * TQ_D) tq_pack_small_kernel(PackArgs a) {
-    __shared__ float s_x[TQ_D], s_u[TQ_D], s_part[4][TQ_D], s_red[4];
-    __shared__ uint8_t s_code[TQ_D];
-    __shared__ float s_bnd[16], s_cen[16];
-    const int tid = threadIdx.x, j = tid & (TQ_D - 1), dq = tid >> 7, lane = tid & 31;
-    const int64_t n_vec = (int64_t)a.B * a.H * a.S;
-    const int64_t item = blockIdx.x;
-    const int kind = a.first_kind + (item >= n_vec ? 1 : 0);
-    const int64_t vid = item >= n_vec ? item - n_vec : item;
-    const int t = (int)(vid % a.S);
-    const int h = (int)((vid / a.S) % a.H);
-    const int b = (int)(vid / ((int64_t)a.S * a.H));
-    const T *src = (const T *)a.x[kind] + b * a.sb[kind] + h * a.sh[kind] + (int64_t)t * a.st[kind];
-    const int64_t row = b * a.cache_sb + h * a.cache_sh + a.pos0 + t;
-    const int bits = a.bits[kind];
-    if (tid < 16) s_bnd[tid] = a.bounds[kind][tid], s_cen[tid] = a.centers_k[tid];
-
-    auto block_norm = [&](float v) {  // sqrt of the sum of v*v over the 128 threads with dq == 0
-        float ss = dq == 0 ? v * v : 0.f;
-        ss = tq_warp_sum(ss);
-        if (dq == 0 && lane == 0) s_red[j >> 5] = ss;
-        __syncthreads();
-        const float tot = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
-        __syncthreads();
-        return sqrtf(tot);
-    };
-    // out[j] = sum_d vec[d] * m[d][j], every thread gets the result for its column j
-    auto matvec = [&](const float *vec, const float *m) {
-        float acc = 0.f;
-#pragma unroll 8
-        for (int i = 0; i < 32; ++i) {
-            const int d = 32 * dq + i;
-            acc = fmaf(vec[d], __ldg(m + d * TQ_D + j), acc);
-        }
-        s_part[dq][j] = acc;
-        __syncthreads();
-        const float r = (s_part[0][j] + s_part[1][j]) + (s_part[2][j] + s_part[3][j]);
-        __syncthreads();
-        return r;
-    };
-
-    const float x = tq_to_float<T>(src[j]);
-    const float nrm = block_norm(x);
-    const float safe = nrm > 0.0f ? nrm : 1.0f;
-    if (dq == 0) s_x[j] = x, s_u[j] = x / safe;
-    __syncthreads();
-    const float z = matvec(s_u, a.rot_t[kind]);
-    int idx = 0;
-#pragma unroll
-    for (int e = 0; e < 15; ++e) idx += (s_bnd[e] < z) ? 1 : 0;
-    if (dq == 0) s_code[j] = (uint8_t)idx;
-    const uint16_t nh = tq_float_to_half_bits(safe);
-    if (tid == 0) a.norms[kind][row] = nh;
-    __syncthreads();
-    if (tid < 4 * bits) ((uint32_t *)(a.codes[kind] + row * (int64_t)(16 * bits)))[tid] = assemble_word(s_code, tid, bits);
-
-    if (QJL && kind == 0) {
-        __syncthreads();
-        if (dq == 0) s_u[j] = s_cen[idx];
-        __syncthreads();
-        const float rec = matvec(s_u, a.rot_k);  // sum_j c[j] * R_k[j][d], d = this thread's column
-        const float res = s_x[j] - tq_round_through<T>(rec * tq_half_bits_to_float(nh));
-        const float rn = block_norm(res);
-        const float rsafe = rn > 0.0f ? rn : 1.0f;
-        if (dq == 0) s_u[j] = res / rsafe;
-        __syncthreads();
-        const float pr = matvec(s_u, a.qjl_t);
-        const uint32_t m = __ballot_sync(0xffffffffu, pr >= 0.0f);
-        if (dq == 0 && lane == 0) ((uint32_t *)(a.signs + row * 16))[j >> 5] = m;
-        if (tid == 0) a.rnorms[row] = tq_float_to_half_bits(rsafe);
-    }
+__global__ void __launch_bounds__(4 * TQ_D, 2) tq_pack_small_kernel(PackArgs a) {
+    tq_pack_small_block<T, QJL>(a, blockIdx.x);
 }
 
 struct DequantArgs {
@@ -381,9 +281,9 @@ int grid_for(int64_t items, int sm_count) {
 
 }  // namespace
 
-int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,
-                       const tq_cache_desc *cache, int32_t pos0, cudaStream_t stream) {
-    PackArgs a;
+void tq_fill_pack_args(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,
+                       const tq_cache_desc *cache, int32_t pos0, TqPackArgs *out) {
+    TqPackArgs &a = *out;
     a.x[0] = k->data;
     a.x[1] = v->data;
     a.sb[0] = k->stride_b, a.sh[0] = k->stride_h, a.st[0] = k->stride_t;
@@ -398,6 +298,13 @@ int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc 
     a.rot_k = ctx->rot_k, a.qjl_t = ctx->qjl_t;
     a.centers_k = ctx->centers_k;
     a.bounds[0] = ctx->bounds_k, a.bounds[1] = ctx->bounds_v;
+    a.first_kind = 0, a.n_kinds = 2;
+}
+
+int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,
+                       const tq_cache_desc *cache, int32_t pos0, cudaStream_t stream) {
+    PackArgs a;
+    tq_fill_pack_args(ctx, k, v, n_tokens, cache, pos0, &a);
     static bool configured = false;
     if (!configured) {  // same shared-memory carve-out as the decode kernels: no SM reconfiguration between them
         configured = true;

@@ -6,12 +6,13 @@
 // one partial (max, sum, acc) per row it touches.  Each CTA serves all G <= 4 query heads of
 // a row, so packed bytes are read from HBM once.
 //
-// Data movement: every warp runs its own ring of 32-token stages in shared
-// memory.  Lane 0 fills a stage with six TMA bulk copies (cp.async.bulk: key codes, QJL
-// signs, value codes and the three fp16 norm streams are each contiguous in HBM) that
-// complete on an mbarrier; the warp waits on it with a bounded spin.  No registers and no
-// load/store-unit issue slots are spent on global loads, and HBM latency is hidden by the
-// ring rather than by occupancy.
+// Data movement: every group of four warps runs its own ring of 128-token slots in shared
+// memory (32 tokens per warp).  One lane of the group fills a slot with six TMA bulk copies
+// (cp.async.bulk: key codes, QJL signs, value codes and the three fp16 norm streams are each
+// contiguous in HBM) that complete on a "full" mbarrier; every warp hands the slot back on an
+// "empty" mbarrier and the warps take turns to wait for it and request the refill.  All waits
+// are bounded spins.  No registers and no load/store-unit issue slots are spent on global
+// loads, and HBM latency is hidden by the ring rather than by occupancy.
 //
 // Math: the 8 columns of every MMA are (head, part) pairs, which gives each lane of a
 // quad its own head:
@@ -42,8 +43,11 @@
 namespace {
 
 constexpr int kWarps = 16;
-constexpr int kStageTok = 32;  // tokens per ring stage (two 16-token MMA tiles)
+constexpr int kStageTok = 32;  // tokens per warp per ring slot (two 16-token MMA tiles)
 constexpr int kStages = 2;
+constexpr int kGroupWarps = 4;  // warps that share a ring: one bulk copy per stream serves all of them
+constexpr int kGroups = kWarps / kGroupWarps;
+constexpr int kGroupTok = kGroupWarps * kStageTok;  // tokens per ring slot
 constexpr int kSlotWords = 64;  // table slot: 32 key words then 32 value words (256 B)
 constexpr uint32_t kSpinLimit = 1u << 22;  // mbarrier polls before a wait gives up
 
@@ -68,12 +72,12 @@ struct Mma4Args {
 
 template <int KB, int VB, bool QJL> struct StageLayout {
     static constexpr int kK = 0;
-    static constexpr int kV = kK + kStageTok * 16 * KB;
-    static constexpr int kS = kV + kStageTok * 16 * VB;
-    static constexpr int kKN = kS + (QJL ? kStageTok * 16 : 0);
-    static constexpr int kVN = kKN + kStageTok * 2;
-    static constexpr int kRN = kVN + kStageTok * 2;
-    static constexpr int kBytes = (kRN + (QJL ? kStageTok * 2 : 0) + 15) / 16 * 16;
+    static constexpr int kV = kK + kGroupTok * 16 * KB;
+    static constexpr int kS = kV + kGroupTok * 16 * VB;
+    static constexpr int kKN = kS + (QJL ? kGroupTok * 16 : 0);
+    static constexpr int kVN = kKN + kGroupTok * 2;
+    static constexpr int kRN = kVN + kGroupTok * 2;
+    static constexpr int kBytes = (kRN + (QJL ? kGroupTok * 2 : 0) + 127) / 128 * 128;
 };
 
 // ---- mbarrier / TMA bulk-copy wrappers (shared::cta addresses) ----
@@ -95,6 +99,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 // Bounded wait: returns false (and the caller flags an error) instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -156,14 +163,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     // Shared-memory map (absolute shared addresses): [dynamic base, 65536) the first rings,
     // [65536, 65536 + table) the centre-pair table, then the remaining rings and the mbarriers.
     const uint32_t dyn_base = smem_u32(smem);
-    constexpr int kRingBytes = kStages * L::kBytes;
-    const int rings_low = dyn_base <= kTableAddr ? min(kWarps, (int)((kTableAddr - dyn_base) / kRingBytes)) : 0;
+    constexpr int kSlots = kGroups * kStages;  // ring slots of the CTA, placed one by one around the table
+    constexpr int kMergeBytes = kWarps * 4 * (TQ_D + 2) * 4;
+    const int slots_low = dyn_base <= kTableAddr ? min(kSlots, (int)((kTableAddr - dyn_base) / L::kBytes)) : 0;
     const uint32_t high_base = kTableAddr + ((kTableBytes + 127) / 128) * 128;
-    const uint32_t bars_addr = high_base + (kWarps - rings_low) * kRingBytes;
+    const uint32_t bars_addr = high_base + (kSlots - slots_low) * L::kBytes;  // full[kSlots] then empty[kSlots]
     {
         uint32_t dyn_size;
         asm("mov.u32 %0, %%dynamic_smem_size;\n" : "=r"(dyn_size));
-        if (dyn_base > kTableAddr || bars_addr + kWarps * kStages * 8 > dyn_base + dyn_size) {
+        if (dyn_base > kTableAddr || bars_addr + 2 * kSlots * 8 > dyn_base + dyn_size ||
+            slots_low * L::kBytes < kMergeBytes) {
             if (threadIdx.x == 0) atomicExch(a.error_flag, 2);  // layout does not fit: refuse to run
             return;
         }
@@ -178,17 +187,20 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     const int64_t flat_begin = (int64_t)blockIdx.x * a.chunk;
     const int64_t flat_end = min(flat_begin + a.chunk, (int64_t)a.rows * a.n_pad);
 
-    // ---- ring set-up
-    const uint32_t ring_u32 = warp < rings_low ? dyn_base + warp * kRingBytes
-                                               : high_base + (warp - rings_low) * kRingBytes;
-    const uint8_t *ring = smem + (ring_u32 - dyn_base);
-    const uint32_t bar_u32 = bars_addr + warp * kStages * 8;
-    if (lane == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(bar_u32 + s * 8, 1);
+    // ---- ring set-up: group gq owns slots gq * kStages + s
+    const int gq = warp / kGroupWarps, wq = warp % kGroupWarps;
+    auto slot_u32 = [&](int st) -> uint32_t {
+        const int q = gq * kStages + st;
+        return q < slots_low ? dyn_base + q * L::kBytes : high_base + (q - slots_low) * L::kBytes;
+    };
+    const uint32_t full_u32 = bars_addr + gq * kStages * 8;
+    const uint32_t empty_u32 = bars_addr + (kSlots + gq * kStages) * 8;
+    if (wq == 0 && lane == 0) {
+        for (int st = 0; st < kStages; ++st) mbar_init(full_u32 + st * 8, 1), mbar_init(empty_u32 + st * 8, kGroupWarps);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
-    uint32_t ring_pos = 0;  // stages this warp has consumed since the kernel began
+    uint32_t ring_pos = 0;  // slots this group has consumed since the kernel began
 
     // ---- per-lane replicated f16x2 centre-pair tables (keys in the low half of each slot);
     // a warp fills one slot at a time, lane l writing words l and 32+l (no bank conflicts)
@@ -225,15 +237,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     const int64_t row0 = (int64_t)b * a.cache_sb + (int64_t)h * a.cache_sh;
     const int t_begin = seg_lo;
     const int t_end = min(a.N, seg_lo + seg_len);
-    const int my_first = t_begin + warp * kStageTok;
-    const int n_iter = my_first < t_end ? (t_end - my_first + kWarps * kStageTok - 1) / (kWarps * kStageTok) : 0;
+    const int grp_first = t_begin + gq * kGroupTok;
+    const int my_first = grp_first + wq * kStageTok;
+    constexpr int kCtaStep = kWarps * kStageTok;
+    const int n_iter = grp_first < t_end ? (t_end - grp_first + kCtaStep - 1) / kCtaStep : 0;
 
-    auto issue = [&](int it) {  // lane 0 only: fill the ring stage of local iteration `it`
-        const int base = my_first + it * kWarps * kStageTok;
-        int n = min(kStageTok, t_end - base);
+    auto issue = [&](int it) {  // one lane of the group: fill the ring slot of local iteration `it`
+        const int base = grp_first + it * kCtaStep;
+        int n = min(kGroupTok, t_end - base);
         n = (n + 7) & ~7;  // whole 16-byte pieces of the norm streams; rows stay inside the row's stride
         const int st = (ring_pos + it) % kStages;
-        const uint32_t dst = ring_u32 + st * L::kBytes, bar = bar_u32 + st * 8;
+        const uint32_t dst = slot_u32(st), bar = full_u32 + st * 8;
         const int64_t r = row0 + base;
         const uint32_t total = n * (16 * KB + 16 * VB + 4 + (QJL ? 18 : 0));
         mbar_expect_tx(bar, total);
@@ -249,13 +263,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     // The kernel is launched as a programmatic dependent of the query-preparation kernel, which
     // may also be appending this step's token: ring stages that hold only older tokens are
     // requested before the dependency wait, everything else after it.
+    // The first slots of a segment are requested by warp 0 of the group (the __syncthreads that
+    // ended the previous segment guarantees that the whole group is done with them).
     const int n_first = min(n_iter, kStages);
     uint32_t deferred = 0;
-    if (lane == 0) {
+    if (wq == 0 && lane == 0) {
         // the ring area was last touched through ordinary loads/stores (previous segment's merge)
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         for (int it = 0; it < n_first; ++it) {
-            if (first_segment && my_first + it * kWarps * kStageTok + kStageTok > a.stable_len)
+            if (first_segment && grp_first + it * kCtaStep + kGroupTok > a.stable_len)
                 deferred |= 1u << it;
             else
                 issue(it);
@@ -299,11 +315,20 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
     for (int it = 0; it < n_iter; ++it) {
-        const int base = my_first + it * kWarps * kStageTok;
+        const int base = my_first + it * kCtaStep;
         const int st = (ring_pos + it) % kStages;
-        const uint8_t *sp = ring + st * L::kBytes;
-        if (!mbar_wait(bar_u32 + st * 8, ((ring_pos + it) / kStages) & 1)) timed_out = true;
+        const uint32_t use_parity = ((ring_pos + it) / kStages) & 1;
+        const uint8_t *slot = smem + (slot_u32(st) - dyn_base);
+        if (base < t_end) {  // (a warp whose tokens all lie past the end only takes part in the hand-shake)
+        if (!mbar_wait(full_u32 + st * 8, use_parity)) timed_out = true;
         const bool tail = base + kStageTok > t_end;
+        // this warp's 32 tokens inside the slot
+        const uint8_t *spK = slot + L::kK + wq * kStageTok * 16 * KB;
+        const uint8_t *spV = slot + L::kV + wq * kStageTok * 16 * VB;
+        const uint8_t *spS = slot + L::kS + wq * kStageTok * 16;
+        const uint16_t *kn = reinterpret_cast<const uint16_t *>(slot + L::kKN) + wq * kStageTok;
+        const uint16_t *vn = reinterpret_cast<const uint16_t *>(slot + L::kVN) + wq * kStageTok;
+        const uint16_t *rn = reinterpret_cast<const uint16_t *>(slot + L::kRN) + wq * kStageTok;
 
         // ------------------------------------------------------------ logits
         float lg[2][2];
@@ -314,8 +339,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
             const int slotA = 16 * i + (g >> 1) + 4 * (g & 1), slotB = slotA + 8;
             uint32_t wa[KB + 1], wb[KB + 1];
             {
-                const uint32_t *pa = reinterpret_cast<const uint32_t *>(sp + L::kK + slotA * (16 * KB)) + KB * t;
-                const uint32_t *pb = reinterpret_cast<const uint32_t *>(sp + L::kK + slotB * (16 * KB)) + KB * t;
+                const uint32_t *pa = reinterpret_cast<const uint32_t *>(spK + slotA * (16 * KB)) + KB * t;
+                const uint32_t *pb = reinterpret_cast<const uint32_t *>(spK + slotB * (16 * KB)) + KB * t;
 #pragma unroll
                 for (int w = 0; w < KB; ++w) wa[w] = pa[w], wb[w] = pb[w];
                 wa[KB] = wb[KB] = 0;
@@ -331,12 +356,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                 const uint32_t a3 = lds_abs(slot_addr(wb, o1, lane_k));
                 mma_f16(d1, a0, a1, a2, a3, bq[s][0], bq[s][1]);
             }
-            const uint16_t *kn = reinterpret_cast<const uint16_t *>(sp + L::kKN);
             float lgA = tq_half_bits_to_float(kn[slotA]) * kA * (d1[0] + d1[1]);
             float lgB = tq_half_bits_to_float(kn[slotB]) * kA * (d1[2] + d1[3]);
             if (QJL) {
-                const uint32_t sa = reinterpret_cast<const uint32_t *>(sp + L::kS + slotA * 16)[t];
-                const uint32_t sb = reinterpret_cast<const uint32_t *>(sp + L::kS + slotB * 16)[t];
+                const uint32_t sa = reinterpret_cast<const uint32_t *>(spS + slotA * 16)[t];
+                const uint32_t sb = reinterpret_cast<const uint32_t *>(spS + slotB * 16)[t];
                 int d2[4] = {0, 0, 0, 0};
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
@@ -346,7 +370,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                     const uint32_t a3 = prmt(sb << (2 * n + 1), 0u, 0xBA98u);
                     mma_s8(d2, a0, a1, a2, a3, bp[n][0], bp[n][1]);
                 }
-                const uint16_t *rn = reinterpret_cast<const uint16_t *>(sp + L::kRN);
                 const float sA = fmaf((float)(d2[0] * 256 + d2[1]), sign_scale, sign_bias);
                 const float sB = fmaf((float)(d2[2] * 256 + d2[3]), sign_scale, sign_bias);
                 lgA = fmaf(tq_half_bits_to_float(rn[slotA]) * kB, sA, lgA);
@@ -376,7 +399,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         uint32_t pb[2][2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const uint16_t *vn = reinterpret_cast<const uint16_t *>(sp + L::kVN);
             const int slotA = 16 * i + (g >> 1) + 4 * (g & 1);
             const float vnA = tq_half_bits_to_float(vn[slotA]), vnB = tq_half_bits_to_float(vn[slotA + 8]);
             const float pA = fast_exp2(lg[i][0] - sub), pB = fast_exp2(lg[i][1] - sub);
@@ -391,7 +413,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         // ------------------------------------------------------------ values
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const uint8_t *vrow = sp + L::kV + (16 * i + t) * (16 * VB);
+            const uint8_t *vrow = spV + (16 * i + t) * (16 * VB);
             const uint64_t w0 = lds_v_chunk<VB>(vrow, g);                    // token t      (k-slot 2t)
             const uint64_t w1 = lds_v_chunk<VB>(vrow + 4 * 16 * VB, g);      // token t+4    (k-slot 2t+1)
             const uint64_t w2 = lds_v_chunk<VB>(vrow + 8 * 16 * VB, g);      // token t+8    (k-slot 2t+8)
@@ -415,9 +437,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                 mma_f16(o[mt], a0, a1, a2, a3, pb[i][0], pb[i][1]);
             }
         }
-        // ------------------------------------------------------------ refill this stage
+        }  // base < t_end
+        // ------------------------------------------------------------ hand the slot back; the warps of the
+        // group take turns to wait until all of them have done so and to request the refill
         __syncwarp();
-        if (lane == 0 && it + kStages < n_iter) issue(it + kStages);
+        if (lane == 0) {
+            mbar_arrive(empty_u32 + st * 8);
+            if (it + kStages < n_iter && wq == (it % kGroupWarps)) {
+                if (mbar_wait(empty_u32 + st * 8, use_parity)) issue(it + kStages);
+                else timed_out = true;
+            }
+        }
     }
     ring_pos += n_iter;
 

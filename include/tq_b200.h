@@ -149,6 +149,22 @@ int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const void *k_host,
                             int32_t n_splits, void *workspace, size_t workspace_bytes, void *out_host,
                             tq_stream stream);
 
+/* The same step with every operand in DEVICE memory and the cache length read from device
+ * memory when the kernels run, so that one recorded launch sequence (a CUDA graph of a whole
+ * model's decode step) can be replayed for every token: append k_new / v_new
+ * [batch, kv_heads, 128] at token *pos_dev of every row, attend with q [batch, q_heads, 128]
+ * over *pos_dev + 1 tokens, write out [batch, q_heads, 128].  The caller advances *pos_dev
+ * between steps (in stream order).  An append past the cache's capacity is dropped and
+ * reported by tq_device_status (4).  16-bit dtypes and at most 4 query heads per KV head;
+ * other shapes return TQ_ERR_UNSUPPORTED.  Replaces the per-token PackedMSELayer.update +
+ * turboquant_attention_forward pair and the host bookkeeping between them
+ * (src/turboquant/runtime/packed_qmse_cache.py:600-679, src/turboquant/runtime/attention.py:28-72,
+ * src/turboquant/runtime/generation.py:140-170).  Workspace: tq_decode_workspace_bytes. */
+int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_new, const void *v_new, int32_t dtype,
+                           int32_t q_heads, const tq_cache_desc *cache, const int32_t *pos_dev,
+                           int32_t n_splits, void *workspace, size_t workspace_bytes, void *out,
+                           tq_stream stream);
+
 /* Dequantise tokens [pos0, pos0 + n_tokens) of the keys (which = 0) or values (which = 1)
  * into a dense [batch, kv_heads, n_tokens, 128] tensor of dtype out->dtype. */
 int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,
@@ -175,7 +191,10 @@ int32_t tq_decode_attn_static(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
 
 /* Device-side status (no reference counterpart).  Kernels never spin without a limit: a
  * wait on an asynchronous copy that runs out sets a status word instead of hanging.  This
- * call synchronises with the device and returns that word (0 = no kernel ever gave up). */
+ * call synchronises with the device and returns that word: 0 = no kernel ever gave up;
+ * 1 = a decode kernel's wait ran out; 2 = a decode kernel found that its shared-memory layout
+ * does not fit and did not run; 3 = the encoder's wait ran out; 4 = an append addressed a
+ * token past the cache's capacity and was dropped.  The word is sticky for the context. */
 int32_t tq_device_status(tq_ctx *ctx, int32_t *status_out);
 
 /* Measurement hooks (no reference counterpart; used by the benchmark).  While enabled, each

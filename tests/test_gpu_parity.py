@@ -281,3 +281,73 @@ def test_host_buffer_decode_step_matches_device_calls(setup_golden, dtype):
         assert torch.equal(out_h, want.cpu())
     for x, y in zip(a.streams(), b.streams()):
         assert torch.equal(x[:, :, :130], y[:, :, :130])
+
+
+def test_decode_step_with_device_length_matches_and_replays_from_a_cuda_graph(setup_golden):
+    """tq_decode_step_dev: the append position / sequence length is a device scalar, so one
+    recorded launch sequence serves every token.  Results must equal the host-length path bit
+    for bit, eagerly and when replayed from a CUDA graph."""
+    from tq_local_b200.runtime.packed_store import PackedStore
+
+    codec = make_codec(4, True, setup_golden)
+    B, Hq, Hkv, N0, steps = 2, 8, 2, 700, 6
+    k, v, _ = O.synth_kvq(B, Hq, Hkv, N0 + steps, 128, seed=21, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(5)
+    qs = torch.randn(steps, B, Hq, 1, 128, generator=g).to(torch.bfloat16).cuda()
+    k, v = k.cuda(), v.cuda()
+    ref = PackedStore(codec, B, Hkv, capacity=1024)
+    dev = PackedStore(codec, B, Hkv, capacity=1024)
+    ref.pack(k[:, :, :N0], v[:, :, :N0])
+    dev.pack(k[:, :, :N0], v[:, :, :N0])
+    want = []
+    for t in range(steps):
+        ref.pack(k[:, :, N0 + t:N0 + t + 1], v[:, :, N0 + t:N0 + t + 1])
+        want.append(ref.decode_attn(qs[t], splits=dev.suggest_splits(dev.capacity)).clone())
+
+    pos = torch.tensor([N0], dtype=torch.int32, device="cuda")
+    sq = torch.empty_like(qs[0])
+    sk = torch.empty(B, Hkv, 1, 128, dtype=torch.bfloat16, device="cuda")
+    sv = torch.empty_like(sk)
+    sout = torch.empty_like(qs[0])
+
+    def load(t):
+        sq.copy_(qs[t]), sk.copy_(k[:, :, N0 + t:N0 + t + 1]), sv.copy_(v[:, :, N0 + t:N0 + t + 1])
+
+    load(0)
+    dev.decode_step_dev(sq, sk, sv, pos, out=sout)  # eager
+    pos.add_(1)
+    assert torch.equal(sout, want[0])
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    load(1)
+    with torch.cuda.graph(graph):
+        dev.decode_step_dev(sq, sk, sv, pos, out=sout)
+        pos.add_(1)
+    for t in range(1, steps):
+        load(t)
+        graph.replay()
+        assert torch.equal(sout, want[t]), f"step {t}"
+    assert int(pos.item()) == N0 + steps
+    dev.length = N0 + steps
+    for a, b in zip(ref.streams(), dev.streams()):
+        assert torch.equal(a[:, :, :N0 + steps], b[:, :, :N0 + steps])
+    assert codec.device_status() == 0
+
+
+def test_decode_step_dev_drops_appends_past_capacity_and_reports_it(setup_golden):
+    from tq_local_b200.runtime.packed_store import PackedStore
+
+    codec = make_codec(4, True, setup_golden)
+    B, Hq, Hkv = 1, 4, 1
+    k, v, q = O.synth_kvq(B, Hq, Hkv, 64, 128, seed=22, dtype=torch.bfloat16)
+    store = PackedStore(codec, B, Hkv, capacity=64)
+    store.pack(k.cuda(), v.cuda())
+    before = [t.clone() for t in store.streams()]
+    pos = torch.tensor([store.capacity], dtype=torch.int32, device="cuda")  # no room left
+    out = store.decode_step_dev(q.cuda(), k[:, :, :1].cuda(), v[:, :, :1].cuda(), pos)
+    torch.cuda.synchronize()
+    assert codec.device_status() == 4
+    for a, b in zip(before, store.streams()):
+        assert torch.equal(a, b)  # nothing was written
+    assert torch.isfinite(out.float()).all()
+    # the status word is sticky by design; a fresh context starts clean

@@ -315,6 +315,32 @@ extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const vo
     return TQ_OK;
 }
 
+extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_new, const void *v_new, int32_t dtype,
+                                      int32_t q_heads, const tq_cache_desc *cache, const int32_t *pos_dev,
+                                      int32_t n_splits, void *workspace, size_t workspace_bytes, void *out,
+                                      tq_stream stream) {
+    if (!ctx || !q || !k_new || !v_new || !out || !workspace || !pos_dev) return TQ_ERR_ARG;
+    int32_t rc = check_cache(ctx, cache);
+    if (rc) return rc;
+    if (dtype < 0 || dtype > 2 || n_splits < 1) return TQ_ERR_ARG;
+    if (q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
+    if (dtype == TQ_DTYPE_F32 || q_heads / cache->kv_heads > 4) return TQ_ERR_UNSUPPORTED;
+    if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)workspace | (uintptr_t)k_new | (uintptr_t)v_new) & 15) return TQ_ERR_ARG;
+    if ((uintptr_t)pos_dev & 3) return TQ_ERR_ARG;
+    if (workspace_bytes < tq_decode_workspace_bytes(cache->batch, q_heads, n_splits)) return TQ_ERR_WORKSPACE;
+    tq_dense_desc kd = {k_new, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
+    tq_dense_desc vd = {v_new, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
+    TqPackArgs append;
+    tq_fill_pack_args(ctx, &kd, &vd, 1, cache, 0, &append);
+    append.pos_ptr = pos_dev;
+    ctx->pending_append = &append;
+    ctx->pending_len_ptr = pos_dev;
+    rc = tq_launch_decode_mma4(ctx, q, dtype, q_heads, cache, cache->capacity, nullptr, nullptr, 0, n_splits, workspace,
+                               out, (cudaStream_t)stream);
+    ctx->pending_append = nullptr, ctx->pending_len_ptr = nullptr;
+    return rc;
+}
+
 extern "C" int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,
                               int32_t n_tokens, const tq_dense_desc *out, tq_stream stream) {
     if (!ctx || !out || !out->data) return TQ_ERR_ARG;

@@ -39,7 +39,8 @@ struct tq_ctx {
     size_t base_bytes;
     struct tq_prof *prof;  // measurement hooks, see tq_profile_enable
     int *error_flag;       // device word, set by a kernel whose bounded wait ran out
-    const struct TqPackArgs *pending_append;  // set by the host-step entry point for the next decode launch
+    const struct TqPackArgs *pending_append;  // set by the step entry points for the next decode launch
+    const int *pending_len_ptr;               // likewise: sequence length kept in device memory
     int64_t splits_cache_key;  // last (rows, length bucket) asked of tq_decode_suggest_splits
     int splits_cache_val;
 };

@@ -316,9 +316,15 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
     tq_load_column(rv, a.rot_v, dq, e);
     tq_grid_dependency_wait();
     int n_valid = a.n_splits;
-    if (a.seg_chunk > 0) {
-        const int64_t lo = R * (int64_t)a.seg_npad;
-        n_valid = (int)((lo + a.seg_npad - 1) / a.seg_chunk - lo / a.seg_chunk) + 1;
+    int seg_chunk = a.seg_chunk, seg_npad = a.seg_npad;
+    if (a.len_ptr) {
+        const TqPlan plan = tq_make_plan(min(*a.len_ptr + a.len_add, a.capacity), a.plan_rows, a.plan_ctas, a.n_splits,
+                                         a.plan_step);
+        seg_chunk = plan.chunk, seg_npad = plan.n_pad;
+    }
+    if (seg_chunk > 0) {
+        const int64_t lo = R * (int64_t)seg_npad;
+        n_valid = (int)((lo + seg_npad - 1) / seg_chunk - lo / seg_chunk) + 1;
     }
     {   // thread (e, dq) merges the splits of head dq
         const int g = dq;
@@ -507,6 +513,7 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
     c.part_m = w.part_m, c.part_l = w.part_l, c.part_acc = w.part_acc;
     c.n_splits = n_splits, c.Hq = q_heads, c.G = a.G;
     c.seg_chunk = 0, c.seg_npad = 0;
+    c.len_ptr = nullptr, c.len_add = 0, c.capacity = 0, c.plan_rows = 0, c.plan_ctas = 0, c.plan_step = 0;
     c.rot_v = ctx->rot_v;
     c.q = q, c.out = out;
     c.n_tail = n_tail;

@@ -376,6 +376,7 @@ int32_t tq_launch_decode_mma(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_
     c.part_m = w.part_m, c.part_l = w.part_l, c.part_acc = w.part_acc;
     c.n_splits = n_splits, c.Hq = q_heads, c.G = a.G;
     c.seg_chunk = 0, c.seg_npad = 0;
+    c.len_ptr = nullptr, c.len_add = 0, c.capacity = 0, c.plan_rows = 0, c.plan_ctas = 0, c.plan_step = 0;
     c.rot_v = ctx->rot_v;
     c.q = q, c.out = out;
     c.n_tail = n_tail;

@@ -64,6 +64,11 @@ struct Mma4Args {
     int n_pad;   // N rounded up to the CTA step: rows are laid end to end in units of n_pad tokens
     int chunk;   // tokens of that flattened (row, token) space per CTA
     int stable_len;  // tokens [0, stable_len) of every row were written before the preceding kernel began
+    // Length kept on the device (launch sequences replayed from a CUDA graph): when len_ptr is
+    // set, N = min(*len_ptr + len_add, capacity), stable_len = *len_ptr, and n_pad / chunk are
+    // planned by the kernel for its own grid.
+    const int *len_ptr;
+    int len_add, capacity;
     const uint32_t *frag;  // per query head: TQ_FRAG_ROW_WORDS words, see tq_qprep_frag_kernel
     float *part_m, *part_l, *part_acc;
     const float *centers_k, *centers_v;
@@ -183,9 +188,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
 
+    int N = a.N, n_pad = a.n_pad, chunk = a.chunk, stable_len = a.stable_len;
+    if (a.len_ptr) {
+        stable_len = *a.len_ptr;
+        N = max(1, min(stable_len + a.len_add, a.capacity));
+        const TqPlan plan = tq_make_plan(N, a.rows, gridDim.x, a.n_splits, kWarps * kStageTok);
+        n_pad = plan.n_pad, chunk = plan.chunk;
+    }
+
     // ---- this CTA's contiguous piece of the flattened (row, token) space
-    const int64_t flat_begin = (int64_t)blockIdx.x * a.chunk;
-    const int64_t flat_end = min(flat_begin + a.chunk, (int64_t)a.rows * a.n_pad);
+    const int64_t flat_begin = (int64_t)blockIdx.x * chunk;
+    const int64_t flat_end = min(flat_begin + chunk, (int64_t)a.rows * n_pad);
 
     // ---- ring set-up: group gq owns slots gq * kStages + s
     const int gq = warp / kGroupWarps, wq = warp % kGroupWarps;
@@ -227,16 +240,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
 
     // ---- one segment per row this CTA touches
     for (int64_t flat = flat_begin; flat < flat_end;) {
-    const int bh = (int)(flat / a.n_pad);
-    const int seg_lo = (int)(flat - (int64_t)bh * a.n_pad);
-    const int seg_len = (int)min((int64_t)(a.n_pad - seg_lo), flat_end - flat);
+    const int bh = (int)(flat / n_pad);
+    const int seg_lo = (int)(flat - (int64_t)bh * n_pad);
+    const int seg_len = (int)min((int64_t)(n_pad - seg_lo), flat_end - flat);
     flat += seg_len;
-    const int split = blockIdx.x - (int)(((int64_t)bh * a.n_pad) / a.chunk);  // partial slot inside the row
+    const int split = blockIdx.x - (int)(((int64_t)bh * n_pad) / chunk);  // partial slot inside the row
     const int b = bh / a.Hkv, h = bh % a.Hkv;
     const int64_t q_row0 = ((int64_t)b * a.Hkv + h) * G;
     const int64_t row0 = (int64_t)b * a.cache_sb + (int64_t)h * a.cache_sh;
     const int t_begin = seg_lo;
-    const int t_end = min(a.N, seg_lo + seg_len);
+    const int t_end = min(N, seg_lo + seg_len);
     const int grp_first = t_begin + gq * kGroupTok;
     const int my_first = grp_first + wq * kStageTok;
     constexpr int kCtaStep = kWarps * kStageTok;
@@ -271,7 +284,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         // the ring area was last touched through ordinary loads/stores (previous segment's merge)
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         for (int it = 0; it < n_first; ++it) {
-            if (first_segment && grp_first + it * kCtaStep + kGroupTok > a.stable_len)
+            if (first_segment && grp_first + it * kCtaStep + kGroupTok > stable_len)
                 deferred |= 1u << it;
             else
                 issue(it);
@@ -517,7 +530,8 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     uint32_t *frag = reinterpret_cast<uint32_t *>(w.qrot);
     const int groups = q_heads / cache->kv_heads;
     const TqPackArgs *append = ctx->pending_append;  // this step's new token, encoded by the same launch
-    ctx->pending_append = nullptr;
+    const int *len_ptr = ctx->pending_len_ptr;       // sequence length kept on the device
+    ctx->pending_append = nullptr, ctx->pending_len_ptr = nullptr;
     int rc = tq_launch_qprep_frag(ctx, q, q_dtype, rows / groups, groups, frag, append, stream);
     if (rc) return rc;
 
@@ -532,22 +546,16 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     // which must fit the n_splits slots the caller's workspace provides.
     const int step = kWarps * kStageTok;
     a.rows = cache->batch * cache->kv_heads;
-    a.n_pad = (seq_len + step - 1) / step * step;
+    const TqPlan plan = tq_make_plan(seq_len, a.rows, ctx->sm_count, n_splits, step);
+    a.n_pad = plan.n_pad, a.chunk = plan.chunk;
     const int64_t total = (int64_t)a.rows * a.n_pad;
-    int64_t chunk = ((total + ctx->sm_count - 1) / ctx->sm_count + step - 1) / step * step;
-    if (n_splits == 1) {
-        chunk = a.n_pad;
-    } else {
-        const int64_t floor_chunk = ((a.n_pad + n_splits - 2) / (n_splits - 1) + step - 1) / step * step;
-        if (chunk < floor_chunk) chunk = floor_chunk;
-    }
-    a.chunk = (int)chunk;
     a.stable_len = append ? append->pos0 : seq_len;
+    a.len_ptr = len_ptr, a.len_add = append ? 1 : 0, a.capacity = cache->capacity;
     a.frag = frag;
     a.part_m = w.part_m, a.part_l = w.part_l, a.part_acc = w.part_acc;
     a.centers_k = ctx->centers_k, a.centers_v = ctx->centers_v;
     a.error_flag = ctx->error_flag;
-    dim3 grid((unsigned)((total + chunk - 1) / chunk));
+    dim3 grid(len_ptr ? (unsigned)ctx->sm_count : (unsigned)((total + a.chunk - 1) / a.chunk));
     const int mode = ctx->use_qjl * 10 + ctx->bits;
     tq_prof_count(ctx, 3);
     tq_prof_begin(ctx, stream);
@@ -568,6 +576,8 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     c.part_m = w.part_m, c.part_l = w.part_l, c.part_acc = w.part_acc;
     c.n_splits = n_splits, c.Hq = q_heads, c.G = a.G;
     c.seg_chunk = a.chunk, c.seg_npad = a.n_pad;
+    c.len_ptr = len_ptr, c.len_add = a.len_add, c.capacity = a.capacity;
+    c.plan_rows = a.rows, c.plan_ctas = (int)grid.x, c.plan_step = step;
     c.rot_v = ctx->rot_v;
     c.q = q, c.out = out;
     c.n_tail = n_tail;

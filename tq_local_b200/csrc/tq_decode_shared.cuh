@@ -10,6 +10,10 @@ struct CombineArgs {
     // When seg_chunk > 0 the partials of KV row r are those of the CTAs whose chunk of the
     // flattened (row * seg_npad + token) space overlaps the row; otherwise all n_splits are valid.
     int seg_chunk, seg_npad;
+    // When len_ptr is set the sequence length is *len_ptr + len_add (clamped to capacity) and the
+    // kernel derives seg_chunk / seg_npad itself, with the plan the decode kernel used.
+    const int *len_ptr;
+    int len_add, capacity, plan_rows, plan_ctas, plan_step;
     const float *rot_v;  // R_v[d][e]
     const void *q;       // original-dtype query, for the dense tail
     void *out;

@@ -299,6 +299,7 @@ void tq_fill_pack_args(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc 
     a.centers_k = ctx->centers_k;
     a.bounds[0] = ctx->bounds_k, a.bounds[1] = ctx->bounds_v;
     a.first_kind = 0, a.n_kinds = 2;
+    a.pos_ptr = nullptr, a.capacity = cache->capacity, a.error_flag = ctx->error_flag;
 }
 
 int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,

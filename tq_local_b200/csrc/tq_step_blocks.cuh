@@ -28,6 +28,9 @@ struct TqPackArgs {
     const float *centers_k;
     const float *bounds[2];
     int first_kind, n_kinds;  // which of {keys, values} this launch encodes
+    const int *pos_ptr;       // when set, the append position is read from device memory instead of pos0
+    int capacity;             // tokens per cache row; an append past it is dropped and flagged
+    int *error_flag;
 };
 
 struct TqQprepArgs {
@@ -42,6 +45,27 @@ struct TqQprepArgs {
 // Words per query head in the fragment area: 8 lane variants of 26 words, padded to the size
 // of the rotated + projected query rows the area overlays in the decode workspace.
 #define TQ_FRAG_ROW_WORDS (2 * TQ_D + 8)
+
+// How the decode kernel cuts the (batch, KV head) rows, laid end to end and each padded to
+// `step` tokens, into one chunk per CTA.  A row then has at most n_splits partials.  Computed by
+// the host for a length it knows and by the kernels themselves for a length kept on the device.
+struct TqPlan {
+    int n_pad, chunk;
+};
+__host__ __device__ inline TqPlan tq_make_plan(int seq_len, int rows, int n_ctas, int n_splits, int step) {
+    TqPlan p;
+    p.n_pad = (seq_len + step - 1) / step * step;
+    const long long total = (long long)rows * p.n_pad;
+    long long chunk = ((total + n_ctas - 1) / n_ctas + step - 1) / step * step;
+    if (n_splits == 1) {
+        chunk = p.n_pad;
+    } else {
+        const long long floor_chunk = ((p.n_pad + n_splits - 2) / (n_splits - 1) + step - 1) / step * step;
+        if (chunk < floor_chunk) chunk = floor_chunk;
+    }
+    p.chunk = (int)chunk;
+    return p;
+}
 
 void tq_fill_pack_args(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,
                        const tq_cache_desc *cache, int32_t pos0, TqPackArgs *a);
@@ -86,7 +110,12 @@ template <typename T, bool QJL> __device__ __forceinline__ void tq_pack_small_bl
     const int h = (int)((vid / a.S) % a.H);
     const int b = (int)(vid / ((int64_t)a.S * a.H));
     const T *src = (const T *)a.x[kind] + b * a.sb[kind] + h * a.sh[kind] + (int64_t)t * a.st[kind];
-    const int64_t row = b * a.cache_sb + h * a.cache_sh + a.pos0 + t;
+    const int pos0 = a.pos_ptr ? *a.pos_ptr : a.pos0;
+    if (pos0 < 0 || pos0 + a.S > a.capacity) {  // (the whole block leaves together)
+        if (tid == 0) atomicExch(a.error_flag, 4);
+        return;
+    }
+    const int64_t row = b * a.cache_sb + h * a.cache_sh + pos0 + t;
     const int bits = a.bits[kind];
     float m[32];
     tq_load_column(m, a.rot_t[kind], dq, j);

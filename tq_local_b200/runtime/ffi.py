@@ -20,7 +20,7 @@ EXPORTS = (
     "tq_abi_version", "tq_last_cuda_error", "tq_ctx_create", "tq_ctx_destroy", "tq_pack",
     "tq_decode_workspace_bytes", "tq_decode_suggest_splits", "tq_decode_attn", "tq_dequant",
     "tq_key_norm_sum", "tq_profile_enable", "tq_profile_read", "tq_device_status", "tq_static_scratch_bytes",
-    "tq_decode_attn_static", "tq_decode_step_workspace_bytes", "tq_decode_step_host",
+    "tq_decode_attn_static", "tq_decode_step_workspace_bytes", "tq_decode_step_host", "tq_decode_step_dev",
 )
 
 _ERRORS = {-1: "bad argument", -2: "unsupported shape or mode", -3: "CUDA error", -4: "workspace too small"}
@@ -107,6 +107,10 @@ def lib() -> C.CDLL:
                                       C.POINTER(CacheDesc), C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p,
                                       C.c_void_p]
     L.tq_decode_step_host.restype = C.c_int32
+    L.tq_decode_step_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                     C.POINTER(CacheDesc), C.c_void_p, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p,
+                                     C.c_void_p]
+    L.tq_decode_step_dev.restype = C.c_int32
     _lib = L
     return L
 

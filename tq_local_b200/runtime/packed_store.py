@@ -169,6 +169,30 @@ class PackedStore:
         self.length += 1
         return out
 
+    def decode_step_dev(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, pos: torch.Tensor,
+                        out: torch.Tensor | None = None, splits: int | None = None) -> torch.Tensor:
+        """One decode step whose cache length is the int32 DEVICE scalar ``pos``: append ``k_new`` /
+        ``v_new`` [B, Hkv, 1, 128] at token ``pos`` and attend with ``q`` [B, Hq, 1, 128] over
+        ``pos + 1`` tokens.  Nothing here depends on the value of ``pos`` on the host, so the call
+        can be recorded in a CUDA graph and replayed; the caller advances ``pos`` and, when it is
+        done, sets ``self.length``.  The cache must already have room (``reserve``)."""
+        b, hq = int(q.shape[0]), int(q.shape[1])
+        if b != self.batch or k_new.shape[1] != self.kv_heads or q.dtype != k_new.dtype:
+            raise ValueError("shape or dtype mismatch")
+        if pos.dtype != torch.int32 or pos.device != self.codec.device or pos.numel() != 1:
+            raise ValueError("pos must be an int32 scalar tensor on the cache's device")
+        qc, kc, vc = (t if t.is_contiguous() else t.contiguous() for t in (q, k_new, v_new))
+        splits = self.suggest_splits(self.capacity) if splits is None else int(splits)
+        ws = self._get_workspace(hq, splits)
+        if out is None:
+            out = torch.empty(b, hq, 1, 128, dtype=q.dtype, device=q.device)
+        with torch.cuda.device(self.codec.device):
+            ffi.check(ffi.lib().tq_decode_step_dev(self.codec.handle, qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                                   tq_dtype(q.dtype), hq, C.byref(self._desc), pos.data_ptr(), splits,
+                                                   ws.data_ptr(), ws.numel(), out.data_ptr(), self._stream_ptr()),
+                      "tq_decode_step_dev")
+        return out
+
     def dequant(self, which: str, lo: int = 0, hi: int | None = None,
                 dtype: torch.dtype = torch.float32) -> torch.Tensor:
         """Dequantise tokens [lo, hi) of ``which`` in {'keys', 'values'} -> [B, Hkv, hi-lo, 128]."""

@@ -369,6 +369,124 @@ def run_gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------
+# Whole-model decode: random-init Llama-3.1-8B over a packed 32k-token cache
+# ----------------------------------------------------------------------------
+
+MODEL_WORKLOAD = dict(name="llama3.1-8b-random-init-decode", batch=16, context=32768, layers=32, hidden=4096,
+                      intermediate=14336, q_heads=32, kv_heads=8, vocab=128256, bits=4, use_qjl=True)
+
+
+def run_model_arm(args) -> None:
+    """Decode tokens/s of a whole model step: random-init Llama-3.1-8B (bf16), batch 16, every
+    layer's cache holding 32768 packed tokens per sequence (4-bit Q_prod), greedy decoding through
+    the library's attention backend with the model step replayed from a CUDA graph.  The caches
+    are filled with packed synthetic K/V (the prompt pass is not part of a decode-rate figure).
+    At N > 1 the weights are replicated, the KV heads are sharded and the batch stays 16."""
+    import torch
+    import torch.distributed as dist
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from transformers.cache_utils import Cache
+
+    from tq_local_b200.adapters.transformers import disable_turboquant_attention, enable_turboquant_attention
+    from tq_local_b200.runtime.generation import RecordedDecoder
+    from tq_local_b200.runtime.packed_qmse_cache import PackedMSELayer
+    from tq_local_b200.runtime.sharding import HeadShard
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    w = dict(MODEL_WORKLOAD)
+    if args.batch_per_gpu:
+        w["batch"] = args.batch_per_gpu
+    if args.context:
+        w["context"] = args.context
+    if args.layers:
+        w["layers"] = args.layers
+    steps, warmup = args.steps, max(args.warmup, 3)
+    cfg = LlamaConfig(vocab_size=w["vocab"], hidden_size=w["hidden"], intermediate_size=w["intermediate"],
+                      num_hidden_layers=w["layers"], num_attention_heads=w["q_heads"],
+                      num_key_value_heads=w["kv_heads"], head_dim=HEAD_DIM, max_position_embeddings=131072,
+                      tie_word_embeddings=False)
+    torch.manual_seed(0)
+    old_dtype = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = LlamaForCausalLM(cfg).eval()
+    finally:
+        torch.set_default_dtype(old_dtype)
+    shard = HeadShard.from_process_group() if world > 1 else HeadShard()
+    gen = torch.Generator(device=dev).manual_seed(99)
+    B, N = w["batch"], w["context"]
+    layers = []
+    with torch.inference_mode():
+        for _ in range(w["layers"]):
+            k = synth_on_device(torch, (B, w["kv_heads"], N, HEAD_DIM), gen, torch.bfloat16)
+            v = synth_on_device(torch, (B, w["kv_heads"], N, HEAD_DIM), gen, torch.bfloat16)
+            layer = PackedMSELayer(bits=w["bits"], use_qjl_keys=w["use_qjl"], quantize_decode=True,
+                                   reserve_tokens=steps + warmup + 8, shard=shard)
+            layer.initialize_from_dense(k, v)
+            layers.append(layer)
+            del k, v
+        cache = Cache(layers=layers)
+        old_impl = enable_turboquant_attention(model, cache)
+        first = torch.randint(0, w["vocab"], (B, 1), device=dev, generator=gen)
+        sampler = ClockSampler(local_rank)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        try:
+            with RecordedDecoder(model, cache, first, warmup + steps) as dec:
+                for _ in range(warmup):
+                    dec.step()
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                if rank == 0:
+                    sampler.start()
+                ev0.record()
+                for _ in range(steps):
+                    dec.step()
+                ev1.record()
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                recorded = bool(dec.graph)
+                tokens = dec.tokens.clone()
+        finally:
+            disable_turboquant_attention(model, cache, old_impl)
+    ms = ev0.elapsed_time(ev1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        unit = bytes_per_unit(w["bits"], w["use_qjl"])
+        packed_bytes = unit * B * w["kv_heads"] * N * w["layers"]
+        weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
+        line = {
+            "metric": "decode_tok_per_s_32k_ctx", "value": B * 1e3 / ms, "unit": "tok/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "global_batch": B, "context": N, "layers": w["layers"],
+                       "q_heads": w["q_heads"], "kv_heads": w["kv_heads"], "bits": w["bits"], "mode": "Q_prod",
+                       "parallelism": f"kv-head-shard{world}, weights replicated" if world > 1 else "single",
+                       "decode_step": "CUDA graph replay" if recorded else "eager"},
+            "packed_kv_bytes_per_step": packed_bytes, "weight_bytes": weight_bytes,
+            "hbm_gbs_lower_bound": (packed_bytes / world + weight_bytes) / (ms * 1e-3) / 1e9,
+            "tokens_checksum": int(tokens.sum().item()),
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -381,9 +499,15 @@ def main() -> None:
     ap.add_argument("--context", type=int, default=None, help="override the context length (profiling captures)")
     ap.add_argument("--splits", type=int, default=None, help="override the library's split choice")
     ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling captures)")
+    ap.add_argument("--workload", default="layer", choices=["layer", "model"],
+                    help="layer: one attention layer's decode step (the headline metric); model: whole-model "
+                         "decode tokens/s of a random-init Llama-3.1-8B over 32k-token packed caches")
+    ap.add_argument("--layers", type=int, default=None, help="model workload: override the layer count (smoke runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "model":
+        run_model_arm(args)
     else:
         run_gpu_arm(args)
 

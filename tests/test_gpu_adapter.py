@@ -130,3 +130,38 @@ def test_cache_layer_views_and_multi_token_queries(setup_golden):
                              c(s.k_signs), c(s.k_rnorms))
         want = O.attend_dequant(q[:, :, i:i + 1], mine, 4)
         assert float((got[:, :, i:i + 1] - want).abs().max() / want.abs().max()) < 1e-5
+
+
+def test_generate_with_recorded_decode_step_matches_eager_stepping(monkeypatch):
+    """``cuda_graph=True``: the model's decode step is recorded once and replayed per token with
+    the cache length on the device.  Replay must give exactly the tokens of the same steps run
+    eagerly, and (up to near-ties of a random-init model) those of the host-length path."""
+    import turboquant
+    from tq_local_b200.runtime import generation
+
+    model = _tiny_model(torch.bfloat16)
+    ids = torch.randint(0, 512, (2, 40), device="cuda", generator=torch.Generator("cuda").manual_seed(3))
+    new = 24
+
+    def run(**kw):
+        turboquant.activate(model, StubTokenizer(), quiet=True, bits=4, verify=False, **kw)
+        try:
+            out = model.generate(ids, max_new_tokens=new)
+            tel = turboquant.last_telemetry(model)
+        finally:
+            turboquant.deactivate(model, quiet=True)
+        return out, tel
+
+    import warnings
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")  # a step that could not be recorded warns; here it must record
+        graphed, tel_g = run(cuda_graph=True)
+    host_len, tel_h = run(cuda_graph=False)
+    monkeypatch.setattr(generation, "_GRAPH_WARMUP_STEPS", 10 ** 9)  # same device-length steps, never recorded
+    stepped, _ = run(cuda_graph=True)
+    assert tuple(graphed.shape) == (2, 40 + new)
+    assert torch.equal(graphed, stepped)
+    assert (graphed == host_len).float().mean() >= 0.9 and torch.equal(graphed[:, :42], host_len[:, :42])
+    assert tel_g["completion_tokens"] == tel_h["completion_tokens"] == new
+    assert tel_g["packed_actual_bytes"] == tel_h["packed_actual_bytes"]

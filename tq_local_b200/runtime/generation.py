@@ -34,6 +34,7 @@ from tq_local_b200.runtime.packed_qmse_cache import (
 )
 
 _EOS_POLL_STEPS = 8
+_GRAPH_WARMUP_STEPS = 2  # eager steps in static mode before the decode step is recorded
 
 
 @dataclass(frozen=True)
@@ -88,6 +89,117 @@ def _prefill(model, inputs):
         return model(**inputs, use_cache=True)
 
 
+def _static_decode_eligible(model, packed_cache, mask) -> bool:
+    """The replayable (CUDA-graph) decode loop needs every layer packed with quantised appends,
+    a tensor-core shape, one GPU, and no padding in the prompt."""
+    import torch
+
+    if packed_cache is None or not torch.cuda.is_available():
+        return False
+    q_heads = int(getattr(model.config, "num_attention_heads", 0))
+    if not q_heads or not all(layer.supports_static_decode(q_heads) for layer in packed_cache.layers):
+        return False
+    return mask is None or bool(mask.all())
+
+
+class RecordedDecoder:
+    """Greedy decode steps with the whole model step recorded once in a CUDA graph and replayed
+    per token.  The cache length, the position ids, the current token and the output cursor all
+    live on the device, so the host only launches the graph.  The first steps run eagerly (they
+    are real steps) and the next one is recorded; if the model's forward pass cannot be recorded,
+    all steps run eagerly with a warning.  Use as a context manager, or call ``close``: it hands
+    the layers back to their normal bookkeeping."""
+
+    def __init__(self, model, cache, first_token, max_steps: int, eager_steps: int | None = None):
+        import torch
+
+        self.model, self.cache = model, cache
+        self.layers = cache.layers
+        device = first_token.device
+        self.length0 = self.layers[0].store.length
+        self.pos32 = torch.tensor([self.length0], dtype=torch.int32, device=device)
+        self.pos_ids = torch.full((1, 1), self.length0, dtype=torch.long, device=device)
+        self.token = first_token.clone()
+        self.produced = torch.zeros((first_token.shape[0], max(max_steps, 1)), dtype=first_token.dtype,
+                                    device=device)
+        self.cursor = torch.zeros(1, dtype=torch.long, device=device)
+        self.max_steps = int(max_steps)
+        self.eager_steps = _GRAPH_WARMUP_STEPS if eager_steps is None else int(eager_steps)
+        self.done = 0
+        self.graph = None  # None: not recorded yet; False: cannot be recorded
+        for layer in self.layers:
+            layer.begin_static_decode(self.pos32, max_steps)
+
+    def _forward_once(self) -> None:
+        import torch
+
+        out = self.model(input_ids=self.token, past_key_values=self.cache, use_cache=True, position_ids=self.pos_ids)
+        nxt = torch.argmax(out.logits[:, -1, :], dim=-1, keepdim=True)
+        self.token.copy_(nxt)
+        self.produced.index_copy_(1, self.cursor, nxt)
+        self.cursor.add_(1), self.pos32.add_(1), self.pos_ids.add_(1)
+
+    def step(self) -> None:
+        """Queue one more token (asynchronous; read ``tokens`` after a synchronise)."""
+        import torch
+
+        if self.done >= self.max_steps:
+            raise RuntimeError("RecordedDecoder: no room left for another token")
+        if self.done >= self.eager_steps and self.graph is None:
+            torch.cuda.synchronize()
+            try:
+                recorded = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(recorded, capture_error_mode="thread_local"):
+                    self._forward_once()
+                self.graph = recorded
+            except Exception as exc:
+                import warnings
+
+                warnings.warn(f"decode step not recorded in a CUDA graph ({exc!r}); running it eagerly")
+                self.graph = False
+        if self.graph:
+            self.graph.replay()
+        else:
+            self._forward_once()
+        self.done += 1
+
+    @property
+    def tokens(self):
+        """The tokens produced so far, [B, done] (a view; synchronise first)."""
+        return self.produced[:, :self.done]
+
+    def close(self) -> None:
+        import torch
+
+        if self.layers is not None:
+            torch.cuda.synchronize()
+            for layer in self.layers:
+                layer.end_static_decode(self.length0 + self.done)
+            self.layers = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+def _graphed_greedy_steps(model, cache, first_token, n_steps, eos_tensor):
+    """Up to ``n_steps`` greedy tokens after ``first_token`` through a ``RecordedDecoder``, looking
+    at the produced tokens every few steps for the EOS test.  Returns them as [B, <= n_steps]."""
+    import torch
+
+    with RecordedDecoder(model, cache, first_token, n_steps) as dec:
+        while dec.done < n_steps:
+            if eos_tensor is not None and dec.done and dec.done % _EOS_POLL_STEPS == 0:
+                so_far = torch.cat((first_token, dec.tokens), dim=-1)
+                if bool(torch.isin(so_far, eos_tensor).any(dim=-1).all()):
+                    break
+            dec.step()
+        torch.cuda.synchronize()
+        return dec.tokens.clone()
+
+
 def greedy_decode_with_prefill_cache(
     *,
     model,
@@ -104,6 +216,7 @@ def greedy_decode_with_prefill_cache(
     norm_guard: bool = True,
     verify: bool = True,
     shard=None,
+    use_cuda_graph: bool | None = None,
 ) -> GenerationOutput:
     import torch
 
@@ -158,7 +271,14 @@ def greedy_decode_with_prefill_cache(
             eos_tensor = (torch.tensor(sorted(eos_ids), device=next_token.device) if eos_ids else None)
             generated = [next_token]
             mask = inputs.get("attention_mask")
-            for step in range(max_new_tokens - 1):
+            if use_cuda_graph is None:
+                use_cuda_graph = variant == "qmse_packed" and max_new_tokens > 8
+            graphed = False
+            if use_cuda_graph and max_new_tokens > 1 and _static_decode_eligible(model, packed_cache, mask):
+                if eos_tensor is None or not bool(torch.isin(next_token, eos_tensor).any(dim=-1).all()):
+                    generated.append(_graphed_greedy_steps(model, cache, next_token, max_new_tokens - 1, eos_tensor))
+                graphed = True
+            for step in range(0 if graphed else max_new_tokens - 1):
                 if eos_tensor is not None and step % _EOS_POLL_STEPS == 0:
                     seen = torch.isin(torch.cat(generated, dim=-1), eos_tensor).any(dim=-1)
                     if bool(seen.all()):

@@ -136,6 +136,8 @@ class PackedMSELayer(CacheLayerMixin):
         self._dense_k = _GrowingDense()
         self._dense_v = _GrowingDense()
         self._kv_heads_total: int | None = None
+        self._static_pos: torch.Tensor | None = None  # see begin_static_decode
+        self._static_kv: tuple[torch.Tensor, torch.Tensor] | None = None
 
     # ---------------------------------------------------------------- reference attributes
     @property
@@ -238,12 +240,38 @@ class PackedMSELayer(CacheLayerMixin):
         self._ensure_store(key_states)
         self.store.pack(self.shard.local_kv(key_states), self.shard.local_kv(value_states))
 
+    # ---------------------------------------------------------------- replayable decode
+    def supports_static_decode(self, q_heads: int) -> bool:
+        """Whether this layer can serve decode steps whose length lives on the device (packed,
+        quantised appends, 16-bit cache, at most 4 query heads per KV head)."""
+        return (self.store is not None and not self._force_dense and self.quantize_decode
+                and self._dense_k.length == 0 and self.dtype in (torch.float16, torch.bfloat16)
+                and q_heads // self._kv_heads_total <= 4)
+
+    def begin_static_decode(self, pos: torch.Tensor, max_new_tokens: int) -> None:
+        """Switch to decode steps that read the cache length from the int32 device scalar ``pos``
+        (shared by all layers of a model and advanced by the caller once per step).  From here on
+        ``update`` only remembers the new token and ``attend`` appends it and attends in one fused
+        call, neither touching host-side state: the whole model step can be recorded in a CUDA
+        graph.  ``end_static_decode`` returns to the normal bookkeeping."""
+        self.store.reserve(self.store.length + int(max_new_tokens))
+        self._static_pos = pos
+
+    def end_static_decode(self, new_length: int) -> None:
+        self._static_pos, self._static_kv = None, None
+        self.store.length = int(new_length)
+
     # ---------------------------------------------------------------- decode-time update
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor,
                cache_kwargs: dict[str, Any] | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         """HF cache hook (reference: packed_qmse_cache.py:600-624)."""
         if not self.is_initialized:
             self.lazy_initialization(key_states, value_states)
+        if self._static_pos is not None:
+            if key_states.shape[2] != 1:
+                raise RuntimeError("static decode serves one new token per step")
+            self._static_kv = (key_states, value_states)
+            return key_states, value_states
         if self._force_dense:
             return self._update_dense_decode(key_states, value_states)
         if self._lazy_update:
@@ -288,6 +316,11 @@ class PackedMSELayer(CacheLayerMixin):
         time with causal visibility (the new tokens were appended before attention)."""
         if self.store is None or self._force_dense:
             raise RuntimeError("attend() needs a packed (non-dense) layer")
+        if self._static_pos is not None:
+            k_new, v_new = self._static_kv
+            out = self.store.decode_step_dev(self.shard.local_q(query_states, self._kv_heads_total),
+                                             self.shard.local_kv(k_new), self.shard.local_kv(v_new), self._static_pos)
+            return self.shard.gather_heads(out)
         b, hq, sq, d = query_states.shape
         q_local = self.shard.local_q(query_states, self._kv_heads_total)
         tail_k, tail_v = self._dense_k.view(), self._dense_v.view()

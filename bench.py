@@ -438,24 +438,45 @@ def run_model_arm(args) -> None:
         first = torch.randint(0, w["vocab"], (B, 1), device=dev, generator=gen)
         sampler = ClockSampler(local_rank)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        def fence():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
         try:
-            with RecordedDecoder(model, cache, first, warmup + steps) as dec:
+            if world == 1:
+                with RecordedDecoder(model, cache, first, warmup + steps) as dec:
+                    for _ in range(warmup):
+                        dec.step()
+                    fence()
+                    sampler.start()
+                    ev0.record()
+                    for _ in range(steps):
+                        dec.step()
+                    ev1.record()
+                    fence()
+                    recorded = bool(dec.graph)
+                    tokens = dec.tokens.clone()
+            else:
+                # sharded layers keep their length on the host: one eager forward pass per token
+                recorded, produced, tok = False, [], first
+
+                def eager_step(tok):
+                    out = model(input_ids=tok, past_key_values=cache, use_cache=True)
+                    return torch.argmax(out.logits[:, -1, :], dim=-1, keepdim=True)
+
                 for _ in range(warmup):
-                    dec.step()
-                if world > 1:
-                    dist.barrier()
-                torch.cuda.synchronize()
+                    tok = eager_step(tok)
+                fence()
                 if rank == 0:
                     sampler.start()
                 ev0.record()
                 for _ in range(steps):
-                    dec.step()
+                    tok = eager_step(tok)
+                    produced.append(tok)
                 ev1.record()
-                if world > 1:
-                    dist.barrier()
-                torch.cuda.synchronize()
-                recorded = bool(dec.graph)
-                tokens = dec.tokens.clone()
+                fence()
+                tokens = torch.cat(produced, dim=-1)
         finally:
             disable_turboquant_attention(model, cache, old_impl)
     ms = ev0.elapsed_time(ev1) / steps

@@ -165,3 +165,42 @@ def test_generate_with_recorded_decode_step_matches_eager_stepping(monkeypatch):
     assert (graphed == host_len).float().mean() >= 0.9 and torch.equal(graphed[:, :42], host_len[:, :42])
     assert tel_g["completion_tokens"] == tel_h["completion_tokens"] == new
     assert tel_g["packed_actual_bytes"] == tel_h["packed_actual_bytes"]
+
+
+def test_streaming_prefill_packs_layer_by_layer_with_the_same_result(setup_golden, capsys):
+    """Without the reconstruction report the prompt pass packs each layer as the model produces
+    it (no dense cache of the whole model).  Tokens, telemetry and norm-guard decisions must equal
+    the pack-after-prefill path."""
+    import turboquant
+    from tq_local_b200.runtime.packed_qmse_cache import build_packed_mse_cache, build_streaming_prefill_cache
+
+    model = _tiny_model()
+    ids = torch.from_numpy(Golden("e2e_tiny_llama").z["input_ids"]).cuda()
+
+    def run(verify):
+        turboquant.activate(model, StubTokenizer(), quiet=True, bits=4, verify=verify)
+        try:
+            return model.generate(ids, max_new_tokens=8), turboquant.last_telemetry(model)
+        finally:
+            turboquant.deactivate(model, quiet=True)
+
+    streamed, tel_s = run(False)
+    packed_after, tel_p = run(True)
+    assert torch.equal(streamed, packed_after)
+    for key in ("dense_kv_bytes", "packed_estimate_bytes", "packed_actual_bytes", "prompt_tokens", "completion_tokens"):
+        assert tel_s[key] == tel_p[key], key
+
+    # norm guard inside the streaming cache: same decisions and bytes as the batch builder
+    k_hi, v_hi, _ = O.synth_kvq(1, 4, 4, 64, 128, seed=11, norm_mode="asym")
+    k_lo, v_lo, _ = O.synth_kvq(1, 4, 4, 64, 128, seed=12)
+    pairs = [(k_hi.cuda(), v_hi.cuda()), (k_lo.cuda(), v_lo.cuda())]
+    want = build_packed_mse_cache(pairs, bits=4, use_qjl_keys=True, quantize_decode=True, norm_guard=True)
+    capsys.readouterr()
+    cache = build_streaming_prefill_cache(2, 4, use_qjl_keys=True, quantize_decode=True, norm_guard=True)
+    for layer, (k, v) in zip(cache.layers, pairs):
+        rk, rv = layer.update(k, v)
+        assert rk is k and rv is v
+    assert [l._force_dense for l in cache.layers] == [l._force_dense for l in want.layers] == [True, False]
+    assert [l.storage_bytes() for l in cache.layers] == [l.storage_bytes() for l in want.layers]
+    assert torch.equal(cache.layers[1].store.k_codes[:, :, :64], want.layers[1].store.k_codes[:, :, :64])
+    assert cache.layers[1].get_seq_length() == 64

@@ -29,7 +29,10 @@ from tq_local_b200.runtime.memory_accounting import (
 )
 from tq_local_b200.runtime.packed_qmse_cache import (
     build_packed_mse_cache,
+    build_streaming_prefill_cache,
     packed_cache_storage_breakdown,
+    report_streamed_norm_guard,
+    streamed_prefill_memory_breakdown,
     verify_packed_reconstruction,
 )
 
@@ -81,12 +84,15 @@ def eos_token_ids(model, tokenizer) -> set[int]:
     return {int(eos)} if isinstance(eos, int) else {int(x) for x in eos}
 
 
-def _prefill(model, inputs):
+def _prefill(model, inputs, cache=None):
     """Dense prefill; ask for the last position's logits only when the model supports it."""
+    extra = {} if cache is None else {"past_key_values": cache}
     try:
-        return model(**inputs, use_cache=True, logits_to_keep=1)
+        return model(**inputs, use_cache=True, logits_to_keep=1, **extra)
     except TypeError:
-        return model(**inputs, use_cache=True)
+        if cache is not None and any(layer.is_initialized for layer in cache.layers):
+            raise  # the cache already holds part of the prompt: a second pass would store it twice
+        return model(**inputs, use_cache=True, **extra)
 
 
 def _static_decode_eligible(model, packed_cache, mask) -> bool:
@@ -231,12 +237,32 @@ def greedy_decode_with_prefill_cache(
     old_impl = None
 
     with torch.inference_mode():
-        outputs = _prefill(model, inputs)
+        cfg = getattr(model, "config", None)
+        n_layers = getattr(cfg, "num_hidden_layers", None)
+        heads = getattr(cfg, "num_attention_heads", None)
+        head_dim = getattr(cfg, "head_dim", None) or (cfg.hidden_size // heads if heads else None)
+        # Without the reconstruction report nothing needs the dense prompt cache: every layer packs
+        # its K/V while the prompt pass runs.
+        streaming = variant == "qmse_packed" and not verify and bool(n_layers) and bool(head_dim)
+        if streaming:
+            t0 = time.monotonic()
+            packed_cache = build_streaming_prefill_cache(
+                n_layers, qmse_bits, head_dim=head_dim, seed=rotation_seed, num_outlier_channels=num_outlier_channels,
+                outlier_extra_bits=outlier_extra_bits, use_qjl_keys=use_qjl_keys, quantize_decode=quantize_decode,
+                norm_guard=norm_guard, reserve_tokens=max_new_tokens, shard=shard)
+            quant_seconds += time.monotonic() - t0
+            outputs = _prefill(model, inputs, packed_cache)
+        else:
+            outputs = _prefill(model, inputs)
         cache = outputs.past_key_values
         next_token = torch.argmax(outputs.logits[:, -1, :], dim=-1, keepdim=True)
         del outputs
-        dense_breakdown = past_key_values_memory_breakdown(cache)
         estimate = actual = recon = None
+        if streaming:
+            report_streamed_norm_guard(packed_cache, qmse_bits, head_dim)
+            dense_breakdown = streamed_prefill_memory_breakdown(packed_cache)
+        else:
+            dense_breakdown = past_key_values_memory_breakdown(cache)
         if variant == "qmse_packed":
             estimate = turboquant_mse_packed_bytes(
                 num_vectors_per_kind=dense_breakdown["num_key_value_vectors_per_kind"],
@@ -244,11 +270,12 @@ def greedy_decode_with_prefill_cache(
                 bits=qmse_bits,
             )
             t0 = time.monotonic()
-            packed_cache = build_packed_mse_cache(
-                cache, bits=qmse_bits, seed=rotation_seed, num_outlier_channels=num_outlier_channels,
-                outlier_extra_bits=outlier_extra_bits, use_qjl_keys=use_qjl_keys, quantize_decode=quantize_decode,
-                norm_guard=norm_guard, reserve_tokens=max_new_tokens, shard=shard, release_dense=not verify,
-            )
+            if not streaming:
+                packed_cache = build_packed_mse_cache(
+                    cache, bits=qmse_bits, seed=rotation_seed, num_outlier_channels=num_outlier_channels,
+                    outlier_extra_bits=outlier_extra_bits, use_qjl_keys=use_qjl_keys, quantize_decode=quantize_decode,
+                    norm_guard=norm_guard, reserve_tokens=max_new_tokens, shard=shard, release_dense=not verify,
+                )
             if verify:
                 recon = verify_packed_reconstruction(cache, packed_cache)
             actual = packed_cache_storage_breakdown(packed_cache)

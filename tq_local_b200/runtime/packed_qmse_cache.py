@@ -137,6 +137,8 @@ class PackedMSELayer(CacheLayerMixin):
         self._dense_v = _GrowingDense()
         self._kv_heads_total: int | None = None
         self._static_pos: torch.Tensor | None = None  # see begin_static_decode
+        self._stream_threshold: float | None = None   # see build_streaming_prefill_cache
+        self._prefill_shape: tuple[int, ...] | None = None
         self._static_kv: tuple[torch.Tensor, torch.Tensor] | None = None
 
     # ---------------------------------------------------------------- reference attributes
@@ -271,6 +273,15 @@ class PackedMSELayer(CacheLayerMixin):
             if key_states.shape[2] != 1:
                 raise RuntimeError("static decode serves one new token per step")
             self._static_kv = (key_states, value_states)
+            return key_states, value_states
+        if self._stream_threshold is not None:
+            # Streaming prefill: this is the prompt's K/V of this layer.  Pack it now (or keep it
+            # dense under the norm guard) and hand the dense tensors back for the prompt's own
+            # attention; nothing dense outlives the layer's forward pass.
+            threshold, self._stream_threshold = self._stream_threshold, None
+            self._prefill_shape = tuple(key_states.shape)
+            dense = threshold != float("inf") and float(key_norm_mean(key_states).item()) > threshold
+            self.initialize_from_dense(key_states, value_states, force_dense=dense)
             return key_states, value_states
         if self._force_dense:
             return self._update_dense_decode(key_states, value_states)
@@ -439,6 +450,60 @@ def build_packed_mse_cache(
         print(f"[TurboQuant] norm_guard: {len(dense_ids)}/{len(layers)} layers kept dense "
               f"(threshold={threshold:.1f}, layers={dense_ids})", file=sys.stderr)
     return Cache(layers=layers)
+
+
+def build_streaming_prefill_cache(
+    num_layers: int,
+    bits: int,
+    head_dim: int = 128,
+    seed: int = 0,
+    grid_size: int = 32769,
+    num_outlier_channels: int = 0,
+    outlier_extra_bits: int = 1,
+    use_qjl_keys: bool = False,
+    quantize_decode: bool = False,
+    norm_guard: bool = True,
+    reserve_tokens: int = 0,
+    shard: HeadShard | None = None,
+) -> Cache:
+    """An empty packed cache to run the PROMPT pass with: each layer packs its keys / values the
+    moment the model hands them over (``update``), applying the same norm-guard rule as
+    ``build_packed_mse_cache``, so the dense cache of the whole model (the reference's
+    generation.py:91-129) never exists — peak memory holds one layer's dense K/V."""
+    threshold = _auto_norm_threshold(bits, head_dim) if norm_guard else float("inf")
+    layers = []
+    for _ in range(num_layers):
+        layer = PackedMSELayer(bits=bits, seed=seed, grid_size=grid_size, num_outlier_channels=num_outlier_channels,
+                               outlier_extra_bits=outlier_extra_bits, use_qjl_keys=use_qjl_keys,
+                               quantize_decode=quantize_decode, reserve_tokens=reserve_tokens, shard=shard)
+        layer._stream_threshold = threshold
+        layers.append(layer)
+    return Cache(layers=layers)
+
+
+def report_streamed_norm_guard(cache: Cache, bits: int, head_dim: int = 128) -> None:
+    """The norm-guard notice of ``build_packed_mse_cache`` for a cache filled by a streaming prefill."""
+    dense_ids = [i for i, layer in enumerate(cache.layers) if layer._force_dense]
+    if dense_ids:
+        print(f"[TurboQuant] norm_guard: {len(dense_ids)}/{len(cache.layers)} layers kept dense "
+              f"(threshold={_auto_norm_threshold(bits, head_dim):.1f}, layers={dense_ids})", file=sys.stderr)
+
+
+def streamed_prefill_memory_breakdown(cache: Cache) -> dict[str, Any]:
+    """What ``past_key_values_memory_breakdown`` reports for the dense prompt cache, computed
+    from the shapes the layers saw (the dense tensors themselves were never kept)."""
+    shapes = [(layer._prefill_shape, layer.dtype) for layer in cache.layers if layer._prefill_shape is not None]
+    per_kind = sum(b * h * s * d * torch.empty((), dtype=dt).element_size() for (b, h, s, d), dt in shapes)
+    return {
+        "num_layers": len(shapes),
+        "vector_dimension": shapes[0][0][3] if shapes else None,
+        "num_key_value_vectors_per_kind": sum(b * h * s for (b, h, s, _), _ in shapes),
+        "key_bytes": per_kind,
+        "value_bytes": per_kind,
+        "dense_kv_bytes": 2 * per_kind,
+        "extra_tensor_bytes": 0,
+        "total_cache_tensor_bytes": 2 * per_kind,
+    }
 
 
 def verify_packed_reconstruction(original_cache, packed_cache: Cache) -> list[dict[str, Any]]:

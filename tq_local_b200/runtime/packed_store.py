@@ -37,6 +37,7 @@ class PackedStore:
         self.length = 0
         self._alloc(max(8, _round_up(int(capacity), 8)))
         self._workspace: torch.Tensor | None = None
+        self._step_plan = None
 
     # ------------------------------------------------------------------ storage
     def _alloc(self, capacity: int) -> None:
@@ -60,6 +61,8 @@ class PackedStore:
             self.v_codes.data_ptr(), self.v_norms.data_ptr(),
             b, h, capacity, h * capacity, capacity,
         )
+        self._desc_ref = C.byref(self._desc)
+        self._step_plan = None
 
     def streams(self) -> list[torch.Tensor]:
         return [t for t in (self.k_codes, self.k_norms, self.k_signs, self.k_rnorms, self.v_codes, self.v_norms)
@@ -114,6 +117,7 @@ class PackedStore:
         need = int(ffi.lib().tq_decode_workspace_bytes(self.batch, q_heads, splits))
         if self._workspace is None or self._workspace.numel() < need:
             self._workspace = torch.empty(need, dtype=torch.uint8, device=self.codec.device)
+            self._step_plan = None  # (it remembers the scratch address)
         return self._workspace
 
     def decode_attn(self, q: torch.Tensor, *, seq_len: int | None = None, tail_k: torch.Tensor | None = None,
@@ -157,15 +161,27 @@ class PackedStore:
         if b != self.batch or k_new.shape[1] != self.kv_heads or q.dtype != k_new.dtype or out.dtype != q.dtype:
             raise ValueError("shape or dtype mismatch")
         self.reserve(self.length + 1)
-        splits = self.suggest_splits(self.length + 1) if splits is None else int(splits)
-        need = int(ffi.lib().tq_decode_step_workspace_bytes(b, hq, self.kv_heads, splits))
-        if self._workspace is None or self._workspace.numel() < need:
-            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.codec.device)
-        with torch.cuda.device(self.codec.device):
-            ffi.check(ffi.lib().tq_decode_step_host(self.codec.handle, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
-                                                    tq_dtype(q.dtype), hq, C.byref(self._desc), self.length, splits,
-                                                    self._workspace.data_ptr(), self._workspace.numel(),
-                                                    out.data_ptr(), self._stream_ptr()), "tq_decode_step_host")
+        # the split count and the scratch size only change when the length crosses a kernel step
+        key = (hq, splits, (self.length + 1) >> 9, self.capacity)
+        if self._step_plan is None or self._step_plan[0] != key:
+            n_splits = self.suggest_splits(self.length + 1) if splits is None else int(splits)
+            need = int(ffi.lib().tq_decode_step_workspace_bytes(b, hq, self.kv_heads, n_splits))
+            if self._workspace is None or self._workspace.numel() < need:
+                self._workspace = torch.empty(need, dtype=torch.uint8, device=self.codec.device)
+            self._step_plan = (key, n_splits, self._workspace.data_ptr(), self._workspace.numel(), tq_dtype(q.dtype))
+        _, n_splits, ws_ptr, ws_bytes, dt = self._step_plan
+        dev = self.codec.device
+        if torch.cuda.current_device() == dev.index:
+            rc = ffi.lib().tq_decode_step_host(self.codec.handle, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), dt,
+                                               hq, self._desc_ref, self.length, n_splits, ws_ptr, ws_bytes,
+                                               out.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+        else:
+            with torch.cuda.device(dev):
+                rc = ffi.lib().tq_decode_step_host(self.codec.handle, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+                                                   dt, hq, self._desc_ref, self.length, n_splits, ws_ptr, ws_bytes,
+                                                   out.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+        if rc:
+            ffi.check(rc, "tq_decode_step_host")
         self.length += 1
         return out
 

@@ -47,7 +47,7 @@ def bytes_per_unit(bits: int, use_qjl: bool) -> int:
 
 
 # DRAM bytes (read + write) per unit of the main decode kernel, from the ncu capture of the
-# batch-4 case summarised in profiles/decode_mma4_persistent_b4_ctx32768.md: 140.74 MB read +
+# batch-4 case summarised in profiles/decode_mma4_b4_ctx32768.md: 140.74 MB read +
 # 3.6 MB written for 1 048 576 units of 134 B.  Every packed byte is read once, so traffic
 # grows in proportion to the units of a launch.
 NCU_TRAFFIC_BYTES_PER_UNIT = (140.74e6 + 3.6e6) / 1048576

@@ -8,16 +8,17 @@
 // are accumulated in the fp32 TMEM accumulator:  x1*r1 + x1*r2 + x2*r1 + x2*r2 + x1*r3 + x3*r1.
 // bf16 x bf16 products are exact in fp32, so the only rounding is the accumulation.
 //
-// One CTA per SM, persistent over 128-vector tiles:
+// One CTA of 8 warps per SM, persistent over 128-vector tiles:
 //   * the rotation's three bf16 terms (96 KB, already in the 128-byte-swizzled K-major image
 //     the MMA wants) are fetched once with TMA bulk copies onto an mbarrier;
-//   * each thread owns one vector: it loads the row, computes the norm, normalises, splits
-//     into three bf16 terms and stores them swizzled into the A tiles (96 KB);
+//   * two threads share a vector (warps w and w + 4 reach the same TMEM lanes), one per half of
+//     its 128 coordinates: both compute the norm, each normalises, splits into three bf16 terms
+//     and stores its 64 coordinates swizzled into the A tiles (96 KB);
 //   * one thread issues 48 tcgen05.mma (M = N = 128, K = 16, kind::f16, bf16 in / fp32 out)
 //     into 128 TMEM columns and commits to an mbarrier;
-//   * each thread reads its own accumulator row back with tcgen05.ld (32 columns at a time),
-//     finds the Lloyd-Max bin by binary search ("value equal to a boundary -> lower bin"),
-//     builds the LSB-first bitstream in registers and writes codes + fp16 norm.
+//   * each thread reads its half of the accumulator row back with tcgen05.ld (32 columns at a
+//     time), finds the Lloyd-Max bin by binary search ("value equal to a boundary -> lower
+//     bin"), builds its half of the LSB-first bitstream in registers and writes it.
 // Every mbarrier wait is bounded and reports through the device status word.
 #include <math.h>
 #include <string.h>
@@ -26,7 +27,8 @@
 
 namespace {
 
-constexpr int kTile = 128;                   // vectors per tile == threads per CTA
+constexpr int kTile = 128;                   // vectors per tile; two threads per vector
+constexpr int kThreads = 2 * kTile;
 constexpr int kTermBytes = kTile * TQ_D * 2;  // one bf16 term of a 128 x 128 operand: 32 KB
 constexpr int kSlabBytes = kTile * 128;       // 128 rows x 64 bf16 (one 128-byte swizzle row each): 16 KB
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -153,7 +155,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // The B operand (96 KB) is swapped between the stages with TMA bulk copies that are issued as
 // soon as the previous stage's MMAs have completed, so they overlap with the epilogues.
 template <typename T, int BITS, bool QJL>
-__global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ float s_bnd[16];
     __shared__ __align__(16) __nv_bfloat16 s_cen3[3][16];  // bf16 terms of the key centres
@@ -164,6 +166,8 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
     uint8_t *a_tiles = smem_raw + (base - raw);    // three A terms, then three B terms
     const uint32_t a_addr = base, b_addr = base + 3 * kTermBytes;
     const int tid = threadIdx.x, warp = tid >> 5;
+    const int vrow = tid & (kTile - 1);  // this thread's vector within the tile (= its TMEM lane)
+    const int hsel = tid >> 7;           // which half of the coordinates it works on
     const uint32_t bar_b = smem_u32(&s_bar[0]), bar_mma = smem_u32(&s_bar[1]);
     bool timed_out = false;
     uint32_t b_phase = 0, mma_phase = 0;
@@ -234,12 +238,13 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = s_tmem;
-    const uint32_t my_tmem = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t row_tmem = tmem + ((uint32_t)((warp & 3) * 32) << 16);  // column 0 of this thread's lane
+    const uint32_t my_tmem = row_tmem + 64 * hsel;                          // its half of the columns
 
     const int64_t n_vec = (int64_t)a.B * a.H * a.S;
     for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
         // ---------------- stage 1: load, normalise, split, store swizzled (thread = vector)
-        const int64_t vid = (int64_t)tile * kTile + tid;
+        const int64_t vid = (int64_t)tile * kTile + vrow;
         const bool valid = vid < n_vec;
         const int64_t v2 = valid ? vid : 0;
         const int t = (int)(v2 % a.S);
@@ -258,13 +263,13 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
         const float nrm = sqrtf(ss);
         const float safe = nrm > 0.0f ? nrm : 1.0f;
 #pragma unroll 2
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 8 * hsel; c < 8 * hsel + 8; ++c) {
             float v[8];
             RowLoader<T>::load8(src + 8 * c, v);
             __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) split3(valid ? v[i] / safe : 0.f, t1[i], t2[i], t3[i]);
-            const int off = operand_offset(tid, 8 * c);
+            const int off = operand_offset(vrow, 8 * c);
             *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
             *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
             *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
@@ -274,11 +279,11 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
         if (QJL && tid == 0) load_b(a.b_image2);  // (a plain Q_mse encode keeps its one operand resident)
 
         // ---------------- epilogue 1: this thread's accumulator row -> codes
-        uint32_t words[4 * BITS + 1];
+        uint32_t words[2 * BITS + 1];  // this half's 64 codes
 #pragma unroll
-        for (int w = 0; w <= 4 * BITS; ++w) words[w] = 0;
+        for (int w = 0; w <= 2 * BITS; ++w) words[w] = 0;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
             uint32_t r[32];
             tmem_ld32(my_tmem + 32 * c, r);
 #pragma unroll
@@ -295,17 +300,16 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
         }
         const uint16_t nh = tq_float_to_half_bits(safe);
         if (valid) {
-            uint4 *dst = reinterpret_cast<uint4 *>(a.codes + row * (int64_t)(16 * BITS));
+            uint2 *dst = reinterpret_cast<uint2 *>(a.codes + row * (int64_t)(16 * BITS) + hsel * (8 * BITS));
 #pragma unroll
-            for (int w = 0; w < BITS; ++w)
-                dst[w] = make_uint4(words[4 * w], words[4 * w + 1], words[4 * w + 2], words[4 * w + 3]);
-            a.norms[row] = nh;
+            for (int w = 0; w < BITS; ++w) dst[w] = make_uint2(words[2 * w], words[2 * w + 1]);
+            if (hsel == 0) a.norms[row] = nh;
         }
 
         if (QJL) {
             // ---------------- stage 2: A = centres[codes] (three bf16 terms from a 2^BITS-entry table)
 #pragma unroll 2
-            for (int c = 0; c < 16; ++c) {
+            for (int c = 0; c < 8; ++c) {
                 __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -315,7 +319,7 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
                     idx &= (1u << BITS) - 1u;
                     t1[i] = s_cen3[0][idx], t2[i] = s_cen3[1][idx], t3[i] = s_cen3[2][idx];
                 }
-                const int off = operand_offset(tid, 8 * c);
+                const int off = operand_offset(vrow, 64 * hsel + 8 * c);
                 *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
                 *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
                 *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
@@ -327,9 +331,9 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
             const float nf = tq_half_bits_to_float(nh);
             float rs = 0.f;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 4; ++c) {  // (both threads of a vector need the whole residual's norm)
                 uint32_t r[32];
-                tmem_ld32(my_tmem + 32 * c, r);
+                tmem_ld32(row_tmem + 32 * c, r);
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     float v[8];
@@ -344,20 +348,20 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
             const float rn = sqrtf(rs);
             const float rsafe = rn > 0.0f ? rn : 1.0f;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t r[32];
                 tmem_ld32(my_tmem + 32 * c, r);
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     float v[8];
-                    RowLoader<T>::load8(src + 32 * c + 8 * q4, v);
+                    RowLoader<T>::load8(src + 64 * hsel + 32 * c + 8 * q4, v);
                     __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float res = v[i] - tq_round_through<T>(__uint_as_float(r[8 * q4 + i]) * nf);
                         split3(valid ? res / rsafe : 0.f, t1[i], t2[i], t3[i]);
                     }
-                    const int off = operand_offset(tid, 32 * c + 8 * q4);
+                    const int off = operand_offset(vrow, 64 * hsel + 32 * c + 8 * q4);
                     *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
                     *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
                     *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
@@ -366,17 +370,17 @@ __global__ void __launch_bounds__(kTile, 1) tq_pack_tc_kernel(PackTcArgs a) {
             // ---------------- stage 3: projection, sign bits
             run_gemm();
             if (tid == 0 && more) load_b(a.b_image);
-            uint32_t sg[4] = {0u, 0u, 0u, 0u};
+            uint32_t sg[2] = {0u, 0u};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t r[32];
                 tmem_ld32(my_tmem + 32 * c, r);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sg[c] |= (__uint_as_float(r[i]) >= 0.0f ? 1u : 0u) << i;
             }
             if (valid) {
-                *reinterpret_cast<uint4 *>(a.signs + row * 16) = make_uint4(sg[0], sg[1], sg[2], sg[3]);
-                a.rnorms[row] = tq_float_to_half_bits(rsafe);
+                *reinterpret_cast<uint2 *>(a.signs + row * 16 + 8 * hsel) = make_uint2(sg[0], sg[1]);
+                if (hsel == 0) a.rnorms[row] = tq_float_to_half_bits(rsafe);
             }
         }
         // every accumulator row is read before the next GEMM overwrites the columns
@@ -433,7 +437,7 @@ static cudaError_t launch_tc(const PackTcArgs &a, int grid, cudaStream_t stream)
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    tq_pack_tc_kernel<T, BITS, QJL><<<grid, kTile, smem, stream>>>(a);
+    tq_pack_tc_kernel<T, BITS, QJL><<<grid, kThreads, smem, stream>>>(a);
     return cudaGetLastError();
 }
 

@@ -8,17 +8,18 @@
 // are accumulated in the fp32 TMEM accumulator:  x1*r1 + x1*r2 + x2*r1 + x2*r2 + x1*r3 + x3*r1.
 // bf16 x bf16 products are exact in fp32, so the only rounding is the accumulation.
 //
-// One CTA of 8 warps per SM, persistent over 128-vector tiles:
+// One CTA of 16 warps per SM, persistent over 128-vector tiles:
 //   * the rotation's three bf16 terms (96 KB, already in the 128-byte-swizzled K-major image
 //     the MMA wants) are fetched once with TMA bulk copies onto an mbarrier;
-//   * two threads share a vector (warps w and w + 4 reach the same TMEM lanes), one per half of
-//     its 128 coordinates: both compute the norm, each normalises, splits into three bf16 terms
-//     and stores its 64 coordinates swizzled into the A tiles (96 KB);
+//   * four threads share a vector (warps w, w + 4, w + 8, w + 12 reach the same TMEM lanes), one
+//     per quarter of its 128 coordinates: they add up the squared norm through shared memory,
+//     each normalises, splits into three bf16 terms and stores its 32 coordinates swizzled into
+//     the A tiles (96 KB);
 //   * one thread issues 48 tcgen05.mma (M = N = 128, K = 16, kind::f16, bf16 in / fp32 out)
 //     into 128 TMEM columns and commits to an mbarrier;
-//   * each thread reads its half of the accumulator row back with tcgen05.ld (32 columns at a
-//     time), finds the Lloyd-Max bin by binary search ("value equal to a boundary -> lower
-//     bin"), builds its half of the LSB-first bitstream in registers and writes it.
+//   * each thread reads its 32 accumulator columns back with one tcgen05.ld, finds the
+//     Lloyd-Max bin by binary search ("value equal to a boundary -> lower bin"), builds its
+//     quarter of the LSB-first bitstream in registers and writes it.
 // Every mbarrier wait is bounded and reports through the device status word.
 #include <math.h>
 #include <string.h>
@@ -27,8 +28,9 @@
 
 namespace {
 
-constexpr int kTile = 128;                   // vectors per tile; two threads per vector
-constexpr int kThreads = 2 * kTile;
+constexpr int kTile = 128;                   // vectors per tile; four threads per vector
+constexpr int kSplit = 4;
+constexpr int kThreads = kSplit * kTile;
 constexpr int kTermBytes = kTile * TQ_D * 2;  // one bf16 term of a 128 x 128 operand: 32 KB
 constexpr int kSlabBytes = kTile * 128;       // 128 rows x 64 bf16 (one 128-byte swizzle row each): 16 KB
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -167,7 +169,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
     const uint32_t a_addr = base, b_addr = base + 3 * kTermBytes;
     const int tid = threadIdx.x, warp = tid >> 5;
     const int vrow = tid & (kTile - 1);  // this thread's vector within the tile (= its TMEM lane)
-    const int hsel = tid >> 7;           // which half of the coordinates it works on
+    const int hsel = tid >> 7;           // which quarter of the coordinates it works on
+    __shared__ float s_sq[kSplit][kTile];  // partial squared norms of the four threads of a vector
     const uint32_t bar_b = smem_u32(&s_bar[0]), bar_mma = smem_u32(&s_bar[1]);
     bool timed_out = false;
     uint32_t b_phase = 0, mma_phase = 0;
@@ -239,7 +242,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = s_tmem;
     const uint32_t row_tmem = tmem + ((uint32_t)((warp & 3) * 32) << 16);  // column 0 of this thread's lane
-    const uint32_t my_tmem = row_tmem + 64 * hsel;                          // its half of the columns
+    const uint32_t my_tmem = row_tmem + 32 * hsel;                          // its quarter of the columns
 
     const int64_t n_vec = (int64_t)a.B * a.H * a.S;
     for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
@@ -252,24 +255,25 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
         const int b = (int)(v2 / ((int64_t)a.S * a.H));
         const T *src = reinterpret_cast<const T *>(a.x) + b * a.sb + h * a.sh + (int64_t)t * a.st;
         const int64_t row = b * a.cache_sb + h * a.cache_sh + a.pos0 + t;
+        float x[32];  // this thread's quarter of the vector
         float ss = 0.f;
-#pragma unroll 4
-        for (int c = 0; c < 16; ++c) {
-            float v[8];
-            RowLoader<T>::load8(src + 8 * c, v);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
-        }
-        const float nrm = sqrtf(ss);
-        const float safe = nrm > 0.0f ? nrm : 1.0f;
-#pragma unroll 2
-        for (int c = 8 * hsel; c < 8 * hsel + 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
             float v[8];
-            RowLoader<T>::load8(src + 8 * c, v);
+            RowLoader<T>::load8(src + 32 * hsel + 8 * c, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[8 * c + i] = v[i], ss = fmaf(v[i], v[i], ss);
+        }
+        s_sq[hsel][vrow] = ss;
+        __syncthreads();
+        const float nrm = sqrtf((s_sq[0][vrow] + s_sq[1][vrow]) + (s_sq[2][vrow] + s_sq[3][vrow]));
+        const float safe = nrm > 0.0f ? nrm : 1.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
             __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) split3(valid ? v[i] / safe : 0.f, t1[i], t2[i], t3[i]);
-            const int off = operand_offset(vrow, 8 * c);
+            for (int i = 0; i < 8; ++i) split3(valid ? x[8 * c + i] / safe : 0.f, t1[i], t2[i], t3[i]);
+            const int off = operand_offset(vrow, 32 * hsel + 8 * c);
             *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
             *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
             *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
@@ -279,13 +283,12 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
         if (QJL && tid == 0) load_b(a.b_image2);  // (a plain Q_mse encode keeps its one operand resident)
 
         // ---------------- epilogue 1: this thread's accumulator row -> codes
-        uint32_t words[2 * BITS + 1];  // this half's 64 codes
+        uint32_t words[BITS + 1];  // this quarter's 32 codes
 #pragma unroll
-        for (int w = 0; w <= 2 * BITS; ++w) words[w] = 0;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int w = 0; w <= BITS; ++w) words[w] = 0;
+        {
             uint32_t r[32];
-            tmem_ld32(my_tmem + 32 * c, r);
+            tmem_ld32(my_tmem, r);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float z = __uint_as_float(r[i]);
@@ -293,23 +296,23 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
 #pragma unroll
                 for (int stepw = 1 << (BITS - 1); stepw > 0; stepw >>= 1)
                     if (s_bnd[idx + stepw - 1] < z) idx += stepw;
-                const int bit = (32 * c + i) * BITS, w = bit >> 5, sh = bit & 31;
+                const int bit = i * BITS, w = bit >> 5, sh = bit & 31;
                 words[w] |= idx << sh;
                 if (sh + BITS > 32) words[w + 1] |= idx >> (32 - sh);
             }
         }
         const uint16_t nh = tq_float_to_half_bits(safe);
         if (valid) {
-            uint2 *dst = reinterpret_cast<uint2 *>(a.codes + row * (int64_t)(16 * BITS) + hsel * (8 * BITS));
+            uint32_t *dst = reinterpret_cast<uint32_t *>(a.codes + row * (int64_t)(16 * BITS) + hsel * (4 * BITS));
 #pragma unroll
-            for (int w = 0; w < BITS; ++w) dst[w] = make_uint2(words[2 * w], words[2 * w + 1]);
+            for (int w = 0; w < BITS; ++w) dst[w] = words[w];
             if (hsel == 0) a.norms[row] = nh;
         }
 
         if (QJL) {
             // ---------------- stage 2: A = centres[codes] (three bf16 terms from a 2^BITS-entry table)
-#pragma unroll 2
-            for (int c = 0; c < 8; ++c) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
                 __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
                     idx &= (1u << BITS) - 1u;
                     t1[i] = s_cen3[0][idx], t2[i] = s_cen3[1][idx], t3[i] = s_cen3[2][idx];
                 }
-                const int off = operand_offset(vrow, 64 * hsel + 8 * c);
+                const int off = operand_offset(vrow, 32 * hsel + 8 * c);
                 *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
                 *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
                 *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
@@ -330,56 +333,41 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
             // ---------------- epilogue 2: residual against the dtype-rounded reconstruction
             const float nf = tq_half_bits_to_float(nh);
             float rs = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {  // (both threads of a vector need the whole residual's norm)
+            {
                 uint32_t r[32];
-                tmem_ld32(row_tmem + 32 * c, r);
+                tmem_ld32(my_tmem, r);
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    float v[8];
-                    RowLoader<T>::load8(src + 32 * c + 8 * q4, v);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float res = v[i] - tq_round_through<T>(__uint_as_float(r[8 * q4 + i]) * nf);
-                        rs = fmaf(res, res, rs);
-                    }
+                for (int i = 0; i < 32; ++i) {
+                    x[i] -= tq_round_through<T>(__uint_as_float(r[i]) * nf);  // x becomes the residual
+                    rs = fmaf(x[i], x[i], rs);
                 }
             }
-            const float rn = sqrtf(rs);
+            s_sq[hsel][vrow] = rs;  // (its last readers passed the barrier inside the first GEMM)
+            __syncthreads();
+            const float rn = sqrtf((s_sq[0][vrow] + s_sq[1][vrow]) + (s_sq[2][vrow] + s_sq[3][vrow]));
             const float rsafe = rn > 0.0f ? rn : 1.0f;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t r[32];
-                tmem_ld32(my_tmem + 32 * c, r);
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    float v[8];
-                    RowLoader<T>::load8(src + 64 * hsel + 32 * c + 8 * q4, v);
-                    __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
+            for (int c = 0; c < 4; ++c) {
+                __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float res = v[i] - tq_round_through<T>(__uint_as_float(r[8 * q4 + i]) * nf);
-                        split3(valid ? res / rsafe : 0.f, t1[i], t2[i], t3[i]);
-                    }
-                    const int off = operand_offset(vrow, 64 * hsel + 32 * c + 8 * q4);
-                    *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
-                    *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
-                    *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
-                }
+                for (int i = 0; i < 8; ++i) split3(valid ? x[8 * c + i] / rsafe : 0.f, t1[i], t2[i], t3[i]);
+                const int off = operand_offset(vrow, 32 * hsel + 8 * c);
+                *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
+                *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
+                *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
             }
             // ---------------- stage 3: projection, sign bits
             run_gemm();
             if (tid == 0 && more) load_b(a.b_image);
-            uint32_t sg[2] = {0u, 0u};
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            uint32_t sg = 0u;
+            {
                 uint32_t r[32];
-                tmem_ld32(my_tmem + 32 * c, r);
+                tmem_ld32(my_tmem, r);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) sg[c] |= (__uint_as_float(r[i]) >= 0.0f ? 1u : 0u) << i;
+                for (int i = 0; i < 32; ++i) sg |= (__uint_as_float(r[i]) >= 0.0f ? 1u : 0u) << i;
             }
             if (valid) {
-                *reinterpret_cast<uint2 *>(a.signs + row * 16 + 8 * hsel) = make_uint2(sg[0], sg[1]);
+                *reinterpret_cast<uint32_t *>(a.signs + row * 16 + 4 * hsel) = sg;
                 if (hsel == 0) a.rnorms[row] = tq_float_to_half_bits(rsafe);
             }
         }

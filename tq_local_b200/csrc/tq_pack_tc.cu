@@ -183,9 +183,10 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
                         bar_b);
         b_pending = true;
     };
-    // Everybody has stored its A row: make the stores visible to the tensor core, let thread 0
-    // wait for B and issue the 48 MMAs of one GEMM, then everybody waits for their completion.
-    auto run_gemm = [&]() {
+    // Everybody has stored its A row: make the stores visible to the tensor core and let thread 0
+    // wait for B and issue the 48 MMAs of one GEMM (gemm_issue); later everybody waits for their
+    // completion (gemm_wait).  Work that does not touch the operands goes in between.
+    auto gemm_issue = [&]() {
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
         __syncthreads();
@@ -215,6 +216,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_mma)
                          : "memory");
         }
+    };
+    auto gemm_wait = [&]() {
         if (!mbar_wait(bar_mma, mma_phase)) timed_out = true;
         mma_phase ^= 1;
         __syncwarp();  // thread 0 took the issue path; tcgen05.ld is warp-collective
@@ -245,25 +248,44 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
     const uint32_t my_tmem = row_tmem + 32 * hsel;                          // its quarter of the columns
 
     const int64_t n_vec = (int64_t)a.B * a.H * a.S;
-    for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
-        // ---------------- stage 1: load, normalise, split, store swizzled (thread = vector)
+    struct RowRef {
+        const T *src;
+        int64_t row;
+        bool valid;
+    };
+    auto locate = [&](int tile) {  // this thread's vector of a tile: where it comes from, where it goes
         const int64_t vid = (int64_t)tile * kTile + vrow;
-        const bool valid = vid < n_vec;
-        const int64_t v2 = valid ? vid : 0;
+        RowRef r;
+        r.valid = vid < n_vec;
+        const int64_t v2 = r.valid ? vid : 0;
         const int t = (int)(v2 % a.S);
         const int h = (int)((v2 / a.S) % a.H);
         const int b = (int)(v2 / ((int64_t)a.S * a.H));
-        const T *src = reinterpret_cast<const T *>(a.x) + b * a.sb + h * a.sh + (int64_t)t * a.st;
-        const int64_t row = b * a.cache_sb + h * a.cache_sh + a.pos0 + t;
-        float x[32];  // this thread's quarter of the vector
-        float ss = 0.f;
+        r.src = reinterpret_cast<const T *>(a.x) + b * a.sb + h * a.sh + (int64_t)t * a.st;
+        r.row = b * a.cache_sb + h * a.cache_sh + a.pos0 + t;
+        return r;
+    };
+    float x[32];  // this thread's quarter of the vector
+    float ss = 0.f;
+    auto fetch = [&](const RowRef &r) {  // load the quarter, start its squared norm
+        ss = 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             float v[8];
-            RowLoader<T>::load8(src + 32 * hsel + 8 * c, v);
+            RowLoader<T>::load8(r.src + 32 * hsel + 8 * c, v);
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[8 * c + i] = v[i], ss = fmaf(v[i], v[i], ss);
         }
+    };
+    RowRef cur = locate(blockIdx.x);
+    if ((int)blockIdx.x < a.n_tiles) fetch(cur);
+    for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+        // ---------------- stage 1: normalise, split, store swizzled.  The rows were loaded while the
+        // previous tile's last GEMM ran.
+        const bool valid = cur.valid;
+        const int64_t row = cur.row;
+        const bool more = tile + (int)gridDim.x < a.n_tiles;
+        RowRef nxt = cur;
         s_sq[hsel][vrow] = ss;
         __syncthreads();
         const float nrm = sqrtf((s_sq[0][vrow] + s_sq[1][vrow]) + (s_sq[2][vrow] + s_sq[3][vrow]));
@@ -278,8 +300,12 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
             *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
             *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
         }
-        run_gemm();
-        const bool more = tile + (int)gridDim.x < a.n_tiles;
+        gemm_issue();
+        if (!QJL && more) {  // the row is split and stored: fetch the next tile's under the MMAs
+            nxt = locate(tile + (int)gridDim.x);
+            fetch(nxt);
+        }
+        gemm_wait();
         if (QJL && tid == 0) load_b(a.b_image2);  // (a plain Q_mse encode keeps its one operand resident)
 
         // ---------------- epilogue 1: this thread's accumulator row -> codes
@@ -327,7 +353,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
                 *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
                 *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
             }
-            run_gemm();
+            gemm_issue();
+            gemm_wait();
             if (tid == 0) load_b(a.b_image3);
 
             // ---------------- epilogue 2: residual against the dtype-rounded reconstruction
@@ -357,7 +384,12 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
                 *reinterpret_cast<uint4 *>(a_tiles + 2 * kTermBytes + off) = *reinterpret_cast<const uint4 *>(t3);
             }
             // ---------------- stage 3: projection, sign bits
-            run_gemm();
+            gemm_issue();
+            if (more) {  // the residual is split and stored: fetch the next tile's rows under the MMAs
+                nxt = locate(tile + (int)gridDim.x);
+                fetch(nxt);
+            }
+            gemm_wait();
             if (tid == 0 && more) load_b(a.b_image);
             uint32_t sg = 0u;
             {
@@ -371,6 +403,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
                 if (hsel == 0) a.rnorms[row] = tq_float_to_half_bits(rsafe);
             }
         }
+        cur = nxt;
         // every accumulator row is read before the next GEMM overwrites the columns
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
         __syncthreads();

@@ -155,7 +155,7 @@ int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const void *k_host,
  * [batch, kv_heads, 128] at token *pos_dev of every row, attend with q [batch, q_heads, 128]
  * over *pos_dev + 1 tokens, write out [batch, q_heads, 128].  The caller advances *pos_dev
  * between steps (in stream order).  An append past the cache's capacity is dropped and
- * reported by tq_device_status (4).  16-bit dtypes and at most 4 query heads per KV head;
+ * reported by tq_device_status (4).  16-bit dtypes and at most 8 query heads per KV head;
  * other shapes return TQ_ERR_UNSUPPORTED.  Replaces the per-token PackedMSELayer.update +
  * turboquant_attention_forward pair and the host bookkeeping between them
  * (src/turboquant/runtime/packed_qmse_cache.py:600-679, src/turboquant/runtime/attention.py:28-72,

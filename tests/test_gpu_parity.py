@@ -39,17 +39,47 @@ def _check_packed(store, ref: O.PackedLayer, k, v, p, what):
     assert fp16_ulp_diff(store.k_norms[:, :, :n].cpu(), ref.k_norms) <= 1
     assert fp16_ulp_diff(store.v_norms[:, :, :n].cpu(), ref.v_norms) <= 1
     if p.use_qjl:
-        # Signs are compared on vectors whose codes match exactly; a flip is tolerated only
-        # where the reference's projected residual is nearly zero.
+        # Signs and residual norms are compared on vectors whose codes match exactly.  The residual
+        # is taken against the reconstruction ROUNDED to the cache dtype (packed_qmse_cache.py:
+        # 295-297), so two things decide how far fp32 summation order can move it:
+        #  * an element of the fp32 reconstruction that sits on a rounding edge of that dtype
+        #    becomes the other neighbour, a jump of one ulp of that element ("rounding edge", the
+        #    same rule as "within 1e-6 of a decision boundary" for the codes);
+        #  * a vector whose fp16 norm landed on the other side of an fp16 rounding edge (allowed
+        #    above) is reconstructed 2^-11 larger or smaller, which re-rounds many elements.
+        # Sign flips are accepted where the reference's projected residual is within 5e-3 of zero
+        # plus what the vector's rounding edges can move it; residual norms may differ by one fp16
+        # ulp plus the same reach.  Norm-edge vectors only get loose bounds.
         *_, proj = O.encode_keys_prod(k.contiguous(), p)
+        proj = proj.reshape(-1, 128).abs()
         got = torch.from_numpy(O.unpack_codes(store.k_signs[:, :, :n].reshape(-1, 16).cpu().numpy(), 1, 128))
         want = torch.from_numpy(O.unpack_codes(ref.k_signs.reshape(-1, 16).numpy(), 1, 128))
+        same_norm = (store.k_norms[:, :, :n].cpu().reshape(-1).view(torch.int16) ==
+                     ref.k_norms.reshape(-1).view(torch.int16))
+        rnorm = ref.k_rnorms.reshape(-1).float()
+        if ref.dtype == torch.float32:
+            edge_ulp = torch.zeros_like(proj)
+        else:
+            idx = torch.from_numpy(O.unpack_codes(ref.k_codes.reshape(-1, ref.k_codes.shape[-1]).numpy(),
+                                                  p.key_bits, 128))
+            norm = ref.k_norms.reshape(-1).float().unsqueeze(1)
+            rec = (p.cen_k[idx] @ p.rot_k) * norm
+            q = rec.to(ref.dtype).float()
+            ulp = (torch.nextafter(q.to(ref.dtype), torch.tensor(float("inf"), dtype=ref.dtype)).float() - q).abs()
+            on_edge = ((rec - q).abs() - ulp / 2).abs() < 1e-6 * norm  # fp32 summation error ~ 1e-7 |k|
+            edge_ulp = on_edge * ulp
+        reach = (edge_ulp @ p.qjl.abs().T) / rnorm.unsqueeze(1)  # how far each projection can move
         flips = (got != want) & exact_k.unsqueeze(1)
-        assert (proj.reshape(-1, 128).abs()[flips] < 5e-3).all(), what + ": QJL sign flips away from zero"
-        assert flips.float().mean() < 1e-3
-        rn_got = store.k_rnorms[:, :, :n].cpu().reshape(-1)[exact_k]
-        rn_ref = ref.k_rnorms.reshape(-1)[exact_k]
-        assert fp16_ulp_diff(rn_got, rn_ref) <= 1
+        judged = flips & same_norm.unsqueeze(1)
+        assert (proj[judged] <= 5e-3 + 1.05 * reach[judged]).all(), what + ": QJL sign flips away from zero"
+        assert (proj[flips] < 0.1).all() and flips.float().mean() < 1e-3
+        rn_got = store.k_rnorms[:, :, :n].cpu().reshape(-1).float()
+        ok = exact_k & same_norm
+        fp16_ulp = torch.maximum(rnorm, torch.tensor(2.0 ** -14)).log2().floor().exp2() * 2.0 ** -10
+        assert ((rn_got - rnorm).abs()[ok] <= (1.01 * fp16_ulp + 1.05 * edge_ulp.sum(dim=1))[ok]).all()
+        edge = exact_k & ~same_norm
+        assert ((rn_got - rnorm).abs()[edge] <= 1e-2 * rnorm[edge]).all()
+        assert (~same_norm).float().mean() < 2e-3
 
 
 @pytest.mark.parametrize("case", LAYER_CASES)
@@ -169,6 +199,11 @@ def test_dense_tail_attention_matches_reference(setup_golden, case):
     (4, True, torch.float32, 1, 16, 2, 640),
     (2, True, torch.bfloat16, 2, 8, 2, 600),
     (3, True, torch.float16, 1, 4, 4, 300),
+    # more than four query heads per KV head (the kernel's wide variant)
+    (4, True, torch.float16, 1, 10, 2, 1100),
+    (4, False, torch.bfloat16, 2, 16, 2, 900),
+    (3, False, torch.bfloat16, 1, 12, 2, 1300),
+    (4, True, torch.bfloat16, 2, 28, 4, 2100),
 ])
 def test_seeded_layer_against_oracle(setup_golden, bits, qjl, dtype, B, Hq, Hkv, N):
     """Larger seeded inputs: encode on the GPU, compare codes with the oracle, then

@@ -239,11 +239,8 @@ extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, i
     if (q_dtype == TQ_DTYPE_F32 || seq_len == 0)
         return tq_launch_decode_exact(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
                                       workspace, out, (cudaStream_t)stream);
-    if (q_heads / cache->kv_heads <= 4)
-        return tq_launch_decode_mma4(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
-                                     workspace, out, (cudaStream_t)stream);
-    return tq_launch_decode_mma(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
-                                workspace, out, (cudaStream_t)stream);
+    return tq_launch_decode_mma4(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
+                                 workspace, out, (cudaStream_t)stream);
 }
 
 extern "C" size_t tq_decode_step_workspace_bytes(int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t n_splits) {
@@ -299,7 +296,7 @@ extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const vo
     int32_t rc = check_cache(ctx, cache);
     if (rc) return rc;
     TqPackArgs append;
-    if (dtype != TQ_DTYPE_F32 && q_heads / cache->kv_heads <= 4) {
+    if (dtype != TQ_DTYPE_F32 && q_heads / cache->kv_heads <= TQ_MAX_GROUPS) {
         // the tensor-core decode path encodes the new token in its own query-preparation launch
         tq_fill_pack_args(ctx, &kd, &vd, 1, cache, pos, &append);
         ctx->pending_append = &append;
@@ -324,7 +321,7 @@ extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_
     if (rc) return rc;
     if (dtype < 0 || dtype > 2 || n_splits < 1) return TQ_ERR_ARG;
     if (q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
-    if (dtype == TQ_DTYPE_F32 || q_heads / cache->kv_heads > 4) return TQ_ERR_UNSUPPORTED;
+    if (dtype == TQ_DTYPE_F32 || q_heads / cache->kv_heads > TQ_MAX_GROUPS) return TQ_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)workspace | (uintptr_t)k_new | (uintptr_t)v_new) & 15) return TQ_ERR_ARG;
     if ((uintptr_t)pos_dev & 3) return TQ_ERR_ARG;
     if (workspace_bytes < tq_decode_workspace_bytes(cache->batch, q_heads, n_splits)) return TQ_ERR_WORKSPACE;

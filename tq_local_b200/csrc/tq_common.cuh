@@ -116,10 +116,6 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
                                const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
                                const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
                                void *workspace, void *out, cudaStream_t stream);
-int32_t tq_launch_decode_mma(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
-                             const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
-                             const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
-                             void *workspace, void *out, cudaStream_t stream);
 int tq_mma4_tokens_per_cta_step();
 int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
                               const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,

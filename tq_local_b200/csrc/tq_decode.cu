@@ -310,7 +310,10 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
     __shared__ float s_o[4][TQ_D];
     __shared__ float s_part[4][4][TQ_D];  // [quarter of d][head][column]
     __shared__ float s_L[4];
-    const int64_t R = blockIdx.x;
+    const int groups = (a.G + 3) >> 2;           // a block serves up to four heads of a KV row
+    const int64_t R = blockIdx.x / groups;
+    const int h0 = 4 * (blockIdx.x % groups);
+    const int n_heads = a.G - h0 < 4 ? a.G - h0 : 4;
     const int tid = threadIdx.x, e = tid & (TQ_D - 1), dq = tid >> 7;
     float rv[32];  // this thread's un-rotation elements, fetched while the decode kernel drains
     tq_load_column(rv, a.rot_v, dq, e);
@@ -329,8 +332,8 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
     {   // thread (e, dq) merges the splits of head dq
         const int g = dq;
         float o = 0.f, L = 0.f;
-        if (g < a.G) {
-            const int64_t row = R * a.G + g;
+        if (g < n_heads) {
+            const int64_t row = R * a.G + h0 + g;
             float M = -INFINITY;
             for (int s = 0; s < n_valid; ++s) M = fmaxf(M, a.part_m[row * a.n_splits + s]);
             for (int s = 0; s < n_valid; ++s) {
@@ -356,10 +359,10 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
         for (int g = 0; g < 4; ++g) s_part[dq][g][e] = out[g];
     }
     __syncthreads();
-    if (dq < a.G) {
+    if (dq < n_heads) {
         const int g = dq;
         const float v = (s_part[0][g][e] + s_part[1][g][e]) + (s_part[2][g][e] + s_part[3][g][e]);
-        ((T *)a.out)[(R * a.G + g) * TQ_D + e] = tq_from_float<T>(v / fmaxf(s_L[g], 1e-8f));
+        ((T *)a.out)[(R * a.G + h0 + g) * TQ_D + e] = tq_from_float<T>(v / fmaxf(s_L[g], 1e-8f));
     }
 }
 
@@ -411,7 +414,7 @@ int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t row
 
 template <typename T>
 static cudaError_t launch_prologue(tq_ctx *ctx, const TqQprepArgs &qa, const TqPackArgs *append, cudaStream_t stream) {
-    const int n_qprep = (int)qa.kv_rows * (qa.use_qjl ? 2 : 1);
+    const int n_qprep = (int)qa.kv_rows * ((qa.G + 3) / 4) * (qa.use_qjl ? 2 : 1);
     if (!append) return tq_launch_kernel(tq_qprep_frag_kernel<T>, dim3(n_qprep), dim3(4 * TQ_D), 0, stream, false, qa);
     const int n_pack = append->n_kinds * append->B * append->H * append->S;
     if (ctx->use_qjl)
@@ -424,7 +427,7 @@ static cudaError_t launch_prologue(tq_ctx *ctx, const TqQprepArgs &qa, const TqP
 int32_t tq_launch_qprep_frag(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t kv_rows, int G, uint32_t *frag,
                              const TqPackArgs *append, cudaStream_t stream) {
     configure_small_kernels();
-    if (G > 4) return TQ_ERR_UNSUPPORTED;
+    if (G > 8) return TQ_ERR_UNSUPPORTED;
     TqQprepArgs qa;
     qa.q = q, qa.rot_k_t = ctx->rot_k_t, qa.qjl_t = ctx->qjl_t, qa.frag = frag;
     qa.G = G, qa.use_qjl = ctx->use_qjl, qa.kv_rows = kv_rows;
@@ -437,8 +440,8 @@ int32_t tq_launch_qprep_frag(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_
 }
 
 int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, cudaStream_t stream, bool programmatic) {
-    if (a.n_tail == 0 && a.G <= 4) {  // grouped variant: one block per KV row
-        const dim3 grid((unsigned)(rows / a.G)), block(4 * TQ_D);
+    if (a.n_tail == 0 && a.G <= 8) {  // grouped variant: one block per four heads of a KV row
+        const dim3 grid((unsigned)(rows / a.G) * ((a.G + 3) / 4)), block(4 * TQ_D);
         cudaError_t e;
         if (q_dtype == TQ_DTYPE_F32) e = tq_launch_kernel(tq_combine_group_kernel<float>, grid, block, 0, stream, programmatic, a);
         else if (q_dtype == TQ_DTYPE_F16) e = tq_launch_kernel(tq_combine_group_kernel<__half>, grid, block, 0, stream, programmatic, a);

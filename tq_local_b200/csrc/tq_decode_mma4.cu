@@ -158,8 +158,13 @@ template <int VB> __device__ __forceinline__ uint64_t lds_v_chunk(const uint8_t 
     }
 }
 
-template <int KB, int VB, bool QJL>
+// WIDE = false: G <= 4 query heads per KV head, MMA columns = (head, hi / lo term of the query).
+// WIDE = true : G <= 8, MMA columns = heads; the rotated query is a single f16 term and the two
+//               s8 terms of the projected query go through two integer MMAs.  A lane then owns
+//               two heads (columns 2t and 2t + 1) in the softmax and all four accumulator columns.
+template <int KB, int VB, bool QJL, bool WIDE>
 __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args a) {
+    constexpr int NH = WIDE ? 2 : 1;  // heads per lane
     using L = StageLayout<KB, VB, QJL>;
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int kEntries = 256;  // indexed by a whole byte; bits beyond the field are ignored
@@ -297,15 +302,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         first_segment = false;
     }
 
-    // ---- B fragments: column g = (head g/2, part g%2)
-    const int hcol = g >> 1, part = g & 1;
+    // ---- B fragments: column g = (head g/2, part g%2), or head g in the wide variant
+    const int hcol = WIDE ? g : g >> 1, part = WIDE ? 0 : g & 1;
     const bool live = hcol < G;
     uint32_t bq[8][2];
-    uint32_t bp[QJL ? 4 : 1][2];
-    float sign_scale = 0.f, sign_bias = 0.f;  // for the head this lane owns in the softmax (head t)
+    uint32_t bp[QJL ? 4 * NH : 1][2];  // wide: [0, 4) hi terms, [4, 8) lo terms
+    float sign_scale[NH], sign_bias[NH];  // for the heads this lane owns in the softmax
     {
-        const uint2 *fr = reinterpret_cast<const uint2 *>(a.frag + (q_row0 + (live ? hcol : 0)) * TQ_FRAG_ROW_WORDS +
-                                                          (part * 4 + t) * 26);
+        const uint32_t *head_frag = a.frag + (q_row0 + (live ? hcol : 0)) * TQ_FRAG_ROW_WORDS;
+        const uint2 *fr = reinterpret_cast<const uint2 *>(head_frag + (part * 4 + t) * 26);
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
             const uint2 v = __ldg(fr + s);
@@ -317,12 +322,26 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                 const uint2 v = __ldg(fr + 8 + n);
                 bp[n][0] = live ? v.x : 0u, bp[n][1] = live ? v.y : 0u;
             }
-            const uint32_t *mine = a.frag + (q_row0 + (t < G ? t : 0)) * TQ_FRAG_ROW_WORDS;
-            sign_scale = __uint_as_float(__ldg(mine + 24));
-            sign_bias = __uint_as_float(__ldg(mine + 25));
+            if (WIDE) {
+                const uint2 *fl = reinterpret_cast<const uint2 *>(head_frag + (4 + t) * 26);
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    const uint2 v = __ldg(fl + 8 + n);
+                    bp[(QJL && WIDE ? 4 : 0) + n][0] = live ? v.x : 0u, bp[(QJL && WIDE ? 4 : 0) + n][1] = live ? v.y : 0u;
+                }
+            }
+        }
+#pragma unroll
+        for (int hl = 0; hl < NH; ++hl) {
+            const int head = WIDE ? 2 * t + hl : t;
+            const uint32_t *mine = a.frag + (q_row0 + (head < G ? head : 0)) * TQ_FRAG_ROW_WORDS;
+            sign_scale[hl] = QJL ? __uint_as_float(__ldg(mine + 24)) : 0.f;
+            sign_bias[hl] = QJL ? __uint_as_float(__ldg(mine + 25)) : 0.f;
         }
     }
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run[NH], l_run[NH];
+#pragma unroll
+    for (int hl = 0; hl < NH; ++hl) m_run[hl] = -INFINITY, l_run[hl] = 0.f;
     float o[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -344,7 +363,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         const uint16_t *rn = reinterpret_cast<const uint16_t *>(slot + L::kRN) + wq * kStageTok;
 
         // ------------------------------------------------------------ logits
-        float lg[2][2];
+        float lg[2][2][NH];  // [tile][token A / B][head of this lane]
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             // token slot s of the tile holds token pi(s): pi(2j) = j, pi(2j+1) = j+4, pi(s+8) = pi(s)+8,
@@ -369,12 +388,21 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                 const uint32_t a3 = lds_abs(slot_addr(wb, o1, lane_k));
                 mma_f16(d1, a0, a1, a2, a3, bq[s][0], bq[s][1]);
             }
-            float lgA = tq_half_bits_to_float(kn[slotA]) * kA * (d1[0] + d1[1]);
-            float lgB = tq_half_bits_to_float(kn[slotB]) * kA * (d1[2] + d1[3]);
+            float lgA[NH], lgB[NH];
+            {
+                const float knA = tq_half_bits_to_float(kn[slotA]) * kA, knB = tq_half_bits_to_float(kn[slotB]) * kA;
+                if (WIDE) {
+#pragma unroll
+                    for (int hl = 0; hl < NH; ++hl) lgA[hl] = knA * d1[hl], lgB[hl] = knB * d1[2 + hl];
+                } else {
+                    lgA[0] = knA * (d1[0] + d1[1]), lgB[0] = knB * (d1[2] + d1[3]);
+                }
+            }
             if (QJL) {
                 const uint32_t sa = reinterpret_cast<const uint32_t *>(spS + slotA * 16)[t];
                 const uint32_t sb = reinterpret_cast<const uint32_t *>(spS + slotB * 16)[t];
                 int d2[4] = {0, 0, 0, 0};
+                int d2l[4] = {0, 0, 0, 0};  // wide: the lo-term products
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
                     const uint32_t a0 = prmt(sa << (2 * n), 0u, 0xBA98u);
@@ -382,46 +410,67 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                     const uint32_t a2 = prmt(sa << (2 * n + 1), 0u, 0xBA98u);
                     const uint32_t a3 = prmt(sb << (2 * n + 1), 0u, 0xBA98u);
                     mma_s8(d2, a0, a1, a2, a3, bp[n][0], bp[n][1]);
+                    if (WIDE) mma_s8(d2l, a0, a1, a2, a3, bp[(WIDE ? 4 : 0) + n][0], bp[(WIDE ? 4 : 0) + n][1]);
                 }
-                const float sA = fmaf((float)(d2[0] * 256 + d2[1]), sign_scale, sign_bias);
-                const float sB = fmaf((float)(d2[2] * 256 + d2[3]), sign_scale, sign_bias);
-                lgA = fmaf(tq_half_bits_to_float(rn[slotA]) * kB, sA, lgA);
-                lgB = fmaf(tq_half_bits_to_float(rn[slotB]) * kB, sB, lgB);
-            }
-            if (tail) {  // rows past the range hold stale bytes
-                if (base + slotA >= t_end) lgA = -INFINITY;
-                if (base + slotB >= t_end) lgB = -INFINITY;
-            }
-            // (lanes whose head t >= G see a zero query: their state is never read)
-            lg[i][0] = lgA, lg[i][1] = lgB;
-        }
-        // ------------------------------------------------------------ online softmax (base 2), head t
-        float mx = fmaxf(fmaxf(lg[0][0], lg[0][1]), fmaxf(lg[1][0], lg[1][1]));
+                const float rnA = tq_half_bits_to_float(rn[slotA]) * kB, rnB = tq_half_bits_to_float(rn[slotB]) * kB;
 #pragma unroll
-        for (int sft = 4; sft <= 16; sft <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
-        const float nm = fmaxf(m_run, mx);
-        if (__any_sync(0xffffffffu, nm > m_run)) {
+                for (int hl = 0; hl < NH; ++hl) {
+                    const int xa = WIDE ? d2[hl] * 256 + d2l[hl] : d2[0] * 256 + d2[1];
+                    const int xb = WIDE ? d2[2 + hl] * 256 + d2l[2 + hl] : d2[2] * 256 + d2[3];
+                    lgA[hl] = fmaf(rnA, fmaf((float)xa, sign_scale[hl], sign_bias[hl]), lgA[hl]);
+                    lgB[hl] = fmaf(rnB, fmaf((float)xb, sign_scale[hl], sign_bias[hl]), lgB[hl]);
+                }
+            }
+#pragma unroll
+            for (int hl = 0; hl < NH; ++hl) {
+                if (tail) {  // rows past the range hold stale bytes
+                    if (base + slotA >= t_end) lgA[hl] = -INFINITY;
+                    if (base + slotB >= t_end) lgB[hl] = -INFINITY;
+                }
+                // (lanes whose head >= G see a zero query: their state is never read)
+                lg[i][0][hl] = lgA[hl], lg[i][1][hl] = lgB[hl];
+            }
+        }
+        // ------------------------------------------------------------ online softmax (base 2), this lane's heads
+        float nm[NH];
+        bool grew = false;
+#pragma unroll
+        for (int hl = 0; hl < NH; ++hl) {
+            float mx = fmaxf(fmaxf(lg[0][0][hl], lg[0][1][hl]), fmaxf(lg[1][0][hl], lg[1][1][hl]));
+#pragma unroll
+            for (int sft = 4; sft <= 16; sft <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
+            nm[hl] = fmaxf(m_run[hl], mx);
+            grew |= nm[hl] > m_run[hl];
+        }
+        if (__any_sync(0xffffffffu, grew)) {
             // every iteration holds at least one real token, so nm is finite; exp2(-inf) = 0
-            const float sc = fast_exp2(m_run - nm);
-            l_run *= sc;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i][0] *= sc, o[i][2] *= sc;
-            m_run = nm;
+            for (int hl = 0; hl < NH; ++hl) {
+                const float sc = fast_exp2(m_run[hl] - nm[hl]);
+                l_run[hl] *= sc;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i][hl] *= sc, o[i][2 + hl] *= sc;
+                m_run[hl] = nm[hl];
+            }
         }
-        const float sub = m_run;
         uint32_t pb[2][2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int slotA = 16 * i + (g >> 1) + 4 * (g & 1);
             const float vnA = tq_half_bits_to_float(vn[slotA]), vnB = tq_half_bits_to_float(vn[slotA + 8]);
-            const float pA = fast_exp2(lg[i][0] - sub), pB = fast_exp2(lg[i][1] - sub);
-            l_run += pA + pB;
-            // rows = token slots, cols = (head t, unused) -> transpose to rows = columns.
-            // (a masked token's staged norm may be stale and not finite)
-            float wA = pA * vnA, wB = pB * vnB;
-            if (tail) wA = pA > 0.f ? wA : 0.f, wB = pB > 0.f ? wB : 0.f;
-            pb[i][0] = movmatrix_trans(pack_half2(wA, 0.f));
-            pb[i][1] = movmatrix_trans(pack_half2(wB, 0.f));
+            float wA[2] = {0.f, 0.f}, wB[2] = {0.f, 0.f};
+#pragma unroll
+            for (int hl = 0; hl < NH; ++hl) {
+                const float pA = fast_exp2(lg[i][0][hl] - m_run[hl]), pB = fast_exp2(lg[i][1][hl] - m_run[hl]);
+                l_run[hl] += pA + pB;
+                // (a masked token's staged norm may be stale and not finite)
+                wA[hl] = pA * vnA, wB[hl] = pB * vnB;
+                if (tail) wA[hl] = pA > 0.f ? wA[hl] : 0.f, wB[hl] = pB > 0.f ? wB[hl] : 0.f;
+            }
+            // rows = token slots, cols = this lane's heads (narrow: head t and an unused column)
+            // -> transpose to rows = columns
+            pb[i][0] = movmatrix_trans(pack_half2(wA[0], wA[1]));
+            pb[i][1] = movmatrix_trans(pack_half2(wB[0], wB[1]));
         }
         // ------------------------------------------------------------ values
 #pragma unroll
@@ -471,30 +520,37 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     float *s_m = s_acc + kWarps * 4 * TQ_D;           // [kWarps][4]
     float *s_l = s_m + kWarps * 4;
 #pragma unroll
-    for (int sft = 4; sft <= 16; sft <<= 1) l_run += __shfl_xor_sync(0xffffffffu, l_run, sft);
-    if (g == 0) s_m[warp * 4 + t] = m_run, s_l[warp * 4 + t] = l_run;
+    for (int hl = 0; hl < NH; ++hl) {  // the wide variant merges its even heads, then its odd heads
+        if (hl) __syncthreads();
+        float l_all = l_run[hl];
 #pragma unroll
-    for (int mt = 0; mt < 8; ++mt) {
-        float *r = s_acc + (warp * 4 + t) * TQ_D + 16 * g + 2 * mt;
-        r[0] = o[mt][0], r[1] = o[mt][2];
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < G * TQ_D; idx += blockDim.x) {
-        const int hh = idx / TQ_D, d = idx % TQ_D;
-        float M = -INFINITY;
+        for (int sft = 4; sft <= 16; sft <<= 1) l_all += __shfl_xor_sync(0xffffffffu, l_all, sft);
+        if (g == 0) s_m[warp * 4 + t] = m_run[hl], s_l[warp * 4 + t] = l_all;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w * 4 + hh]);
-        float Lsum = 0.f, A = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            const float mw = s_m[w * 4 + hh];
-            const float sc = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-            Lsum += s_l[w * 4 + hh] * sc;
-            A += s_acc[(w * 4 + hh) * TQ_D + d] * sc;
+        for (int mt = 0; mt < 8; ++mt) {
+            float *r = s_acc + (warp * 4 + t) * TQ_D + 16 * g + 2 * mt;
+            r[0] = o[mt][hl], r[1] = o[mt][2 + hl];
         }
-        const int64_t prow = (q_row0 + hh) * a.n_splits + split;
-        a.part_acc[prow * TQ_D + d] = A;
-        if (d == 0) a.part_m[prow] = M * 0.6931471805599453f, a.part_l[prow] = Lsum;  // natural-log units
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 4 * TQ_D; idx += blockDim.x) {
+            const int tt = idx / TQ_D, d = idx % TQ_D;
+            const int hh = WIDE ? 2 * tt + hl : tt;
+            if (hh >= G) continue;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w * 4 + tt]);
+            float Lsum = 0.f, A = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float mw = s_m[w * 4 + tt];
+                const float sc = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+                Lsum += s_l[w * 4 + tt] * sc;
+                A += s_acc[(w * 4 + tt) * TQ_D + d] * sc;
+            }
+            const int64_t prow = (q_row0 + hh) * a.n_splits + split;
+            a.part_acc[prow * TQ_D + d] = A;
+            if (d == 0) a.part_m[prow] = M * 0.6931471805599453f, a.part_l[prow] = Lsum;  // natural-log units
+        }
     }
     __syncthreads();  // the merge buffer is free again before the next segment refills the rings
     }  // segment loop
@@ -503,17 +559,23 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
 
 template <int KB, int VB, bool QJL> size_t mma4_smem_bytes() { return 227 * 1024; }
 
-template <int KB, int VB, bool QJL> cudaError_t launch_mma4(const Mma4Args &a, dim3 grid, cudaStream_t stream) {
+template <int KB, int VB, bool QJL, bool WIDE>
+cudaError_t launch_mma4_variant(const Mma4Args &a, dim3 grid, cudaStream_t stream) {
     const size_t smem = mma4_smem_bytes<KB, VB, QJL>();
     static bool configured = false;  // per instantiation
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(tq_decode_mma4_kernel<KB, VB, QJL>,
+        cudaError_t e = cudaFuncSetAttribute(tq_decode_mma4_kernel<KB, VB, QJL, WIDE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    return tq_launch_kernel(tq_decode_mma4_kernel<KB, VB, QJL>, grid, dim3(kWarps * 32), smem, stream,
+    return tq_launch_kernel(tq_decode_mma4_kernel<KB, VB, QJL, WIDE>, grid, dim3(kWarps * 32), smem, stream,
                             /*programmatic=*/true, a);
+}
+
+template <int KB, int VB, bool QJL> cudaError_t launch_mma4(const Mma4Args &a, dim3 grid, cudaStream_t stream) {
+    return a.G > 4 ? launch_mma4_variant<KB, VB, QJL, true>(a, grid, stream)
+                   : launch_mma4_variant<KB, VB, QJL, false>(a, grid, stream);
 }
 
 }  // namespace

@@ -80,9 +80,6 @@ extern "C" int32_t tq_decode_attn_static(tq_ctx *ctx, const void *q, int32_t q_d
     if (q_dtype == TQ_DTYPE_F32)
         return tq_launch_decode_exact(ctx, q, q_dtype, q_heads, cache, seq_len, nullptr, nullptr, 0, n_splits, scratch,
                                       out, s);
-    if (groups <= 4)
-        return tq_launch_decode_mma4(ctx, q, q_dtype, q_heads, cache, seq_len, nullptr, nullptr, 0, n_splits, scratch,
-                                     out, s);
-    return tq_launch_decode_mma(ctx, q, q_dtype, q_heads, cache, seq_len, nullptr, nullptr, 0, n_splits, scratch, out,
-                                s);
+    return tq_launch_decode_mma4(ctx, q, q_dtype, q_heads, cache, seq_len, nullptr, nullptr, 0, n_splits, scratch, out,
+                                 s);
 }

@@ -183,10 +183,11 @@ template <typename T, bool QJL> __device__ __forceinline__ void tq_pack_small_bl
 }
 
 // ---------------------------------------------------------------------------------------------
-// Query preparation for the tensor-core decode kernel.  Block `blk` < kv_rows rotates the G
-// query heads of KV row `blk` (q @ R_k^T) and writes their f16 hi / lo MMA fragments;
-// block kv_rows + r projects the heads of row r (q @ S^T), quantises the result to 16-bit
-// fixed point and writes its s8 hi / lo fragments with the scale and bias that undo it.
+// Query preparation for the tensor-core decode kernel.  A block serves up to four query heads
+// of one KV row (a row with G > 4 heads takes two blocks).  The first kv_rows * ceil(G / 4)
+// blocks rotate their heads (q @ R_k^T) and write the f16 hi / lo MMA fragments; the next
+// kv_rows * ceil(G / 4) blocks project them (q @ S^T), quantise the result to 16-bit fixed
+// point and write the s8 hi / lo fragments with the scale and bias that undo it.
 // Fragment layout per head: 8 lane variants (part * 4 + t) of 26 words: 16 rotated-query
 // words, 8 projected-query words, scale, bias.
 template <typename T> __device__ __forceinline__ void tq_qprep_block(const TqQprepArgs &a, int64_t blk) {
@@ -194,14 +195,18 @@ template <typename T> __device__ __forceinline__ void tq_qprep_block(const TqQpr
     __shared__ float s_part[4][4][TQ_D];  // [quarter of d][head][column]
     __shared__ int s_x[4][TQ_D];
     __shared__ float s_scale[4], s_bias[4];
-    const bool proj = blk >= a.kv_rows;
-    const int64_t R = proj ? blk - a.kv_rows : blk;
-    const int G = a.G;
+    const int groups = (a.G + 3) >> 2;  // blocks per KV row
+    const bool proj = blk >= a.kv_rows * groups;
+    const int64_t item = proj ? blk - a.kv_rows * groups : blk;
+    const int64_t R = item / groups;
+    const int h0 = 4 * (int)(item % groups);                  // first head of this block
+    const int G = a.G - h0 < 4 ? a.G - h0 : 4;                // heads of this block
+    const int64_t head0 = R * a.G + h0;                       // their first row in q / frag
     const int tid = threadIdx.x, j = tid & (TQ_D - 1), dq = tid >> 7;
     const int warp = tid >> 5, lane = tid & 31;
     float m[32];
     tq_load_column(m, proj ? a.qjl_t : a.rot_k_t, dq, j);
-    if (dq < G) s_q[dq][j] = tq_to_float<T>(((const T *)a.q)[(R * G + dq) * TQ_D + j]);
+    if (dq < G) s_q[dq][j] = tq_to_float<T>(((const T *)a.q)[(head0 + dq) * TQ_D + j]);
     __syncthreads();
     {
         float r[4] = {0.f, 0.f, 0.f, 0.f};
@@ -231,7 +236,7 @@ template <typename T> __device__ __forceinline__ void tq_qprep_block(const TqQpr
                 x[i] = part ? (v - hi) : hi;
             }
             const __half2 hh = __floats2half2_rn(x[0], x[1]);
-            a.frag[(R * G + hcol) * TQ_FRAG_ROW_WORDS + (variant & 7) * 26 + k] = *reinterpret_cast<const uint32_t *>(&hh);
+            a.frag[(head0 + hcol) * TQ_FRAG_ROW_WORDS + (variant & 7) * 26 + k] = *reinterpret_cast<const uint32_t *>(&hh);
         }
         return;
     }
@@ -273,6 +278,6 @@ template <typename T> __device__ __forceinline__ void tq_qprep_block(const TqQpr
         } else {
             word = __float_as_uint(k == 8 ? s_scale[hcol] : s_bias[hcol]);
         }
-        a.frag[(R * G + hcol) * TQ_FRAG_ROW_WORDS + (variant & 7) * 26 + 16 + k] = word;
+        a.frag[(head0 + hcol) * TQ_FRAG_ROW_WORDS + (variant & 7) * 26 + 16 + k] = word;
     }
 }

@@ -245,10 +245,10 @@ class PackedMSELayer(CacheLayerMixin):
     # ---------------------------------------------------------------- replayable decode
     def supports_static_decode(self, q_heads: int) -> bool:
         """Whether this layer can serve decode steps whose length lives on the device (packed,
-        quantised appends, 16-bit cache, at most 4 query heads per KV head, not sharded)."""
+        quantised appends, 16-bit cache, at most 8 query heads per KV head, not sharded)."""
         return (self.store is not None and not self._force_dense and self.quantize_decode
                 and self._dense_k.length == 0 and self.dtype in (torch.float16, torch.bfloat16)
-                and self.shard.world_size == 1 and q_heads // self._kv_heads_total <= 4)
+                and self.shard.world_size == 1 and q_heads // self._kv_heads_total <= 8)
 
     def begin_static_decode(self, pos: torch.Tensor, max_new_tokens: int) -> None:
         """Switch to decode steps that read the cache length from the int32 device scalar ``pos``

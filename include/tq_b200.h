@@ -175,6 +175,46 @@ int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32
 int32_t tq_key_norm_sum(const tq_dense_desc *k, int32_t batch, int32_t heads, int32_t n_tokens,
                         double *sum_out, tq_stream stream);
 
+/* ---- KV-head sharding over the GPUs of one box (no counterpart in the reference, which is
+ * single-GPU).  Rank r serves kv_heads / world KV heads and their query heads; the only exchange
+ * per decode step is the per-head attention outputs.  tq_decode_attn_gather fuses that exchange
+ * into the combine kernel: every block stores its finished rows straight into the gathered-output
+ * buffer of EVERY rank (plain stores to peer memory over NVLink), the last block of a rank raises
+ * that rank's flag in every peer, and tq_gather_wait (one small kernel, stream-ordered before the
+ * consumer of the gathered output) waits - with a time limit, reporting through tq_device_status
+ * (5) instead of hanging - until all ranks' flags show the step's sequence number.
+ *
+ * Buffers come from tq_peer_buffer_create (device memory that other processes on the box can
+ * map): exchange the 64-byte handles by any host-side means and map the peers' buffers with
+ * tq_peer_buffer_open.  A rank needs: two gathered-output buffers (steps alternate between them,
+ * so a fast rank never overwrites what a slow rank still reads) of batch * q_heads_total * 128
+ * elements each, and one flag block of TQ_MAX_PEERS uint32 (zero-initialised); plus a local
+ * zero-initialised uint32 counter. */
+#define TQ_MAX_PEERS 8
+typedef struct tq_gather_desc {
+    int32_t world, rank;
+    int32_t q_heads_total;          /* query heads of the whole model (all ranks) */
+    uint32_t seq;                   /* step sequence number: 1, 2, 3, ... (the same on all ranks) */
+    void *out[TQ_MAX_PEERS];        /* out[r]: rank r's gathered-output buffer for THIS step (as mapped here) */
+    uint32_t *flags[TQ_MAX_PEERS];  /* flags[r]: rank r's flag block (as mapped here); entry [rank] is ours */
+    uint32_t *counter;              /* local scratch word, zero between calls */
+} tq_gather_desc;
+
+int32_t tq_peer_buffer_create(size_t bytes, void **dev_ptr, void *handle64_out);
+int32_t tq_peer_buffer_open(const void *handle64, void **dev_ptr);
+int32_t tq_peer_buffer_close(void *dev_ptr);
+int32_t tq_peer_buffer_destroy(void *dev_ptr);
+
+/* tq_decode_attn without a dense tail, for 16-bit queries, with the output rows
+ * [batch, q_heads, 128] of this rank written at head offset rank * q_heads into every rank's
+ * gathered buffer [batch, q_heads_total, 128]. */
+int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                              const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits,
+                              void *workspace, size_t workspace_bytes, const tq_gather_desc *gather,
+                              tq_stream stream);
+/* Stream-ordered wait for all ranks' flags of step gather->seq (see above). */
+int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, tq_stream stream);
+
 /* Decode attention for callers that cannot allocate (no counterpart in the reference).
  * Same computation and arguments as tq_decode_attn without a dense tail, but the scratch
  * lives in an 8 MiB array built into the library instead of a caller workspace: use it from
@@ -194,7 +234,8 @@ int32_t tq_decode_attn_static(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
  * call synchronises with the device and returns that word: 0 = no kernel ever gave up;
  * 1 = a decode kernel's wait ran out; 2 = a decode kernel found that its shared-memory layout
  * does not fit and did not run; 3 = the encoder's wait ran out; 4 = an append addressed a
- * token past the cache's capacity and was dropped.  The word is sticky for the context. */
+ * token past the cache's capacity and was dropped; 5 = tq_gather_wait gave up waiting for a peer.
+ * The word is sticky for the context. */
 int32_t tq_device_status(tq_ctx *ctx, int32_t *status_out);
 
 /* Measurement hooks (no reference counterpart; used by the benchmark).  While enabled, each

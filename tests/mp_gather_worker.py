@@ -1,0 +1,51 @@
+"""Worker of the 2-GPU gather test (one process per GPU, launched by torchrun): KV-head sharded
+decode attention with the fused peer gather must equal the NCCL all-gather of the same outputs."""
+
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main() -> None:
+    from tq_local_b200.runtime.codec import Codec
+    from tq_local_b200.runtime.packed_store import PackedStore
+    from tq_local_b200.runtime.sharding import HeadShard, PeerGather
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    shard = HeadShard.from_process_group()
+    B, Hq, Hkv, N, steps = 3, 16, 4, 1500, 5
+    g = torch.Generator().manual_seed(7)  # identical on every rank
+    k = torch.randn(B, Hkv, N, 128, generator=g).to(torch.bfloat16).to(dev)
+    v = torch.randn(B, Hkv, N, 128, generator=g).to(torch.bfloat16).to(dev)
+    qs = torch.randn(steps, B, Hq, 1, 128, generator=g).to(torch.bfloat16).to(dev)
+    codec = Codec.get(dev, 4, True, 0)
+    store = PackedStore(codec, B, Hkv // world, capacity=N + 8)
+    store.pack(shard.local_kv(k), shard.local_kv(v))
+    gather = PeerGather(shard, B, Hq, torch.bfloat16, dev)
+    try:
+        for t in range(steps):
+            q_local = shard.local_q(qs[t], Hkv)
+            want = shard.gather_heads(store.decode_attn(q_local))  # NCCL all-gather
+            got = store.decode_attn_gather(q_local, gather)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), f"rank {rank} step {t}"
+        assert codec.device_status() == 0
+    finally:
+        gather.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("GATHER_OK")
+
+
+if __name__ == "__main__":
+    main()

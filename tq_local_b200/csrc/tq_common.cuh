@@ -41,6 +41,7 @@ struct tq_ctx {
     int *error_flag;       // device word, set by a kernel whose bounded wait ran out
     const struct TqPackArgs *pending_append;  // set by the step entry points for the next decode launch
     const int *pending_len_ptr;               // likewise: sequence length kept in device memory
+    const tq_gather_desc *pending_gather;     // likewise: write the outputs into every rank's gathered buffer
     int64_t splits_cache_key;  // last (rows, length bucket) asked of tq_decode_suggest_splits
     int splits_cache_val;
 };

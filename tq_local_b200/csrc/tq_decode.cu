@@ -362,8 +362,47 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
     if (dq < n_heads) {
         const int g = dq;
         const float v = (s_part[0][g][e] + s_part[1][g][e]) + (s_part[2][g][e] + s_part[3][g][e]);
-        ((T *)a.out)[(R * a.G + h0 + g) * TQ_D + e] = tq_from_float<T>(v / fmaxf(s_L[g], 1e-8f));
+        const T res = tq_from_float<T>(v / fmaxf(s_L[g], 1e-8f));
+        const int64_t row = R * a.G + h0 + g;  // = batch index * local query heads + local head
+        if (a.gather_world > 0) {
+            const int64_t bi = row / a.Hq, hl = row % a.Hq;
+            const int64_t dst = (bi * a.gather_heads_total + (int64_t)a.gather_rank * a.Hq + hl) * TQ_D + e;
+            for (int p = 0; p < a.gather_world; ++p) ((T *)a.gather_out[p])[dst] = res;
+        } else {
+            ((T *)a.out)[row * TQ_D + e] = res;
+        }
     }
+    if (a.gather_world > 0) {
+        // the rank's last block tells every peer that this rank's rows of the step are in place
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            if (atomicAdd(a.gather_counter, 1u) == gridDim.x - 1) {
+                *a.gather_counter = 0;
+                __threadfence_system();
+                for (int p = 0; p < a.gather_world; ++p)
+                    *reinterpret_cast<volatile unsigned *>(a.gather_flags[p] + a.gather_rank) = a.gather_seq;
+            }
+        }
+    }
+}
+
+// Waits until the flags of all ranks show the step's sequence number (written by the peers'
+// combine kernels), for at most about two seconds.
+__global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned seq, int *error_flag) {
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    const long long t0 = clock64();
+    const volatile unsigned *f = flags + p;
+    // (flags only grow; a peer may already be one step ahead)
+    while ((int)(*f - seq) < 0) {
+        if (clock64() - t0 > 4000000000ll) {
+            atomicExch(error_flag, 5);
+            return;
+        }
+        __nanosleep(200);
+    }
+    __threadfence_system();
 }
 
 // The decode kernels run with the largest shared-memory carve-out.  The small kernels around
@@ -461,6 +500,12 @@ int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, c
     return TQ_OK;
 }
 
+int32_t tq_launch_gather_wait(const unsigned *flags, int world, unsigned seq, int *error_flag, cudaStream_t stream) {
+    tq_gather_wait_kernel<<<1, 32, 0, stream>>>(flags, world, seq, error_flag);
+    TQ_CUDA_CHECK(cudaGetLastError());
+    return TQ_OK;
+}
+
 DecodeWorkspace tq_carve_workspace(void *workspace, int64_t rows, int n_splits) {
     DecodeWorkspace w;
     float *p = (float *)workspace;
@@ -517,6 +562,7 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
     c.n_splits = n_splits, c.Hq = q_heads, c.G = a.G;
     c.seg_chunk = 0, c.seg_npad = 0;
     c.len_ptr = nullptr, c.len_add = 0, c.capacity = 0, c.plan_rows = 0, c.plan_ctas = 0, c.plan_step = 0;
+    c.gather_world = 0;
     c.rot_v = ctx->rot_v;
     c.q = q, c.out = out;
     c.n_tail = n_tail;

@@ -593,7 +593,9 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     const int groups = q_heads / cache->kv_heads;
     const TqPackArgs *append = ctx->pending_append;  // this step's new token, encoded by the same launch
     const int *len_ptr = ctx->pending_len_ptr;       // sequence length kept on the device
-    ctx->pending_append = nullptr, ctx->pending_len_ptr = nullptr;
+    const tq_gather_desc *gather = ctx->pending_gather;
+    ctx->pending_append = nullptr, ctx->pending_len_ptr = nullptr, ctx->pending_gather = nullptr;
+    if (gather && n_tail) return TQ_ERR_UNSUPPORTED;
     int rc = tq_launch_qprep_frag(ctx, q, q_dtype, rows / groups, groups, frag, append, stream);
     if (rc) return rc;
 
@@ -640,6 +642,15 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     c.seg_chunk = a.chunk, c.seg_npad = a.n_pad;
     c.len_ptr = len_ptr, c.len_add = a.len_add, c.capacity = a.capacity;
     c.plan_rows = a.rows, c.plan_ctas = (int)grid.x, c.plan_step = step;
+    c.gather_world = 0;
+    if (gather) {
+        c.gather_world = gather->world, c.gather_rank = gather->rank, c.gather_heads_total = gather->q_heads_total;
+        c.gather_seq = gather->seq, c.gather_counter = gather->counter;
+        for (int p = 0; p < TQ_MAX_PEERS; ++p) {
+            c.gather_out[p] = p < gather->world ? gather->out[p] : nullptr;
+            c.gather_flags[p] = p < gather->world ? gather->flags[p] : nullptr;
+        }
+    }
     c.rot_v = ctx->rot_v;
     c.q = q, c.out = out;
     c.n_tail = n_tail;

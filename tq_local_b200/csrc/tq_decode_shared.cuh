@@ -14,6 +14,13 @@ struct CombineArgs {
     // kernel derives seg_chunk / seg_npad itself, with the plan the decode kernel used.
     const int *len_ptr;
     int len_add, capacity, plan_rows, plan_ctas, plan_step;
+    // Peer gather (KV-head sharding): when gather_world > 0 the finished rows go to every rank's
+    // gathered buffer instead of `out`, and the last block raises this rank's flag in every peer.
+    int gather_world, gather_rank, gather_heads_total;
+    unsigned gather_seq;
+    void *gather_out[TQ_MAX_PEERS];
+    unsigned *gather_flags[TQ_MAX_PEERS];
+    unsigned *gather_counter;
     const float *rot_v;  // R_v[d][e]
     const void *q;       // original-dtype query, for the dense tail
     void *out;
@@ -32,6 +39,7 @@ struct DecodeWorkspace {
 };
 
 DecodeWorkspace tq_carve_workspace(void *workspace, int64_t rows, int n_splits);
+int32_t tq_launch_gather_wait(const unsigned *flags, int world, unsigned seq, int *error_flag, cudaStream_t stream);
 int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
                         cudaStream_t stream);
 // Query preparation for the G <= 4 kernel; with `append` the same launch also encodes and

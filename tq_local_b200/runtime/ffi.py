@@ -21,6 +21,8 @@ EXPORTS = (
     "tq_decode_workspace_bytes", "tq_decode_suggest_splits", "tq_decode_attn", "tq_dequant",
     "tq_key_norm_sum", "tq_profile_enable", "tq_profile_read", "tq_device_status", "tq_static_scratch_bytes",
     "tq_decode_attn_static", "tq_decode_step_workspace_bytes", "tq_decode_step_host", "tq_decode_step_dev",
+    "tq_peer_buffer_create", "tq_peer_buffer_open", "tq_peer_buffer_close", "tq_peer_buffer_destroy",
+    "tq_decode_attn_gather", "tq_gather_wait",
 )
 
 _ERRORS = {-1: "bad argument", -2: "unsupported shape or mode", -3: "CUDA error", -4: "workspace too small"}
@@ -52,6 +54,16 @@ class DenseDesc(C.Structure):
     _fields_ = [
         ("data", C.c_void_p), ("dtype", C.c_int32),
         ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_t", C.c_int64),
+    ]
+
+
+TQ_MAX_PEERS = 8
+
+
+class GatherDesc(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32), ("q_heads_total", C.c_int32), ("seq", C.c_uint32),
+        ("out", C.c_void_p * TQ_MAX_PEERS), ("flags", C.c_void_p * TQ_MAX_PEERS), ("counter", C.c_void_p),
     ]
 
 
@@ -111,6 +123,16 @@ def lib() -> C.CDLL:
                                      C.POINTER(CacheDesc), C.c_void_p, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p,
                                      C.c_void_p]
     L.tq_decode_step_dev.restype = C.c_int32
+    L.tq_peer_buffer_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
+    L.tq_peer_buffer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    L.tq_peer_buffer_close.argtypes = [C.c_void_p]
+    L.tq_peer_buffer_destroy.argtypes = [C.c_void_p]
+    L.tq_decode_attn_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.POINTER(CacheDesc), C.c_int32,
+                                        C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(GatherDesc), C.c_void_p]
+    L.tq_gather_wait.argtypes = [C.c_void_p, C.POINTER(GatherDesc), C.c_void_p]
+    for name in ("tq_peer_buffer_create", "tq_peer_buffer_open", "tq_peer_buffer_close", "tq_peer_buffer_destroy",
+                 "tq_decode_attn_gather", "tq_gather_wait"):
+        getattr(L, name).restype = C.c_int32
     _lib = L
     return L
 

@@ -148,6 +148,30 @@ class PackedStore:
                       "tq_decode_attn")
         return out
 
+    def decode_attn_gather(self, q: torch.Tensor, gather, *, seq_len: int | None = None,
+                           splits: int | None = None) -> torch.Tensor:
+        """``decode_attn`` for a KV-head shard with the exchange fused in: ``q`` holds this rank's
+        query heads [B, Hq_local, 1, 128]; the result is the gathered output of ALL ranks
+        [B, Hq_total, 1, 128] (a view of ``gather``'s buffer for this step, valid until the
+        step after next).  ``gather`` is a ``PeerGather``; every rank must make the same calls."""
+        b, hq = int(q.shape[0]), int(q.shape[1])
+        if q.shape[-1] != 128 or q.numel() != b * hq * 128 or b != self.batch:
+            raise ValueError(f"expected a single-token query [B={self.batch}, Hq, 1, 128], got {tuple(q.shape)}")
+        qc = q.reshape(b, hq, 128)
+        if not qc.is_contiguous():
+            qc = qc.contiguous()
+        n = self.length if seq_len is None else int(seq_len)
+        splits = self.suggest_splits(n) if splits is None else int(splits)
+        ws = self._get_workspace(hq, splits)
+        desc, view = gather.next_desc()
+        stream = self._stream_ptr()
+        with torch.cuda.device(self.codec.device):
+            ffi.check(ffi.lib().tq_decode_attn_gather(self.codec.handle, qc.data_ptr(), tq_dtype(q.dtype), hq,
+                                                      C.byref(self._desc), n, splits, ws.data_ptr(), ws.numel(),
+                                                      C.byref(desc), stream), "tq_decode_attn_gather")
+            ffi.check(ffi.lib().tq_gather_wait(self.codec.handle, C.byref(desc), stream), "tq_gather_wait")
+        return view
+
     def decode_step_host(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, out: torch.Tensor,
                          splits: int | None = None) -> torch.Tensor:
         """One decode step with HOST tensors (pinned memory keeps the copies asynchronous): append

@@ -10,6 +10,7 @@ backend (NCCL on GPUs, gloo in the CPU tests).
 
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 
 import torch
@@ -76,3 +77,84 @@ class HeadShard:
         dist.all_gather_into_tensor(parts, out_local, group=self.group)
         parts = parts.view(self.world_size, b, *out_local.shape[1:])
         return parts.permute(1, 0, 2, 3, 4).reshape(b, self.world_size * hl, *out_local.shape[2:])
+
+
+class _DeviceBytes:
+    """Lets torch alias device memory that the library allocated."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerGather:
+    """Buffers for the fused gather of ``PackedStore.decode_attn_gather``: every rank owns two
+    gathered-output buffers ``[batch, q_heads_total, 1, 128]`` (steps alternate between them) and
+    a flag block, all in memory that the other ranks of the box map through CUDA IPC, so a rank's
+    combine kernel stores its rows straight into every rank's buffer over NVLink and no
+    collective library call is on the path.  Set-up exchanges the 64-byte handles with
+    ``all_gather_object``; ``world_size`` 1 works too (nothing is mapped)."""
+
+    def __init__(self, shard: HeadShard, batch: int, q_heads_total: int, dtype: torch.dtype, device: torch.device):
+        from tq_local_b200.runtime import ffi
+
+        if shard.world_size > ffi.TQ_MAX_PEERS:
+            raise ValueError(f"at most {ffi.TQ_MAX_PEERS} ranks")
+        self.shard, self.device, self.dtype = shard, torch.device(device), dtype
+        self.shape = (int(batch), int(q_heads_total), 1, 128)
+        self.out_bytes = (batch * q_heads_total * 128 * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256
+        self.total = 2 * self.out_bytes + 256
+        self.seq = 0
+        self._lib = ffi.lib()
+        base, handle = C.c_void_p(), (C.c_uint8 * 64)()
+        with torch.cuda.device(self.device):
+            ffi.check(self._lib.tq_peer_buffer_create(self.total, C.byref(base), handle), "tq_peer_buffer_create")
+        self.bases = [0] * shard.world_size
+        self.bases[shard.rank] = int(base.value)
+        if shard.world_size > 1:
+            handles = [None] * shard.world_size
+            dist.all_gather_object(handles, bytes(handle), group=shard.group)
+            for r, h in enumerate(handles):
+                if r == shard.rank:
+                    continue
+                ptr = C.c_void_p()
+                with torch.cuda.device(self.device):
+                    ffi.check(self._lib.tq_peer_buffer_open((C.c_uint8 * 64).from_buffer_copy(h), C.byref(ptr)),
+                              "tq_peer_buffer_open")
+                self.bases[r] = int(ptr.value)
+            dist.barrier(group=shard.group)  # nobody writes before everybody has mapped
+        raw = torch.as_tensor(_DeviceBytes(self.bases[shard.rank], 2 * self.out_bytes), device=self.device)
+        self._views = [raw[i * self.out_bytes:i * self.out_bytes + self._numel_bytes()].view(dtype).view(self.shape)
+                       for i in range(2)]
+
+    def _numel_bytes(self) -> int:
+        b, h, _, d = self.shape
+        return b * h * d * torch.empty((), dtype=self.dtype).element_size()
+
+    def next_desc(self):
+        """Descriptor of the next step (advances the sequence number) and the view of this rank's
+        gathered output for it."""
+        from tq_local_b200.runtime import ffi
+
+        self.seq += 1
+        parity = self.seq & 1
+        d = ffi.GatherDesc()
+        d.world, d.rank, d.q_heads_total, d.seq = self.shard.world_size, self.shard.rank, self.shape[1], self.seq
+        for r, base in enumerate(self.bases):
+            d.out[r] = base + parity * self.out_bytes
+            d.flags[r] = base + 2 * self.out_bytes
+        d.counter = self.bases[self.shard.rank] + 2 * self.out_bytes + 64
+        return d, self._views[parity]
+
+    def close(self) -> None:
+        if self._lib is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.shard.world_size > 1:
+            dist.barrier(group=self.shard.group)  # peers are done writing into this rank's memory
+        with torch.cuda.device(self.device):
+            for r, base in enumerate(self.bases):
+                if r != self.shard.rank and base:
+                    self._lib.tq_peer_buffer_close(C.c_void_p(base))
+            self._views = None
+            self._lib.tq_peer_buffer_destroy(C.c_void_p(self.bases[self.shard.rank]))
+        self._lib = None

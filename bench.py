@@ -242,8 +242,37 @@ def run_gpu_arm(args) -> None:
     out = torch.empty(batch, hq, 1, HEAD_DIM, dtype=dtype, device=dev)
     gathered = torch.empty(world, batch, hq, 1, HEAD_DIM, dtype=dtype, device=dev) if world > 1 else None
     splits = args.splits or store.suggest_splits(n_ctx)
+    # N > 1: the per-head outputs are exchanged by the combine kernel itself (stores into the peers'
+    # buffers).  If the peer buffers cannot be set up on this box, or a trial step reports a
+    # device-side problem on any rank, every rank falls back to an NCCL all-gather.
+    peer = None
+    if world > 1 and args.gather in ("auto", "p2p"):
+        from tq_local_b200.runtime.sharding import HeadShard, PeerGather
+
+        ok = torch.ones(1, device=dev)
+        try:
+            peer = PeerGather(HeadShard.from_process_group(), batch, hq * world, dtype, dev)
+        except Exception as exc:  # noqa: BLE001
+            print(f"[bench] rank {rank}: peer buffers unavailable ({exc!r})", file=sys.stderr)
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() > 0:
+            for _ in range(2):
+                store.decode_attn_gather(q, peer, seq_len=n_ctx, splits=splits)
+            torch.cuda.synchronize()
+            ok.fill_(1.0 if codec.device_status() == 0 else 0.0)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            if peer is not None:
+                peer.close()
+            peer = None
+            if args.gather == "p2p":
+                raise SystemExit("--gather p2p: the peer gather is not usable on this box")
 
     def step():
+        if peer is not None:  # the combine kernel writes every rank's gathered buffer itself
+            store.decode_attn_gather(q, peer, seq_len=n_ctx, splits=splits)
+            return
         store.decode_attn(q, seq_len=n_ctx, splits=splits, out=out)
         if world > 1:
             dist.all_gather_into_tensor(gathered, out)
@@ -340,7 +369,9 @@ def run_gpu_arm(args) -> None:
             "config": {
                 "workload": w["name"], "global_batch": batch, "q_heads": w["q_heads"], "kv_heads": w["kv_heads"],
                 "context": n_ctx, "bits": w["bits"], "mode": "Q_prod", "bytes_per_token_head": unit_bytes,
-                "parallelism": f"kv-head-shard{world}" if world > 1 else "single",
+                "parallelism": (f"kv-head-shard{world}, outputs gathered by "
+                                + ("peer stores from the combine kernel" if peer is not None else "NCCL all-gather"))
+                if world > 1 else "single",
                 "splits": splits, "l2": f"inputs larger than L2 ({unit_bytes * batch * hkv * n_ctx / 1e6:.0f} MB of packed cache per GPU per step vs 126 MB)",
             },
             "decode_tok_per_s_layer": batch / (ms * 1e-3),
@@ -503,6 +534,8 @@ def run_model_arm(args) -> None:
             "clocks": clocks,
         }
         print(json.dumps(line))
+    if peer is not None:
+        peer.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -523,6 +556,9 @@ def main() -> None:
     ap.add_argument("--workload", default="layer", choices=["layer", "model"],
                     help="layer: one attention layer's decode step (the headline metric); model: whole-model "
                          "decode tokens/s of a random-init Llama-3.1-8B over 32k-token packed caches")
+    ap.add_argument("--gather", default="auto", choices=["auto", "nccl", "p2p"],
+                    help="N > 1: how the per-head outputs are exchanged: p2p = stores into the peers' buffers fused "
+                         "into the combine kernel, nccl = NCCL all-gather, auto = p2p with a fall-back to nccl")
     ap.add_argument("--layers", type=int, default=None, help="model workload: override the layer count (smoke runs)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -105,23 +105,38 @@ class PeerGather:
         self.total = 2 * self.out_bytes + 256
         self.seq = 0
         self._lib = ffi.lib()
-        base, handle = C.c_void_p(), (C.c_uint8 * 64)()
+        self._views = None
+        # Set-up is collective: every rank takes part in every exchange below even when a step failed
+        # locally, and all ranks then fail together, so nobody is left waiting in a collective.
+        base, handle, problem = C.c_void_p(), (C.c_uint8 * 64)(), None
         with torch.cuda.device(self.device):
-            ffi.check(self._lib.tq_peer_buffer_create(self.total, C.byref(base), handle), "tq_peer_buffer_create")
+            rc = self._lib.tq_peer_buffer_create(self.total, C.byref(base), handle)
+        if rc:
+            problem = f"tq_peer_buffer_create: status {rc}"
         self.bases = [0] * shard.world_size
-        self.bases[shard.rank] = int(base.value)
+        self.bases[shard.rank] = int(base.value or 0)
         if shard.world_size > 1:
             handles = [None] * shard.world_size
-            dist.all_gather_object(handles, bytes(handle), group=shard.group)
-            for r, h in enumerate(handles):
-                if r == shard.rank:
-                    continue
-                ptr = C.c_void_p()
-                with torch.cuda.device(self.device):
-                    ffi.check(self._lib.tq_peer_buffer_open((C.c_uint8 * 64).from_buffer_copy(h), C.byref(ptr)),
-                              "tq_peer_buffer_open")
-                self.bases[r] = int(ptr.value)
-            dist.barrier(group=shard.group)  # nobody writes before everybody has mapped
+            dist.all_gather_object(handles, None if problem else bytes(handle), group=shard.group)
+            if problem is None and any(h is None for h in handles):
+                problem = "a peer could not create its buffer"
+            if problem is None:
+                for r, h in enumerate(handles):
+                    if r == shard.rank:
+                        continue
+                    ptr = C.c_void_p()
+                    with torch.cuda.device(self.device):
+                        rc = self._lib.tq_peer_buffer_open((C.c_uint8 * 64).from_buffer_copy(h), C.byref(ptr))
+                    if rc:
+                        problem = f"tq_peer_buffer_open(rank {r}): status {rc}"
+                        break
+                    self.bases[r] = int(ptr.value)
+            states = [None] * shard.world_size  # also the barrier: nobody writes before everybody has mapped
+            dist.all_gather_object(states, problem, group=shard.group)
+            problem = problem or next((f"rank {r}: {p}" for r, p in enumerate(states) if p), None)
+        if problem:
+            self._release()
+            raise ffi.TQError(f"peer buffers unavailable: {problem}")
         raw = torch.as_tensor(_DeviceBytes(self.bases[shard.rank], 2 * self.out_bytes), device=self.device)
         self._views = [raw[i * self.out_bytes:i * self.out_bytes + self._numel_bytes()].view(dtype).view(self.shape)
                        for i in range(2)]
@@ -145,16 +160,21 @@ class PeerGather:
         d.counter = self.bases[self.shard.rank] + 2 * self.out_bytes + 64
         return d, self._views[parity]
 
-    def close(self) -> None:
-        if self._lib is None:
-            return
-        torch.cuda.synchronize(self.device)
-        if self.shard.world_size > 1:
-            dist.barrier(group=self.shard.group)  # peers are done writing into this rank's memory
+    def _release(self) -> None:
         with torch.cuda.device(self.device):
             for r, base in enumerate(self.bases):
                 if r != self.shard.rank and base:
                     self._lib.tq_peer_buffer_close(C.c_void_p(base))
             self._views = None
-            self._lib.tq_peer_buffer_destroy(C.c_void_p(self.bases[self.shard.rank]))
+            if self.bases[self.shard.rank]:
+                self._lib.tq_peer_buffer_destroy(C.c_void_p(self.bases[self.shard.rank]))
         self._lib = None
+
+    def close(self) -> None:
+        """Collective: unmap the peers' buffers and free this rank's."""
+        if self._lib is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.shard.world_size > 1:
+            dist.barrier(group=self.shard.group)  # peers are done writing into this rank's memory
+        self._release()

@@ -24,7 +24,7 @@ import numpy as np
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the unmodified reference project (its root)")
     args = ap.parse_args()
     here = os.path.dirname(os.path.abspath(__file__))
     # The reference must shadow any other package called ``turboquant``.

@@ -52,6 +52,7 @@ extern "C" {
 #define TQ_MAX_GROUPS 8 /* query heads per KV head */
 
 typedef struct tq_ctx tq_ctx;
+typedef struct tq_gather_desc tq_gather_desc; /* KV-head sharding, defined below */
 typedef void *tq_stream; /* a cudaStream_t */
 
 /* Codec set-up, all pointers to HOST memory, row-major float32.
@@ -159,11 +160,14 @@ int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const void *k_host,
  * other shapes return TQ_ERR_UNSUPPORTED.  Replaces the per-token PackedMSELayer.update +
  * turboquant_attention_forward pair and the host bookkeeping between them
  * (src/turboquant/runtime/packed_qmse_cache.py:600-679, src/turboquant/runtime/attention.py:28-72,
- * src/turboquant/runtime/generation.py:140-170).  Workspace: tq_decode_workspace_bytes. */
+ * src/turboquant/runtime/generation.py:140-170).  Workspace: tq_decode_workspace_bytes.
+ * With gather != NULL (KV-head sharding, see tq_gather_desc below; gather->seq_dev must be set)
+ * the outputs of all ranks are exchanged by the combine kernel, the call also queues the wait,
+ * and out receives the gathered [batch, q_heads_total, 128] output. */
 int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_new, const void *v_new, int32_t dtype,
                            int32_t q_heads, const tq_cache_desc *cache, const int32_t *pos_dev,
                            int32_t n_splits, void *workspace, size_t workspace_bytes, void *out,
-                           tq_stream stream);
+                           const tq_gather_desc *gather, tq_stream stream);
 
 /* Dequantise tokens [pos0, pos0 + n_tokens) of the keys (which = 0) or values (which = 1)
  * into a dense [batch, kv_heads, n_tokens, 128] tensor of dtype out->dtype. */
@@ -191,14 +195,18 @@ int32_t tq_key_norm_sum(const tq_dense_desc *k, int32_t batch, int32_t heads, in
  * elements each, and one flag block of TQ_MAX_PEERS uint32 (zero-initialised); plus a local
  * zero-initialised uint32 counter. */
 #define TQ_MAX_PEERS 8
-typedef struct tq_gather_desc {
+struct tq_gather_desc {
     int32_t world, rank;
     int32_t q_heads_total;          /* query heads of the whole model (all ranks) */
-    uint32_t seq;                   /* step sequence number: 1, 2, 3, ... (the same on all ranks) */
-    void *out[TQ_MAX_PEERS];        /* out[r]: rank r's gathered-output buffer for THIS step (as mapped here) */
+    uint32_t seq;                   /* step sequence number: 1, 2, 3, ... (the same on all ranks); unused with seq_dev */
+    void *out[TQ_MAX_PEERS];        /* out[r]: the first of rank r's two gathered-output buffers (as mapped here) */
+    int64_t out_stride;             /* bytes from a rank's first buffer to its second; step s uses buffer s & 1 */
     uint32_t *flags[TQ_MAX_PEERS];  /* flags[r]: rank r's flag block (as mapped here); entry [rank] is ours */
     uint32_t *counter;              /* local scratch word, zero between calls */
-} tq_gather_desc;
+    uint32_t *seq_dev;              /* optional local device word holding the LAST completed sequence number
+                                       (zero-initialised): the step then takes its number from the device, the
+                                       combine kernel advances it, and a recorded launch sequence can be replayed */
+};
 
 int32_t tq_peer_buffer_create(size_t bytes, void **dev_ptr, void *handle64_out);
 int32_t tq_peer_buffer_open(const void *handle64, void **dev_ptr);
@@ -212,8 +220,12 @@ int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
                               const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits,
                               void *workspace, size_t workspace_bytes, const tq_gather_desc *gather,
                               tq_stream stream);
-/* Stream-ordered wait for all ranks' flags of step gather->seq (see above). */
-int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, tq_stream stream);
+/* Stream-ordered wait for all ranks' flags of the step (see above).  With out_final != NULL the
+ * gathered output [batch, q_heads_total, 128] is then copied from this rank's buffer of the step
+ * into out_final (device memory), which is what a caller needs when the step number lives on the
+ * device and it cannot know which of the two buffers was used. */
+int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, int32_t batch, int32_t dtype, void *out_final,
+                       tq_stream stream);
 
 /* Decode attention for callers that cannot allocate (no counterpart in the reference).
  * Same computation and arguments as tq_decode_attn without a dense tail, but the scratch

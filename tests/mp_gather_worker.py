@@ -41,6 +41,44 @@ def main() -> None:
         assert codec.device_status() == 0
     finally:
         gather.close()
+
+    # the same exchange inside the device-length step, numbered on the device and replayed from a
+    # CUDA graph; the reference is the un-sharded result of the NCCL path
+    N0 = N - 4
+    dev_store = PackedStore(codec, B, Hkv // world, capacity=N + 8)
+    ref_store = PackedStore(codec, B, Hkv // world, capacity=N + 8)
+    for st in (dev_store, ref_store):
+        st.pack(shard.local_kv(k[:, :, :N0]), shard.local_kv(v[:, :, :N0]))
+    gather = PeerGather(shard, B, Hq, torch.bfloat16, dev, device_sequence=True)
+    try:
+        pos = torch.tensor([N0], dtype=torch.int32, device=dev)
+        sq = torch.empty(B, Hq // world, 1, 128, dtype=torch.bfloat16, device=dev)
+        sk = torch.empty(B, Hkv // world, 1, 128, dtype=torch.bfloat16, device=dev)
+        sv = torch.empty_like(sk)
+        sout = torch.empty(B, Hq, 1, 128, dtype=torch.bfloat16, device=dev)
+        graph = None
+        for t in range(4):
+            kt, vt = shard.local_kv(k[:, :, N0 + t:N0 + t + 1]), shard.local_kv(v[:, :, N0 + t:N0 + t + 1])
+            ref_store.pack(kt, vt)
+            want = shard.gather_heads(ref_store.decode_attn(shard.local_q(qs[t], Hkv),
+                                                            splits=dev_store.suggest_splits(dev_store.capacity)))
+            sq.copy_(shard.local_q(qs[t], Hkv)), sk.copy_(kt), sv.copy_(vt)
+            if t == 0:
+                dev_store.decode_step_dev(sq, sk, sv, pos, out=sout, gather=gather)
+                pos.add_(1)
+            else:
+                if graph is None:
+                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                        dev_store.decode_step_dev(sq, sk, sv, pos, out=sout, gather=gather)
+                        pos.add_(1)
+                graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(sout, want), f"rank {rank} device-length step {t}"
+        assert codec.device_status() == 0
+    finally:
+        gather.close()
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:

@@ -41,6 +41,56 @@ def test_gather_of_one_rank_equals_plain_decode(setup_golden):
     assert codec.device_status() == 0
 
 
+def test_device_sequenced_gather_in_the_device_length_step_and_in_a_graph(setup_golden):
+    """world = 1: decode_step_dev with a PeerGather whose step numbers live on the device equals
+    the plain device-length step, eagerly and replayed from a CUDA graph (both gathered buffers
+    get used: the step number advances on the device)."""
+    from tq_local_b200.runtime.packed_store import PackedStore
+    from tq_local_b200.runtime.sharding import HeadShard, PeerGather
+
+    codec = make_codec(4, True, setup_golden)
+    B, Hq, Hkv, N0, steps = 2, 8, 2, 600, 6
+    k, v, _ = O.synth_kvq(B, Hq, Hkv, N0 + steps, 128, seed=33, dtype=torch.bfloat16)
+    k, v = k.cuda(), v.cuda()
+    g = torch.Generator().manual_seed(2)
+    qs = torch.randn(steps, B, Hq, 1, 128, generator=g).to(torch.bfloat16).cuda()
+    plain, fused = (PackedStore(codec, B, Hkv, capacity=1024) for _ in range(2))
+    for st in (plain, fused):
+        st.pack(k[:, :, :N0], v[:, :, :N0])
+    gather = PeerGather(HeadShard(), B, Hq, torch.bfloat16, codec.device, device_sequence=True)
+    try:
+        pos_a = torch.tensor([N0], dtype=torch.int32, device="cuda")
+        pos_b = pos_a.clone()
+        want = []
+        for t in range(steps):
+            want.append(plain.decode_step_dev(qs[t], k[:, :, N0 + t:N0 + t + 1], v[:, :, N0 + t:N0 + t + 1], pos_a).clone())
+            pos_a.add_(1)
+        sq, sk, sv = torch.empty_like(qs[0]), torch.empty_like(k[:, :, :1]), torch.empty_like(v[:, :, :1])
+        sout = torch.empty_like(qs[0])
+
+        def load(t):
+            sq.copy_(qs[t]), sk.copy_(k[:, :, N0 + t:N0 + t + 1]), sv.copy_(v[:, :, N0 + t:N0 + t + 1])
+
+        load(0)
+        fused.decode_step_dev(sq, sk, sv, pos_b, out=sout, gather=gather)
+        pos_b.add_(1)
+        assert torch.equal(sout, want[0])
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        load(1)
+        with torch.cuda.graph(graph):
+            fused.decode_step_dev(sq, sk, sv, pos_b, out=sout, gather=gather)
+            pos_b.add_(1)
+        for t in range(1, steps):
+            load(t)
+            graph.replay()
+            assert torch.equal(sout, want[t]), t
+        assert int(gather.seq_dev.item()) == steps
+    finally:
+        gather.close()
+    assert codec.device_status() == 0
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_gather_between_two_gpus_equals_nccl_all_gather():
     worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_gather_worker.py")

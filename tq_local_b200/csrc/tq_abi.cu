@@ -315,8 +315,11 @@ extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const vo
 extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_new, const void *v_new, int32_t dtype,
                                       int32_t q_heads, const tq_cache_desc *cache, const int32_t *pos_dev,
                                       int32_t n_splits, void *workspace, size_t workspace_bytes, void *out,
-                                      tq_stream stream) {
+                                      const tq_gather_desc *gather, tq_stream stream) {
     if (!ctx || !q || !k_new || !v_new || !out || !workspace || !pos_dev) return TQ_ERR_ARG;
+    if (gather && (!gather->seq_dev || gather->world < 1 || gather->world > TQ_MAX_PEERS ||
+                   gather->q_heads_total != q_heads * gather->world))
+        return TQ_ERR_ARG;
     int32_t rc = check_cache(ctx, cache);
     if (rc) return rc;
     if (dtype < 0 || dtype > 2 || n_splits < 1) return TQ_ERR_ARG;
@@ -332,10 +335,12 @@ extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_
     append.pos_ptr = pos_dev;
     ctx->pending_append = &append;
     ctx->pending_len_ptr = pos_dev;
+    ctx->pending_gather = gather;
     rc = tq_launch_decode_mma4(ctx, q, dtype, q_heads, cache, cache->capacity, nullptr, nullptr, 0, n_splits, workspace,
-                               out, (cudaStream_t)stream);
-    ctx->pending_append = nullptr, ctx->pending_len_ptr = nullptr;
-    return rc;
+                               gather ? nullptr : out, (cudaStream_t)stream);
+    ctx->pending_append = nullptr, ctx->pending_len_ptr = nullptr, ctx->pending_gather = nullptr;
+    if (rc || !gather) return rc;
+    return tq_gather_wait(ctx, gather, cache->batch, dtype, out, stream);
 }
 
 extern "C" int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,

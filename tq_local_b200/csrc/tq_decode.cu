@@ -365,9 +365,12 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
         const T res = tq_from_float<T>(v / fmaxf(s_L[g], 1e-8f));
         const int64_t row = R * a.G + h0 + g;  // = batch index * local query heads + local head
         if (a.gather_world > 0) {
+            const unsigned seq = a.gather_seq_ptr ? *a.gather_seq_ptr + 1u : a.gather_seq;
+            const long long buf = (seq & 1u) ? a.gather_out_stride : 0;
             const int64_t bi = row / a.Hq, hl = row % a.Hq;
             const int64_t dst = (bi * a.gather_heads_total + (int64_t)a.gather_rank * a.Hq + hl) * TQ_D + e;
-            for (int p = 0; p < a.gather_world; ++p) ((T *)a.gather_out[p])[dst] = res;
+            for (int p = 0; p < a.gather_world; ++p)
+                reinterpret_cast<T *>(static_cast<char *>(a.gather_out[p]) + buf)[dst] = res;
         } else {
             ((T *)a.out)[row * TQ_D + e] = res;
         }
@@ -377,32 +380,45 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
         __threadfence_system();
         __syncthreads();
         if (tid == 0) {
-            if (atomicAdd(a.gather_counter, 1u) == gridDim.x - 1) {
+            const unsigned seq = a.gather_seq_ptr ? *a.gather_seq_ptr + 1u : a.gather_seq;
+            if (atomicAdd(a.gather_counter, 1u) == gridDim.x - 1) {  // every block has read the step number
                 *a.gather_counter = 0;
                 __threadfence_system();
                 for (int p = 0; p < a.gather_world; ++p)
-                    *reinterpret_cast<volatile unsigned *>(a.gather_flags[p] + a.gather_rank) = a.gather_seq;
+                    *reinterpret_cast<volatile unsigned *>(a.gather_flags[p] + a.gather_rank) = seq;
+                if (a.gather_seq_ptr) *const_cast<unsigned *>(a.gather_seq_ptr) = seq;
             }
         }
     }
 }
 
 // Waits until the flags of all ranks show the step's sequence number (written by the peers'
-// combine kernels), for at most about two seconds.
-__global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned seq, int *error_flag) {
-    const int p = threadIdx.x;
-    if (p >= world) return;
-    const long long t0 = clock64();
-    const volatile unsigned *f = flags + p;
-    // (flags only grow; a peer may already be one step ahead)
-    while ((int)(*f - seq) < 0) {
-        if (clock64() - t0 > 4000000000ll) {
-            atomicExch(error_flag, 5);
-            return;
+// combine kernels), for at most about two seconds; then, optionally, every block copies its
+// slice of this rank's gathered buffer of the step to `dst`.
+__global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned seq_arg, const unsigned *seq_ptr,
+                                      int *error_flag, const uint4 *src0, long long stride, uint4 *dst, size_t n16) {
+    const unsigned seq = seq_ptr ? *seq_ptr : seq_arg;  // (the combine kernel has already stored the step's number)
+    __shared__ int s_failed;
+    if (threadIdx.x == 0) s_failed = 0;
+    __syncthreads();
+    if ((int)threadIdx.x < world) {
+        const long long t0 = clock64();
+        const volatile unsigned *f = flags + threadIdx.x;
+        while ((int)(*f - seq) < 0) {  // (flags only grow; a peer may already be one step ahead)
+            if (clock64() - t0 > 4000000000ll) {
+                atomicExch(error_flag, 5);
+                s_failed = 1;
+                break;
+            }
+            __nanosleep(200);
         }
-        __nanosleep(200);
+        __threadfence_system();
     }
-    __threadfence_system();
+    __syncthreads();
+    if (!dst || s_failed) return;
+    const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(src0) + ((seq & 1u) ? stride : 0));
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = src[i];
 }
 
 // The decode kernels run with the largest shared-memory carve-out.  The small kernels around
@@ -500,8 +516,13 @@ int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, c
     return TQ_OK;
 }
 
-int32_t tq_launch_gather_wait(const unsigned *flags, int world, unsigned seq, int *error_flag, cudaStream_t stream) {
-    tq_gather_wait_kernel<<<1, 32, 0, stream>>>(flags, world, seq, error_flag);
+int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, size_t bytes, void *out_final,
+                              cudaStream_t stream) {
+    const size_t n16 = out_final ? bytes / 16 : 0;
+    const int blocks = out_final ? (int)((n16 + 255) / 256 < 64 ? (n16 + 255) / 256 : 64) : 1;
+    tq_gather_wait_kernel<<<blocks < 1 ? 1 : blocks, 256, 0, stream>>>(
+        g->flags[g->rank], g->world, g->seq, g->seq_dev, error_flag, reinterpret_cast<const uint4 *>(g->out[g->rank]),
+        g->out_stride, reinterpret_cast<uint4 *>(out_final), n16);
     TQ_CUDA_CHECK(cudaGetLastError());
     return TQ_OK;
 }

@@ -18,6 +18,8 @@ struct CombineArgs {
     // gathered buffer instead of `out`, and the last block raises this rank's flag in every peer.
     int gather_world, gather_rank, gather_heads_total;
     unsigned gather_seq;
+    const unsigned *gather_seq_ptr;  // when set, the step number is *gather_seq_ptr + 1 and the last block stores it back
+    long long gather_out_stride;     // bytes between a rank's two gathered buffers (step s uses buffer s & 1)
     void *gather_out[TQ_MAX_PEERS];
     unsigned *gather_flags[TQ_MAX_PEERS];
     unsigned *gather_counter;
@@ -39,7 +41,8 @@ struct DecodeWorkspace {
 };
 
 DecodeWorkspace tq_carve_workspace(void *workspace, int64_t rows, int n_splits);
-int32_t tq_launch_gather_wait(const unsigned *flags, int world, unsigned seq, int *error_flag, cudaStream_t stream);
+int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, size_t bytes, void *out_final,
+                              cudaStream_t stream);
 int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
                         cudaStream_t stream);
 // Query preparation for the G <= 4 kernel; with `append` the same launch also encodes and

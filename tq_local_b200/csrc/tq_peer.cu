@@ -45,7 +45,8 @@ extern "C" int32_t tq_peer_buffer_destroy(void *dev_ptr) {
 
 static int check_gather(const tq_gather_desc *g) {
     if (!g || g->world < 1 || g->world > TQ_MAX_PEERS || g->rank < 0 || g->rank >= g->world) return TQ_ERR_ARG;
-    if (g->seq == 0 || !g->counter || g->q_heads_total <= 0) return TQ_ERR_ARG;
+    if ((g->seq == 0 && !g->seq_dev) || !g->counter || g->q_heads_total <= 0) return TQ_ERR_ARG;
+    if (g->out_stride < 0 || (g->out_stride & 15) || ((uintptr_t)g->seq_dev & 3)) return TQ_ERR_ARG;
     for (int p = 0; p < g->world; ++p)
         if (!g->out[p] || !g->flags[p] || ((uintptr_t)g->out[p] & 15) || ((uintptr_t)g->flags[p] & 3)) return TQ_ERR_ARG;
     return TQ_OK;
@@ -75,10 +76,15 @@ extern "C" int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_d
     return rc;
 }
 
-extern "C" int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, tq_stream stream) {
+extern "C" int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, int32_t batch, int32_t dtype,
+                                  void *out_final, tq_stream stream) {
     if (!ctx) return TQ_ERR_ARG;
     int rc = check_gather(gather);
     if (rc) return rc;
-    return tq_launch_gather_wait(gather->flags[gather->rank], gather->world, gather->seq, ctx->error_flag,
-                                 (cudaStream_t)stream);
+    size_t bytes = 0;
+    if (out_final) {
+        if (batch <= 0 || (dtype != TQ_DTYPE_F16 && dtype != TQ_DTYPE_BF16) || ((uintptr_t)out_final & 15)) return TQ_ERR_ARG;
+        bytes = (size_t)batch * gather->q_heads_total * TQ_D * 2;
+    }
+    return tq_launch_gather_wait(gather, ctx->error_flag, bytes, out_final, (cudaStream_t)stream);
 }

@@ -63,7 +63,8 @@ TQ_MAX_PEERS = 8
 class GatherDesc(C.Structure):
     _fields_ = [
         ("world", C.c_int32), ("rank", C.c_int32), ("q_heads_total", C.c_int32), ("seq", C.c_uint32),
-        ("out", C.c_void_p * TQ_MAX_PEERS), ("flags", C.c_void_p * TQ_MAX_PEERS), ("counter", C.c_void_p),
+        ("out", C.c_void_p * TQ_MAX_PEERS), ("out_stride", C.c_int64), ("flags", C.c_void_p * TQ_MAX_PEERS),
+        ("counter", C.c_void_p), ("seq_dev", C.c_void_p),
     ]
 
 
@@ -121,7 +122,7 @@ def lib() -> C.CDLL:
     L.tq_decode_step_host.restype = C.c_int32
     L.tq_decode_step_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                      C.POINTER(CacheDesc), C.c_void_p, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p,
-                                     C.c_void_p]
+                                     C.POINTER(GatherDesc), C.c_void_p]
     L.tq_decode_step_dev.restype = C.c_int32
     L.tq_peer_buffer_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
     L.tq_peer_buffer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
@@ -129,7 +130,7 @@ def lib() -> C.CDLL:
     L.tq_peer_buffer_destroy.argtypes = [C.c_void_p]
     L.tq_decode_attn_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.POINTER(CacheDesc), C.c_int32,
                                         C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(GatherDesc), C.c_void_p]
-    L.tq_gather_wait.argtypes = [C.c_void_p, C.POINTER(GatherDesc), C.c_void_p]
+    L.tq_gather_wait.argtypes = [C.c_void_p, C.POINTER(GatherDesc), C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
     for name in ("tq_peer_buffer_create", "tq_peer_buffer_open", "tq_peer_buffer_close", "tq_peer_buffer_destroy",
                  "tq_decode_attn_gather", "tq_gather_wait"):
         getattr(L, name).restype = C.c_int32

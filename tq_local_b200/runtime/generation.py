@@ -133,8 +133,17 @@ class RecordedDecoder:
         self.eager_steps = _GRAPH_WARMUP_STEPS if eager_steps is None else int(eager_steps)
         self.done = 0
         self.graph = None  # None: not recorded yet; False: cannot be recorded
+        # KV-head shards exchange their outputs through one shared set of peer buffers whose step
+        # numbers live on the device (created and closed collectively by all ranks)
+        self.gather = None
+        shard = self.layers[0].shard
+        if shard.world_size > 1:
+            from tq_local_b200.runtime.sharding import PeerGather
+
+            self.gather = PeerGather(shard, int(first_token.shape[0]), int(model.config.num_attention_heads),
+                                     self.layers[0].dtype, device, device_sequence=True)
         for layer in self.layers:
-            layer.begin_static_decode(self.pos32, max_steps)
+            layer.begin_static_decode(self.pos32, max_steps, gather=self.gather)
 
     def _forward_once(self) -> None:
         import torch
@@ -182,6 +191,9 @@ class RecordedDecoder:
             for layer in self.layers:
                 layer.end_static_decode(self.length0 + self.done)
             self.layers = None
+            if self.gather is not None:
+                self.gather.close()
+                self.gather = None
 
     def __enter__(self):
         return self

@@ -140,6 +140,7 @@ class PackedMSELayer(CacheLayerMixin):
         self._stream_threshold: float | None = None   # see build_streaming_prefill_cache
         self._prefill_shape: tuple[int, ...] | None = None
         self._static_kv: tuple[torch.Tensor, torch.Tensor] | None = None
+        self._static_gather = None
 
     # ---------------------------------------------------------------- reference attributes
     @property
@@ -245,22 +246,26 @@ class PackedMSELayer(CacheLayerMixin):
     # ---------------------------------------------------------------- replayable decode
     def supports_static_decode(self, q_heads: int) -> bool:
         """Whether this layer can serve decode steps whose length lives on the device (packed,
-        quantised appends, 16-bit cache, at most 8 query heads per KV head, not sharded)."""
+        quantised appends, 16-bit cache, at most 8 query heads per KV head).  A sharded layer
+        additionally needs a device-sequenced ``PeerGather`` (see ``begin_static_decode``)."""
         return (self.store is not None and not self._force_dense and self.quantize_decode
                 and self._dense_k.length == 0 and self.dtype in (torch.float16, torch.bfloat16)
-                and self.shard.world_size == 1 and q_heads // self._kv_heads_total <= 8)
+                and q_heads // self._kv_heads_total <= 8)
 
-    def begin_static_decode(self, pos: torch.Tensor, max_new_tokens: int) -> None:
+    def begin_static_decode(self, pos: torch.Tensor, max_new_tokens: int, gather=None) -> None:
         """Switch to decode steps that read the cache length from the int32 device scalar ``pos``
         (shared by all layers of a model and advanced by the caller once per step).  From here on
         ``update`` only remembers the new token and ``attend`` appends it and attends in one fused
         call, neither touching host-side state: the whole model step can be recorded in a CUDA
         graph.  ``end_static_decode`` returns to the normal bookkeeping."""
+        if self.shard.world_size > 1 and gather is None:
+            raise RuntimeError("a sharded layer needs a PeerGather(device_sequence=True) for static decode")
         self.store.reserve(self.store.length + int(max_new_tokens))
         self._static_pos = pos
+        self._static_gather = gather if self.shard.world_size > 1 else None
 
     def end_static_decode(self, new_length: int) -> None:
-        self._static_pos, self._static_kv = None, None
+        self._static_pos, self._static_kv, self._static_gather = None, None, None
         self.store.length = int(new_length)
 
     # ---------------------------------------------------------------- decode-time update
@@ -329,9 +334,10 @@ class PackedMSELayer(CacheLayerMixin):
             raise RuntimeError("attend() needs a packed (non-dense) layer")
         if self._static_pos is not None:
             k_new, v_new = self._static_kv
-            out = self.store.decode_step_dev(self.shard.local_q(query_states, self._kv_heads_total),
-                                             self.shard.local_kv(k_new), self.shard.local_kv(v_new), self._static_pos)
-            return self.shard.gather_heads(out)
+            # (sharded: the combine kernel writes every rank's gathered buffer, the result is complete)
+            return self.store.decode_step_dev(self.shard.local_q(query_states, self._kv_heads_total),
+                                              self.shard.local_kv(k_new), self.shard.local_kv(v_new), self._static_pos,
+                                              gather=self._static_gather)
         b, hq, sq, d = query_states.shape
         q_local = self.shard.local_q(query_states, self._kv_heads_total)
         tail_k, tail_v = self._dense_k.view(), self._dense_v.view()

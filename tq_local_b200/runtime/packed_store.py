@@ -169,7 +169,8 @@ class PackedStore:
             ffi.check(ffi.lib().tq_decode_attn_gather(self.codec.handle, qc.data_ptr(), tq_dtype(q.dtype), hq,
                                                       C.byref(self._desc), n, splits, ws.data_ptr(), ws.numel(),
                                                       C.byref(desc), stream), "tq_decode_attn_gather")
-            ffi.check(ffi.lib().tq_gather_wait(self.codec.handle, C.byref(desc), stream), "tq_gather_wait")
+            ffi.check(ffi.lib().tq_gather_wait(self.codec.handle, C.byref(desc), b, tq_dtype(q.dtype), None, stream),
+                      "tq_gather_wait")
         return view
 
     def decode_step_host(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, out: torch.Tensor,
@@ -210,12 +211,14 @@ class PackedStore:
         return out
 
     def decode_step_dev(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, pos: torch.Tensor,
-                        out: torch.Tensor | None = None, splits: int | None = None) -> torch.Tensor:
+                        out: torch.Tensor | None = None, splits: int | None = None, gather=None) -> torch.Tensor:
         """One decode step whose cache length is the int32 DEVICE scalar ``pos``: append ``k_new`` /
         ``v_new`` [B, Hkv, 1, 128] at token ``pos`` and attend with ``q`` [B, Hq, 1, 128] over
         ``pos + 1`` tokens.  Nothing here depends on the value of ``pos`` on the host, so the call
         can be recorded in a CUDA graph and replayed; the caller advances ``pos`` and, when it is
-        done, sets ``self.length``.  The cache must already have room (``reserve``)."""
+        done, sets ``self.length``.  The cache must already have room (``reserve``).  With ``gather``
+        (a ``PeerGather`` created with ``device_sequence=True``) this store is a KV-head shard and
+        the result is the gathered output of all ranks [B, Hq_total, 1, 128]."""
         b, hq = int(q.shape[0]), int(q.shape[1])
         if b != self.batch or k_new.shape[1] != self.kv_heads or q.dtype != k_new.dtype:
             raise ValueError("shape or dtype mismatch")
@@ -224,12 +227,14 @@ class PackedStore:
         qc, kc, vc = (t if t.is_contiguous() else t.contiguous() for t in (q, k_new, v_new))
         splits = self.suggest_splits(self.capacity) if splits is None else int(splits)
         ws = self._get_workspace(hq, splits)
+        gdesc = None if gather is None else gather.static_desc()
         if out is None:
-            out = torch.empty(b, hq, 1, 128, dtype=q.dtype, device=q.device)
+            out = torch.empty(b, hq if gather is None else gather.shape[1], 1, 128, dtype=q.dtype, device=q.device)
         with torch.cuda.device(self.codec.device):
             ffi.check(ffi.lib().tq_decode_step_dev(self.codec.handle, qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
                                                    tq_dtype(q.dtype), hq, C.byref(self._desc), pos.data_ptr(), splits,
-                                                   ws.data_ptr(), ws.numel(), out.data_ptr(), self._stream_ptr()),
+                                                   ws.data_ptr(), ws.numel(), out.data_ptr(),
+                                                   None if gdesc is None else C.byref(gdesc), self._stream_ptr()),
                       "tq_decode_step_dev")
         return out
 

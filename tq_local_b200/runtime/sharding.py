@@ -92,9 +92,14 @@ class PeerGather:
     a flag block, all in memory that the other ranks of the box map through CUDA IPC, so a rank's
     combine kernel stores its rows straight into every rank's buffer over NVLink and no
     collective library call is on the path.  Set-up exchanges the 64-byte handles with
-    ``all_gather_object``; ``world_size`` 1 works too (nothing is mapped)."""
+    ``all_gather_object``; ``world_size`` 1 works too (nothing is mapped).
 
-    def __init__(self, shard: HeadShard, batch: int, q_heads_total: int, dtype: torch.dtype, device: torch.device):
+    ``device_sequence=True`` keeps the step number in device memory (advanced by the kernels), for
+    launch sequences that are recorded once and replayed (``PackedStore.decode_step_dev``); such a
+    gather must not be used through ``next_desc``."""
+
+    def __init__(self, shard: HeadShard, batch: int, q_heads_total: int, dtype: torch.dtype, device: torch.device,
+                 device_sequence: bool = False):
         from tq_local_b200.runtime import ffi
 
         if shard.world_size > ffi.TQ_MAX_PEERS:
@@ -104,6 +109,7 @@ class PeerGather:
         self.out_bytes = (batch * q_heads_total * 128 * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256
         self.total = 2 * self.out_bytes + 256
         self.seq = 0
+        self.seq_dev = torch.zeros(1, dtype=torch.int32, device=self.device) if device_sequence else None
         self._lib = ffi.lib()
         self._views = None
         # Set-up is collective: every rank takes part in every exchange below even when a step failed
@@ -145,20 +151,34 @@ class PeerGather:
         b, h, _, d = self.shape
         return b * h * d * torch.empty((), dtype=self.dtype).element_size()
 
-    def next_desc(self):
-        """Descriptor of the next step (advances the sequence number) and the view of this rank's
-        gathered output for it."""
+    def _desc(self):
         from tq_local_b200.runtime import ffi
 
-        self.seq += 1
-        parity = self.seq & 1
         d = ffi.GatherDesc()
-        d.world, d.rank, d.q_heads_total, d.seq = self.shard.world_size, self.shard.rank, self.shape[1], self.seq
+        d.world, d.rank, d.q_heads_total, d.seq = self.shard.world_size, self.shard.rank, self.shape[1], 0
+        d.out_stride = self.out_bytes
         for r, base in enumerate(self.bases):
-            d.out[r] = base + parity * self.out_bytes
+            d.out[r] = base
             d.flags[r] = base + 2 * self.out_bytes
         d.counter = self.bases[self.shard.rank] + 2 * self.out_bytes + 64
-        return d, self._views[parity]
+        d.seq_dev = self.seq_dev.data_ptr() if self.seq_dev is not None else None
+        return d
+
+    def next_desc(self):
+        """Descriptor of the next step (advances the host-side sequence number) and the view of this
+        rank's gathered output for it."""
+        if self.seq_dev is not None:
+            raise RuntimeError("this PeerGather takes its step numbers from the device")
+        self.seq += 1
+        d = self._desc()
+        d.seq = self.seq
+        return d, self._views[self.seq & 1]
+
+    def static_desc(self):
+        """Descriptor for steps numbered on the device (the same for every step)."""
+        if self.seq_dev is None:
+            raise RuntimeError("create the PeerGather with device_sequence=True")
+        return self._desc()
 
     def _release(self) -> None:
         with torch.cuda.device(self.device):

@@ -416,7 +416,9 @@ def run_model_arm(args) -> None:
     layer's cache holding 32768 packed tokens per sequence (4-bit Q_prod), greedy decoding through
     the library's attention backend with the model step replayed from a CUDA graph.  The caches
     are filled with packed synthetic K/V (the prompt pass is not part of a decode-rate figure).
-    At N > 1 the weights are replicated, the KV heads are sharded and the batch stays 16."""
+    At N > 1 the weights are replicated and the KV heads are sharded (outputs exchanged by the
+    fused peer gather inside the recorded step); the batch stays 16 (``--model-scaling strong``) or
+    grows with N (``weak``)."""
     import torch
     import torch.distributed as dist
     from transformers import LlamaConfig, LlamaForCausalLM
@@ -437,6 +439,8 @@ def run_model_arm(args) -> None:
     w = dict(MODEL_WORKLOAD)
     if args.batch_per_gpu:
         w["batch"] = args.batch_per_gpu
+    if args.model_scaling == "weak":
+        w["batch"] *= world  # every GPU then streams the same packed bytes as one GPU does at N = 1
     if args.context:
         w["context"] = args.context
     if args.layers:
@@ -478,12 +482,15 @@ def run_model_arm(args) -> None:
             torch.cuda.synchronize()
 
         try:
-            if world == 1:
+            q_heads = w["q_heads"]
+            if all(layer.supports_static_decode(q_heads) for layer in layers):
+                # (sharded layers exchange their outputs through the fused peer gather inside the step)
                 with RecordedDecoder(model, cache, first, warmup + steps) as dec:
                     for _ in range(warmup):
                         dec.step()
                     fence()
-                    sampler.start()
+                    if rank == 0:
+                        sampler.start()
                     ev0.record()
                     for _ in range(steps):
                         dec.step()
@@ -492,7 +499,6 @@ def run_model_arm(args) -> None:
                     recorded = bool(dec.graph)
                     tokens = dec.tokens.clone()
             else:
-                # sharded layers keep their length on the host: one eager forward pass per token
                 recorded, produced, tok = False, [], first
 
                 def eager_step(tok):
@@ -525,7 +531,8 @@ def run_model_arm(args) -> None:
         weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
         line = {
             "metric": "decode_tok_per_s_32k_ctx", "value": B * 1e3 / ms, "unit": "tok/s", "n_gpus": world,
-            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": args.model_scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": w["name"], "global_batch": B, "context": N, "layers": w["layers"],
                        "q_heads": w["q_heads"], "kv_heads": w["kv_heads"], "bits": w["bits"], "mode": "Q_prod",
@@ -562,6 +569,8 @@ def main() -> None:
     ap.add_argument("--gather", default="auto", choices=["auto", "nccl", "p2p"],
                     help="N > 1: how the per-head outputs are exchanged: p2p = stores into the peers' buffers fused "
                          "into the combine kernel, nccl = NCCL all-gather, auto = p2p with a fall-back to nccl")
+    ap.add_argument("--model-scaling", default="strong", choices=["strong", "weak"],
+                    help="model workload at N > 1: strong = batch 16 in total (BASELINE config 5), weak = 16 per GPU")
     ap.add_argument("--layers", type=int, default=None, help="model workload: override the layer count (smoke runs)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -398,6 +398,8 @@ def run_gpu_arm(args) -> None:
             cb = cpu_reference_run(steps=3, warmup=1)
             line["cpu_baseline"] = {k_: cb[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
+    if peer is not None:
+        peer.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -544,8 +546,6 @@ def run_model_arm(args) -> None:
             "clocks": clocks,
         }
         print(json.dumps(line))
-    if peer is not None:
-        peer.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

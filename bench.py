@@ -324,11 +324,12 @@ def run_gpu_arm(args) -> None:
     d2h = (gathered if world > 1 else out).numel() * out.element_size()
 
     h_out1 = torch.empty(batch, hq, 1, HEAD_DIM, **pin)
+    host_step = store.bind_host_step(h_q, h_k, h_v, h_out1) if world == 1 else None
 
     def e2e_step():
         if world == 1:
             # the library's host-buffer entry point: H2D of q / k / v, append, attend, D2H of the output
-            store.decode_step_host(h_q, h_k, h_v, h_out1)
+            host_step()
         else:
             d_q.copy_(h_q, non_blocking=True)
             d_k.copy_(h_k, non_blocking=True)

@@ -318,6 +318,36 @@ def test_host_buffer_decode_step_matches_device_calls(setup_golden, dtype):
         assert torch.equal(x[:, :, :130], y[:, :, :130])
 
 
+def test_bound_host_step_reuses_buffers_across_capacity_growth(setup_golden):
+    """bind_host_step: buffers checked once, one call per token, including a step that has to grow
+    the cache; pageable (not page-locked) buffers take the staged-copy route."""
+    from tq_local_b200.runtime.packed_store import PackedStore
+
+    codec = make_codec(3, True, setup_golden)
+    k, v, _ = O.synth_kvq(1, 4, 2, 40, 128, seed=78, dtype=torch.float16)
+    g = torch.Generator().manual_seed(3)
+    for pinned in (True, False):
+        a = PackedStore(codec, 1, 2, capacity=32)
+        b = PackedStore(codec, 1, 2, capacity=64)
+        a.pack(k[:, :, :30].cuda(), v[:, :, :30].cuda())
+        b.pack(k[:, :, :30].cuda(), v[:, :, :30].cuda())
+        bufs = [torch.empty(1, 4, 1, 128, dtype=torch.float16), torch.empty(1, 2, 1, 128, dtype=torch.float16),
+                torch.empty(1, 2, 1, 128, dtype=torch.float16), torch.empty(1, 4, 1, 128, dtype=torch.float16)]
+        if pinned:
+            bufs = [t.pin_memory() for t in bufs]
+        hq, hk, hv, hout = bufs
+        step = a.bind_host_step(hq, hk, hv, hout)
+        for t in range(30, 40):  # crosses the capacity of 32
+            q = torch.randn(1, 4, 1, 128, generator=g).to(torch.float16)
+            hq.copy_(q), hk.copy_(k[:, :, t:t + 1]), hv.copy_(v[:, :, t:t + 1])
+            step()
+            b.pack(k[:, :, t:t + 1].cuda(), v[:, :, t:t + 1].cuda())
+            want = b.decode_attn(q.cuda())
+            torch.cuda.synchronize()
+            assert torch.equal(hout, want.cpu()), (pinned, t)
+        assert a.length == 40 and a.capacity >= 40
+
+
 def test_decode_step_with_device_length_matches_and_replays_from_a_cuda_graph(setup_golden):
     """tq_decode_step_dev: the append position / sequence length is a device scalar, so one
     recorded launch sequence serves every token.  Results must equal the host-length path bit

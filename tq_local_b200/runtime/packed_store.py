@@ -210,6 +210,43 @@ class PackedStore:
         self.length += 1
         return out
 
+    def bind_host_step(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, out: torch.Tensor):
+        """``decode_step_host`` for a serving loop that reuses the same four host buffers every
+        step: checks them once and returns a function that runs one step per call (append the
+        buffers' current K/V, attend with the current query, write ``out``; queued on the current
+        stream).  The buffers must stay alive and unmoved while the function is in use."""
+        for t in (q, k_new, v_new, out):
+            if t.device.type != "cpu" or not t.is_contiguous():
+                raise ValueError("bind_host_step takes contiguous host tensors")
+        b, hq = int(q.shape[0]), int(q.shape[1])
+        if b != self.batch or k_new.shape[1] != self.kv_heads or q.dtype != k_new.dtype or out.dtype != q.dtype:
+            raise ValueError("shape or dtype mismatch")
+        fn = ffi.lib().tq_decode_step_host
+        handle, dt, dev = self.codec.handle, tq_dtype(q.dtype), self.codec.device
+        ptrs = (q.data_ptr(), k_new.data_ptr(), v_new.data_ptr())
+        out_ptr, keep = out.data_ptr(), (q, k_new, v_new, out)
+        state = {"bucket": None}
+
+        def step() -> None:
+            n = self.length + 1
+            if n > self.capacity or state["bucket"] != (n >> 9, self.capacity):
+                self.reserve(n)
+                splits = self.suggest_splits(n)
+                need = int(ffi.lib().tq_decode_step_workspace_bytes(b, hq, self.kv_heads, splits))
+                if self._workspace is None or self._workspace.numel() < need:
+                    self._workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+                    self._step_plan = None
+                state.update(bucket=(n >> 9, self.capacity), splits=splits, ws=self._workspace,
+                             ws_ptr=self._workspace.data_ptr(), ws_bytes=self._workspace.numel())
+            rc = fn(handle, ptrs[0], ptrs[1], ptrs[2], dt, hq, self._desc_ref, self.length, state["splits"],
+                    state["ws_ptr"], state["ws_bytes"], out_ptr, torch.cuda.current_stream(dev).cuda_stream)
+            if rc:
+                ffi.check(rc, "tq_decode_step_host")
+            self.length = n
+
+        step.buffers = keep
+        return step
+
     def decode_step_dev(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, pos: torch.Tensor,
                         out: torch.Tensor | None = None, splits: int | None = None, gather=None) -> torch.Tensor:
         """One decode step whose cache length is the int32 DEVICE scalar ``pos``: append ``k_new`` /

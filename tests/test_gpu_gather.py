@@ -99,3 +99,13 @@ def test_gather_between_two_gpus_equals_nccl_all_gather():
                           "--master-addr", "127.0.0.1", "--master-port", "29611", worker],
                          capture_output=True, text=True, timeout=240, env=env)
     assert out.returncode == 0 and "GATHER_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_generation_on_two_gpus_eager_and_recorded():
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_generate_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29613", worker],
+                         capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0 and "GENERATE_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-3000:]

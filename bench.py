@@ -360,6 +360,31 @@ def run_gpu_arm(args) -> None:
         e2e_ms = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---- context figure: the same decode step over a DENSE bf16 cache with torch's SDPA (what the
+    # reference calls its baseline), N = 1 only; the dense cache is 3.8x the packed bytes
+    dense = None
+    if world == 1 and not args.skip_e2e:
+        try:
+            import torch.nn.functional as F
+
+            dk = torch.randn(batch, hkv, n_ctx, HEAD_DIM, device=dev, dtype=dtype)
+            dv = torch.randn(batch, hkv, n_ctx, HEAD_DIM, device=dev, dtype=dtype)
+            for _ in range(3):
+                F.scaled_dot_product_attention(q, dk, dv, enable_gqa=True)
+            torch.cuda.synchronize()
+            ev0.record()
+            for _ in range(10):
+                F.scaled_dot_product_attention(q, dk, dv, enable_gqa=True)
+            ev1.record()
+            torch.cuda.synchronize()
+            dense_ms = ev0.elapsed_time(ev1) / 10
+            dense = {"ms_per_step": dense_ms, "dense_bytes": 2 * dk.numel() * dk.element_size(),
+                     "dense_gbs": 2 * dk.numel() * dk.element_size() / (dense_ms * 1e-3) / 1e9,
+                     "what": "torch scaled_dot_product_attention over the same keys/values kept dense in bf16"}
+            del dk, dv
+        except Exception as exc:  # noqa: BLE001
+            dense = {"unavailable": repr(exc)}
+
     if rank == 0:
         units_total = batch * hkv * n_ctx * world  # every rank attends batch x hkv rows
         total_bytes = unit_bytes * units_total
@@ -394,6 +419,7 @@ def run_gpu_arm(args) -> None:
             "device_status": codec.device_status(),
             "clocks": clocks,
             "pack": {"seconds": pack_s, "vectors_per_s": 2 * batch * hkv * n_ctx / pack_s},
+            "dense_sdpa": dense,
         }
         if world == 1 and not args.no_cpu_baseline:
             cb = cpu_reference_run(steps=3, warmup=1)

@@ -348,14 +348,15 @@ def test_bound_host_step_reuses_buffers_across_capacity_growth(setup_golden):
         assert a.length == 40 and a.capacity >= 40
 
 
-def test_decode_step_with_device_length_matches_and_replays_from_a_cuda_graph(setup_golden):
+@pytest.mark.parametrize("Hq", [8, 14])
+def test_decode_step_with_device_length_matches_and_replays_from_a_cuda_graph(setup_golden, Hq):
     """tq_decode_step_dev: the append position / sequence length is a device scalar, so one
     recorded launch sequence serves every token.  Results must equal the host-length path bit
     for bit, eagerly and when replayed from a CUDA graph."""
     from tq_local_b200.runtime.packed_store import PackedStore
 
     codec = make_codec(4, True, setup_golden)
-    B, Hq, Hkv, N0, steps = 2, 8, 2, 700, 6
+    B, Hkv, N0, steps = 2, 2, 700, 6
     k, v, _ = O.synth_kvq(B, Hq, Hkv, N0 + steps, 128, seed=21, dtype=torch.bfloat16)
     g = torch.Generator().manual_seed(5)
     qs = torch.randn(steps, B, Hq, 1, 128, generator=g).to(torch.bfloat16).cuda()

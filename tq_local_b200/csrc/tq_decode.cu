@@ -284,11 +284,11 @@ __global__ void __launch_bounds__(TQ_D) tq_combine_kernel(CombineArgs a) {
 }
 
 // Query preparation for the G <= 4 tensor-core kernel (see tq_qprep_block): kv_rows blocks
-// rotate, another kv_rows blocks project when the keys carry a QJL sketch.  The blocks let the
-// decode kernel, launched as a programmatic dependent, start its own set-up at once.
+// rotate, another kv_rows blocks project when the keys carry a QJL sketch.  Launched as a
+// programmatic dependent of whatever precedes it in the stream: a block fetches its matrix
+// column, waits for that kernel, then lets the decode kernel begin its own set-up.
 template <typename T>
 __global__ void __launch_bounds__(4 * TQ_D, 2) tq_qprep_frag_kernel(TqQprepArgs a) {
-    tq_launch_dependents();
     tq_qprep_block<T>(a, blockIdx.x);
 }
 
@@ -296,7 +296,6 @@ __global__ void __launch_bounds__(4 * TQ_D, 2) tq_qprep_frag_kernel(TqQprepArgs 
 // first, then one block per new key and value vector to append (tq_pack_small_block).
 template <typename T, bool QJL>
 __global__ void __launch_bounds__(4 * TQ_D, 2) tq_step_prologue_kernel(TqQprepArgs qa, TqPackArgs pa, int n_qprep) {
-    tq_launch_dependents();
     if ((int)blockIdx.x < n_qprep)
         tq_qprep_block<T>(qa, blockIdx.x);
     else
@@ -470,12 +469,12 @@ int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t row
 template <typename T>
 static cudaError_t launch_prologue(tq_ctx *ctx, const TqQprepArgs &qa, const TqPackArgs *append, cudaStream_t stream) {
     const int n_qprep = (int)qa.kv_rows * ((qa.G + 3) / 4) * (qa.use_qjl ? 2 : 1);
-    if (!append) return tq_launch_kernel(tq_qprep_frag_kernel<T>, dim3(n_qprep), dim3(4 * TQ_D), 0, stream, false, qa);
+    if (!append) return tq_launch_kernel(tq_qprep_frag_kernel<T>, dim3(n_qprep), dim3(4 * TQ_D), 0, stream, true, qa);
     const int n_pack = append->n_kinds * append->B * append->H * append->S;
     if (ctx->use_qjl)
         return tq_launch_kernel(tq_step_prologue_kernel<T, true>, dim3(n_qprep + n_pack), dim3(4 * TQ_D), 0, stream,
-                                false, qa, *append, n_qprep);
-    return tq_launch_kernel(tq_step_prologue_kernel<T, false>, dim3(n_qprep + n_pack), dim3(4 * TQ_D), 0, stream, false,
+                                true, qa, *append, n_qprep);
+    return tq_launch_kernel(tq_step_prologue_kernel<T, false>, dim3(n_qprep + n_pack), dim3(4 * TQ_D), 0, stream, true,
                             qa, *append, n_qprep);
 }
 

@@ -110,16 +110,20 @@ template <typename T, bool QJL> __device__ __forceinline__ void tq_pack_small_bl
     const int h = (int)((vid / a.S) % a.H);
     const int b = (int)(vid / ((int64_t)a.S * a.H));
     const T *src = (const T *)a.x[kind] + b * a.sb[kind] + h * a.sh[kind] + (int64_t)t * a.st[kind];
+    const int bits = a.bits[kind];
+    float m[32];
+    tq_load_column(m, a.rot_t[kind], dq, j);  // (codec constants: fetched before the wait)
+    if (tid < 16) s_bnd[tid] = a.bounds[kind][tid], s_cen[tid] = a.centers_k[tid];
+    // the new vectors and the append position come from, and the cache may still be read by, the
+    // preceding kernel of the stream
+    tq_grid_dependency_wait();
+    tq_launch_dependents();
     const int pos0 = a.pos_ptr ? *a.pos_ptr : a.pos0;
     if (pos0 < 0 || pos0 + a.S > a.capacity) {  // (the whole block leaves together)
         if (tid == 0) atomicExch(a.error_flag, 4);
         return;
     }
     const int64_t row = b * a.cache_sb + h * a.cache_sh + pos0 + t;
-    const int bits = a.bits[kind];
-    float m[32];
-    tq_load_column(m, a.rot_t[kind], dq, j);
-    if (tid < 16) s_bnd[tid] = a.bounds[kind][tid], s_cen[tid] = a.centers_k[tid];
 
     auto block_norm = [&](float v) {  // sqrt of the sum of v*v over the 128 threads with dq == 0
         float ss = dq == 0 ? v * v : 0.f;
@@ -205,7 +209,9 @@ template <typename T> __device__ __forceinline__ void tq_qprep_block(const TqQpr
     const int tid = threadIdx.x, j = tid & (TQ_D - 1), dq = tid >> 7;
     const int warp = tid >> 5, lane = tid & 31;
     float m[32];
-    tq_load_column(m, proj ? a.qjl_t : a.rot_k_t, dq, j);
+    tq_load_column(m, proj ? a.qjl_t : a.rot_k_t, dq, j);  // (codec constants: fetched before the wait)
+    tq_grid_dependency_wait();   // the query comes from the preceding kernel of the stream
+    tq_launch_dependents();      // the decode kernel may begin its set-up now
     if (dq < G) s_q[dq][j] = tq_to_float<T>(((const T *)a.q)[(head0 + dq) * TQ_D + j]);
     __syncthreads();
     {

@@ -204,6 +204,9 @@ def test_dense_tail_attention_matches_reference(setup_golden, case):
     (4, False, torch.bfloat16, 2, 16, 2, 900),
     (3, False, torch.bfloat16, 1, 12, 2, 1300),
     (4, True, torch.bfloat16, 2, 28, 4, 2100),
+    # more (batch, KV head) rows than SMs: a CTA's chunk spans several rows
+    (4, True, torch.bfloat16, 40, 8, 4, 600),
+    (3, True, torch.float16, 23, 14, 7, 200),
 ])
 def test_seeded_layer_against_oracle(setup_golden, bits, qjl, dtype, B, Hq, Hkv, N):
     """Larger seeded inputs: encode on the GPU, compare codes with the oracle, then

@@ -78,7 +78,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -302,6 +302,13 @@ def run_gpu_arm(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
 
+    # The timed region lasts a few milliseconds, too short for more than one clock sample: keep the
+    # identical steps running (untimed) for about half a second so that the clock / throttle record
+    # describes this load.  (Same count on every rank: the steps synchronise the ranks.)
+    for _ in range(min(20000, max(steps, int(0.5 / max(ms * 1e-3, 1e-6))))):
+        step()
+    fence()
+
     # ---- same steps again with the library's hooks on: CUDA events around the main kernel
     # (on its launch stream) give the roofline numerator; every launch is counted
     codec.profile(True)
@@ -417,7 +424,8 @@ def run_gpu_arm(args) -> None:
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(all_launches),
             "device_status": codec.device_status(),
-            "clocks": clocks,
+            "clocks": dict(clocks or {}, window="the timed steps and ~0.5 s of the same steps kept running after them, "
+                                                "the hooked steps and the end-to-end steps"),
             "pack": {"seconds": pack_s, "vectors_per_s": 2 * batch * hkv * n_ctx / pack_s},
             "dense_sdpa": dense,
         }

@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(TQ_D) tq_combine_kernel(CombineArgs a) {
     ((T *)a.out)[row * TQ_D + e] = tq_from_float<T>(out / fmaxf(L, 1e-8f));
 }
 
-// Query preparation for the G <= 4 tensor-core kernel (see tq_qprep_block): kv_rows blocks
+// Query preparation for the tensor-core kernel (see tq_qprep_block): kv_rows * ceil(G / 4) blocks
 // rotate, another kv_rows blocks project when the keys carry a QJL sketch.  Launched as a
 // programmatic dependent of whatever precedes it in the stream: a block fetches its matrix
 // column, waits for that kernel, then lets the decode kernel begin its own set-up.
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(4 * TQ_D, 2) tq_step_prologue_kernel(TqQprepAr
         tq_pack_small_block<T, QJL>(pa, (int64_t)blockIdx.x - n_qprep);
 }
 
-// Split combine for all G <= 4 heads of one (batch, KV head) row per block (no dense tail):
+// Split combine for up to four heads of one (batch, KV head) row per block (no dense tail):
 // the un-rotation matrix is read once for the G heads.
 template <typename T>
 __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs a) {

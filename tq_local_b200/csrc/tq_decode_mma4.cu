@@ -1,10 +1,11 @@
 // Decode attention over the packed cache: tensor-core kernel for fp16 / bf16 queries
-// with at most 4 query heads per KV head (Llama-3.1-8B: 32 / 8).
+// with at most 8 query heads per KV head (Llama-3.1-8B: 32 / 8; Qwen2.5-7B: 28 / 4).
 //
 // Persistent CTAs, one per SM: the (batch, KV head) rows are laid end to end and cut into
 // equal token chunks, one per CTA, so every SM streams the same number of bytes; a CTA emits
-// one partial (max, sum, acc) per row it touches.  Each CTA serves all G <= 4 query heads of
-// a row, so packed bytes are read from HBM once.
+// one partial (max, sum, acc) per row it touches.  Each CTA serves all G query heads of a
+// row, so packed bytes are read from HBM once.  The description below is the G <= 4 variant;
+// the wide variant (see the kernel's template note) differs in how the MMA columns are used.
 //
 // Data movement: every group of four warps runs its own ring of 128-token slots in shared
 // memory (32 tokens per warp).  One lane of the group fills a slot with six TMA bulk copies

@@ -45,7 +45,7 @@ int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, size_t b
                               cudaStream_t stream);
 int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
                         cudaStream_t stream);
-// Query preparation for the G <= 4 kernel; with `append` the same launch also encodes and
+// Query preparation for the tensor-core kernel; with `append` the same launch also encodes and
 // appends the step's new key / value vectors.
 int32_t tq_launch_qprep_frag(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t kv_rows, int G, uint32_t *frag,
                              const TqPackArgs *append, cudaStream_t stream);

@@ -396,7 +396,10 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
 // slice of this rank's gathered buffer of the step to `dst`.
 __global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned seq_arg, const unsigned *seq_ptr,
                                       int *error_flag, const uint4 *src0, long long stride, uint4 *dst, size_t n16) {
-    const unsigned seq = seq_ptr ? *seq_ptr : seq_arg;  // (the combine kernel has already stored the step's number)
+    // A step numbered on the device gets its number from the combine kernel's last block, so that
+    // kernel has to be complete before the number is read; a host-numbered step may start polling early.
+    if (seq_ptr) tq_grid_dependency_wait();
+    const unsigned seq = seq_ptr ? *seq_ptr : seq_arg;
     __shared__ int s_failed;
     if (threadIdx.x == 0) s_failed = 0;
     __syncthreads();
@@ -519,10 +522,16 @@ int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, size_t b
                               cudaStream_t stream) {
     const size_t n16 = out_final ? bytes / 16 : 0;
     const int blocks = out_final ? (int)((n16 + 255) / 256 < 64 ? (n16 + 255) / 256 : 64) : 1;
-    tq_gather_wait_kernel<<<blocks < 1 ? 1 : blocks, 256, 0, stream>>>(
-        g->flags[g->rank], g->world, g->seq, g->seq_dev, error_flag, reinterpret_cast<const uint4 *>(g->out[g->rank]),
-        g->out_stride, reinterpret_cast<uint4 *>(out_final), n16);
-    TQ_CUDA_CHECK(cudaGetLastError());
+    // Launched as a programmatic dependent: with a host-side step number it begins polling while the
+    // combine kernel that raises this rank's own flag is still finishing (harmless: the flags carry
+    // the step number); what follows it in the stream still starts only after it has seen every
+    // rank's flag, this rank's included.
+    cudaError_t e = tq_launch_kernel(tq_gather_wait_kernel, dim3(blocks < 1 ? 1 : blocks), dim3(256), 0, stream, true,
+                                     (const unsigned *)g->flags[g->rank], (int)g->world, (unsigned)g->seq,
+                                     (const unsigned *)g->seq_dev, error_flag,
+                                     reinterpret_cast<const uint4 *>(g->out[g->rank]), (long long)g->out_stride,
+                                     reinterpret_cast<uint4 *>(out_final), n16);
+    TQ_CUDA_CHECK(e);
     return TQ_OK;
 }
 

@@ -221,10 +221,11 @@ extern "C" int32_t tq_device_status(tq_ctx *ctx, int32_t *status_out) {
     return TQ_OK;
 }
 
-extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
-                                  const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
-                                  const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
-                                  void *workspace, size_t workspace_bytes, void *out, tq_stream stream) {
+// tq_decode_attn, plus what the whole-step entry points add (`extras`, tensor-core path only).
+static int32_t decode_attn_impl(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                                const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
+                                const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits, void *workspace,
+                                size_t workspace_bytes, void *out, const TqStepExtras *extras, tq_stream stream) {
     if (!ctx || !q || !out || !workspace) return TQ_ERR_ARG;
     int rc = check_cache(ctx, cache);
     if (rc) return rc;
@@ -240,7 +241,15 @@ extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, i
         return tq_launch_decode_exact(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
                                       workspace, out, (cudaStream_t)stream);
     return tq_launch_decode_mma4(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits,
-                                 workspace, out, (cudaStream_t)stream);
+                                 workspace, out, extras, (cudaStream_t)stream);
+}
+
+extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                                  const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
+                                  const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
+                                  void *workspace, size_t workspace_bytes, void *out, tq_stream stream) {
+    return decode_attn_impl(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits, workspace,
+                            workspace_bytes, out, nullptr, stream);
 }
 
 extern "C" size_t tq_decode_step_workspace_bytes(int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t n_splits) {
@@ -296,17 +305,17 @@ extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const vo
     int32_t rc = check_cache(ctx, cache);
     if (rc) return rc;
     TqPackArgs append;
+    TqStepExtras extras = {nullptr, nullptr, nullptr};
     if (dtype != TQ_DTYPE_F32 && q_heads / cache->kv_heads <= TQ_MAX_GROUPS) {
         // the tensor-core decode path encodes the new token in its own query-preparation launch
         tq_fill_pack_args(ctx, &kd, &vd, 1, cache, pos, &append);
-        ctx->pending_append = &append;
+        extras.append = &append;
     } else {
         rc = tq_pack(ctx, &kd, &vd, 1, cache, pos, stream);
         if (rc) return rc;
     }
-    rc = tq_decode_attn(ctx, d_q, dtype, q_heads, cache, pos + 1, nullptr, nullptr, 0, n_splits, workspace, ws, d_out,
-                        stream);
-    ctx->pending_append = nullptr;
+    rc = decode_attn_impl(ctx, d_q, dtype, q_heads, cache, pos + 1, nullptr, nullptr, 0, n_splits, workspace, ws, d_out,
+                          extras.append ? &extras : nullptr, stream);
     if (rc) return rc;
     if (!direct) TQ_CUDA_CHECK(cudaMemcpyAsync(out_host, d_out, q_bytes, cudaMemcpyDeviceToHost, s));
     return TQ_OK;
@@ -333,12 +342,9 @@ extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_
     TqPackArgs append;
     tq_fill_pack_args(ctx, &kd, &vd, 1, cache, 0, &append);
     append.pos_ptr = pos_dev;
-    ctx->pending_append = &append;
-    ctx->pending_len_ptr = pos_dev;
-    ctx->pending_gather = gather;
+    const TqStepExtras extras = {&append, pos_dev, gather};
     rc = tq_launch_decode_mma4(ctx, q, dtype, q_heads, cache, cache->capacity, nullptr, nullptr, 0, n_splits, workspace,
-                               gather ? nullptr : out, (cudaStream_t)stream);
-    ctx->pending_append = nullptr, ctx->pending_len_ptr = nullptr, ctx->pending_gather = nullptr;
+                               gather ? nullptr : out, &extras, (cudaStream_t)stream);
     if (rc || !gather) return rc;
     return tq_gather_wait(ctx, gather, cache->batch, dtype, out, stream);
 }

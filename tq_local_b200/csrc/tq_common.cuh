@@ -39,9 +39,6 @@ struct tq_ctx {
     size_t base_bytes;
     struct tq_prof *prof;  // measurement hooks, see tq_profile_enable
     int *error_flag;       // device word, set by a kernel whose bounded wait ran out
-    const struct TqPackArgs *pending_append;  // set by the step entry points for the next decode launch
-    const int *pending_len_ptr;               // likewise: sequence length kept in device memory
-    const tq_gather_desc *pending_gather;     // likewise: write the outputs into every rank's gathered buffer
     int64_t splits_cache_key;  // last (rows, length bucket) asked of tq_decode_suggest_splits
     int splits_cache_val;
 };
@@ -117,11 +114,17 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
                                const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
                                const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
                                void *workspace, void *out, cudaStream_t stream);
+// What a whole-step entry point adds to a plain decode launch (all optional).
+struct TqStepExtras {
+    const struct TqPackArgs *append;  // encode and append the step's new token in the query-preparation launch
+    const int *len_ptr;               // the sequence length lives in device memory
+    const tq_gather_desc *gather;     // KV-head shard: write the outputs into every rank's gathered buffer
+};
 int tq_mma4_tokens_per_cta_step();
 int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
                               const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
                               const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
-                              void *workspace, void *out, cudaStream_t stream);
+                              void *workspace, void *out, const TqStepExtras *extras, cudaStream_t stream);
 void tq_build_operand_image(const float *m, uint16_t *image);
 int32_t tq_launch_pack_tc(tq_ctx *ctx, const tq_dense_desc *x, int which, int32_t n_tokens,
                           const tq_cache_desc *cache, int32_t pos0, cudaStream_t stream);

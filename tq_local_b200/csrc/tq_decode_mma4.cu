@@ -586,16 +586,15 @@ int tq_mma4_tokens_per_cta_step() { return kWarps * kStageTok; }
 int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
                               const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
                               const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits, void *workspace,
-                              void *out, cudaStream_t stream) {
+                              void *out, const TqStepExtras *extras, cudaStream_t stream) {
     const int64_t rows = (int64_t)cache->batch * q_heads;
     DecodeWorkspace w = tq_carve_workspace(workspace, rows, n_splits);
     // the fragment area overlays the rotated / projected query rows of the workspace
     uint32_t *frag = reinterpret_cast<uint32_t *>(w.qrot);
     const int groups = q_heads / cache->kv_heads;
-    const TqPackArgs *append = ctx->pending_append;  // this step's new token, encoded by the same launch
-    const int *len_ptr = ctx->pending_len_ptr;       // sequence length kept on the device
-    const tq_gather_desc *gather = ctx->pending_gather;
-    ctx->pending_append = nullptr, ctx->pending_len_ptr = nullptr, ctx->pending_gather = nullptr;
+    const TqPackArgs *append = extras ? extras->append : nullptr;  // this step's new token, encoded by the same launch
+    const int *len_ptr = extras ? extras->len_ptr : nullptr;       // sequence length kept on the device
+    const tq_gather_desc *gather = extras ? extras->gather : nullptr;
     if (gather && n_tail) return TQ_ERR_UNSUPPORTED;
     int rc = tq_launch_qprep_frag(ctx, q, q_dtype, rows / groups, groups, frag, append, stream);
     if (rc) return rc;

@@ -81,5 +81,5 @@ extern "C" int32_t tq_decode_attn_static(tq_ctx *ctx, const void *q, int32_t q_d
         return tq_launch_decode_exact(ctx, q, q_dtype, q_heads, cache, seq_len, nullptr, nullptr, 0, n_splits, scratch,
                                       out, s);
     return tq_launch_decode_mma4(ctx, q, q_dtype, q_heads, cache, seq_len, nullptr, nullptr, 0, n_splits, scratch, out,
-                                 s);
+                                 nullptr, s);
 }

@@ -213,6 +213,14 @@ def run_gpu_arm(args) -> None:
         w["batch_per_gpu"] = args.batch_per_gpu
     if args.context:
         w["context"] = args.context
+    if args.q_heads:
+        w["q_heads"] = args.q_heads
+    if args.kv_heads:
+        w["kv_heads"] = args.kv_heads
+    if args.bits:
+        w["bits"] = args.bits
+    if args.batch_per_gpu or args.context or args.q_heads or args.kv_heads or args.bits:
+        w["name"] += " (shape overridden)"
     if w["kv_heads"] % world:
         raise SystemExit(f"{w['kv_heads']} KV heads do not shard over {world} ranks")
     dtype = getattr(torch, w["dtype"])
@@ -596,6 +604,9 @@ def main() -> None:
     ap.add_argument("--batch-per-gpu", type=int, default=None,
                     help="override the workload's batch (profiling captures use a smaller one)")
     ap.add_argument("--context", type=int, default=None, help="override the context length (profiling captures)")
+    ap.add_argument("--q-heads", type=int, default=None, help="override the query-head count (profiling captures)")
+    ap.add_argument("--kv-heads", type=int, default=None, help="override the KV-head count (profiling captures)")
+    ap.add_argument("--bits", type=int, default=None, choices=[2, 3, 4], help="override the bit width (profiling captures)")
     ap.add_argument("--splits", type=int, default=None, help="override the library's split choice")
     ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling captures)")
     ap.add_argument("--workload", default="layer", choices=["layer", "model"],

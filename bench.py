@@ -345,18 +345,18 @@ def run_gpu_arm(args) -> None:
         if world == 1:
             # the library's host-buffer entry point: H2D of q / k / v, append, attend, D2H of the output
             host_step()
+        elif peer is not None:
+            # shard: host buffers in, gathered output of all ranks straight into the host buffer
+            store.decode_step_host_gather(h_q, h_k, h_v, h_out, peer)
         else:
             d_q.copy_(h_q, non_blocking=True)
             d_k.copy_(h_k, non_blocking=True)
             d_v.copy_(h_v, non_blocking=True)
             store.pack(d_k, d_v)
-            if peer is not None:
-                h_out.copy_(store.decode_attn_gather(d_q, peer, splits=splits), non_blocking=True)
-            else:
-                store.decode_attn(d_q, splits=splits, out=out)
-                dist.all_gather_into_tensor(gathered, out)
-                h_out.view(batch, world, hq, HEAD_DIM).copy_(
-                    gathered.view(world, batch, hq, HEAD_DIM).transpose(0, 1), non_blocking=True)
+            store.decode_attn(d_q, splits=splits, out=out)
+            dist.all_gather_into_tensor(gathered, out)
+            h_out.view(batch, world, hq, HEAD_DIM).copy_(
+                gathered.view(world, batch, hq, HEAD_DIM).transpose(0, 1), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the host needs the result before the next token
 
     e2e_steps = 0 if args.skip_e2e else steps

@@ -220,6 +220,15 @@ int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
                               const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits,
                               void *workspace, size_t workspace_bytes, const tq_gather_desc *gather,
                               tq_stream stream);
+/* tq_decode_step_host for a KV-head shard: q_host [batch, q_heads, 128] and k_host / v_host
+ * [batch, kv_heads, 128] are this rank's heads, out_host receives the gathered output of all
+ * ranks [batch, q_heads_total, 128].  All four buffers must be page-locked host memory mapped
+ * into the device's address space (or device memory); 16-bit dtypes only.  Queues the append,
+ * the attention, the exchange and the wait. */
+int32_t tq_decode_step_host_gather(tq_ctx *ctx, const void *q_host, const void *k_host, const void *v_host,
+                                   int32_t dtype, int32_t q_heads, const tq_cache_desc *cache, int32_t pos,
+                                   int32_t n_splits, void *workspace, size_t workspace_bytes,
+                                   const tq_gather_desc *gather, void *out_host, tq_stream stream);
 /* Stream-ordered wait for all ranks' flags of the step (see above).  With out_final != NULL the
  * gathered output [batch, q_heads_total, 128] is then copied from this rank's buffer of the step
  * into out_final (device memory), which is what a caller needs when the step number lives on the

@@ -42,6 +42,27 @@ def main() -> None:
     finally:
         gather.close()
 
+    # host buffers in, gathered output into a host buffer (append + attend + exchange in one call)
+    host_store = PackedStore(codec, B, Hkv // world, capacity=N + 8)
+    ref2 = PackedStore(codec, B, Hkv // world, capacity=N + 8)
+    for st in (host_store, ref2):
+        st.pack(shard.local_kv(k[:, :, :N - 4]), shard.local_kv(v[:, :, :N - 4]))
+    gather = PeerGather(shard, B, Hq, torch.bfloat16, dev)
+    try:
+        h_out = torch.empty(B, Hq, 1, 128, dtype=torch.bfloat16).pin_memory()
+        for t in range(3):
+            pos = N - 4 + t
+            kt, vt = shard.local_kv(k[:, :, pos:pos + 1]), shard.local_kv(v[:, :, pos:pos + 1])
+            ref2.pack(kt, vt)
+            want = shard.gather_heads(ref2.decode_attn(shard.local_q(qs[t], Hkv)))
+            host_store.decode_step_host_gather(shard.local_q(qs[t], Hkv).contiguous().cpu().pin_memory(),
+                                               kt.contiguous().cpu().pin_memory(), vt.contiguous().cpu().pin_memory(),
+                                               h_out, gather)
+            torch.cuda.synchronize()
+            assert torch.equal(h_out, want.cpu()), f"rank {rank} host step {t}"
+    finally:
+        gather.close()
+
     # the same exchange inside the device-length step, numbered on the device and replayed from a
     # CUDA graph; the reference is the un-sharded result of the NCCL path
     N0 = N - 4

@@ -321,6 +321,35 @@ extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const vo
     return TQ_OK;
 }
 
+extern "C" int32_t tq_decode_step_host_gather(tq_ctx *ctx, const void *q_host, const void *k_host, const void *v_host,
+                                              int32_t dtype, int32_t q_heads, const tq_cache_desc *cache, int32_t pos,
+                                              int32_t n_splits, void *workspace, size_t workspace_bytes,
+                                              const tq_gather_desc *gather, void *out_host, tq_stream stream) {
+    if (!ctx || !q_host || !k_host || !v_host || !out_host || !workspace || !cache || !gather) return TQ_ERR_ARG;
+    if (pos < 0 || pos >= cache->capacity || n_splits < 1) return TQ_ERR_ARG;
+    if (dtype != TQ_DTYPE_F16 && dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
+    int32_t rc = check_cache(ctx, cache);
+    if (rc) return rc;
+    if (q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
+    if (q_heads / cache->kv_heads > TQ_MAX_GROUPS) return TQ_ERR_UNSUPPORTED;
+    if (gather->world < 1 || gather->world > TQ_MAX_PEERS || gather->q_heads_total != q_heads * gather->world)
+        return TQ_ERR_ARG;
+    if (workspace_bytes < tq_decode_workspace_bytes(cache->batch, q_heads, n_splits)) return TQ_ERR_WORKSPACE;
+    // the kernels read and write the host buffers themselves: they must be page-locked and mapped
+    void *d_q = device_view(q_host), *d_k = device_view(k_host), *d_v = device_view(v_host);
+    void *d_out = device_view(out_host);
+    if (!d_q || !d_k || !d_v || !d_out) return TQ_ERR_ARG;
+    tq_dense_desc kd = {d_k, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
+    tq_dense_desc vd = {d_v, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
+    TqPackArgs append;
+    tq_fill_pack_args(ctx, &kd, &vd, 1, cache, pos, &append);
+    const TqStepExtras extras = {&append, nullptr, gather};
+    rc = tq_launch_decode_mma4(ctx, d_q, dtype, q_heads, cache, pos + 1, nullptr, nullptr, 0, n_splits, workspace,
+                               nullptr, &extras, (cudaStream_t)stream);
+    if (rc) return rc;
+    return tq_gather_wait(ctx, gather, cache->batch, dtype, d_out, stream);
+}
+
 extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_new, const void *v_new, int32_t dtype,
                                       int32_t q_heads, const tq_cache_desc *cache, const int32_t *pos_dev,
                                       int32_t n_splits, void *workspace, size_t workspace_bytes, void *out,

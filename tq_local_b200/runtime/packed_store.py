@@ -210,6 +210,31 @@ class PackedStore:
         self.length += 1
         return out
 
+    def decode_step_host_gather(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, out: torch.Tensor,
+                                gather, splits: int | None = None) -> torch.Tensor:
+        """``decode_step_host`` for a KV-head shard: ``q`` / ``k_new`` / ``v_new`` hold this rank's
+        heads, ``out`` [B, Hq_total, 1, 128] receives the gathered output of all ranks.  All four
+        must be pinned host tensors; ``gather`` is a host-sequenced ``PeerGather``."""
+        for t in (q, k_new, v_new, out):
+            if t.device.type != "cpu" or not t.is_contiguous() or not t.is_pinned():
+                raise ValueError("decode_step_host_gather takes contiguous pinned host tensors")
+        b, hq = int(q.shape[0]), int(q.shape[1])
+        if b != self.batch or k_new.shape[1] != self.kv_heads or q.dtype != k_new.dtype or out.dtype != q.dtype:
+            raise ValueError("shape or dtype mismatch")
+        if tuple(out.shape) != tuple(gather.shape):
+            raise ValueError(f"out must have the gathered shape {gather.shape}")
+        self.reserve(self.length + 1)
+        splits = self.suggest_splits(self.length + 1) if splits is None else int(splits)
+        ws = self._get_workspace(hq, splits)
+        desc, _ = gather.next_desc()
+        with torch.cuda.device(self.codec.device):
+            ffi.check(ffi.lib().tq_decode_step_host_gather(
+                self.codec.handle, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), tq_dtype(q.dtype), hq,
+                C.byref(self._desc), self.length, splits, ws.data_ptr(), ws.numel(), C.byref(desc), out.data_ptr(),
+                self._stream_ptr()), "tq_decode_step_host_gather")
+        self.length += 1
+        return out
+
     def bind_host_step(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, out: torch.Tensor):
         """``decode_step_host`` for a serving loop that reuses the same four host buffers every
         step: checks them once and returns a function that runs one step per call (append the

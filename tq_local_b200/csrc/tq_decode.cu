@@ -333,13 +333,31 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
         float o = 0.f, L = 0.f;
         if (g < n_heads) {
             const int64_t row = R * a.G + h0 + g;
-            float M = -INFINITY;
-            for (int s = 0; s < n_valid; ++s) M = fmaxf(M, a.part_m[row * a.n_splits + s]);
-            for (int s = 0; s < n_valid; ++s) {
-                const float ms = a.part_m[row * a.n_splits + s];
-                const float w = (ms == -INFINITY) ? 0.f : expf(ms - M);
-                L += a.part_l[row * a.n_splits + s] * w;
-                o += a.part_acc[(row * a.n_splits + s) * TQ_D + e] * w;
+            if (n_valid <= 4) {  // the usual case: everything is requested in one batch of loads
+                float pm[4], pl[4], pa[4];
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const bool on = s < n_valid;
+                    pm[s] = on ? a.part_m[row * a.n_splits + s] : -INFINITY;
+                    pl[s] = on ? a.part_l[row * a.n_splits + s] : 0.f;
+                    pa[s] = on ? a.part_acc[(row * a.n_splits + s) * TQ_D + e] : 0.f;
+                }
+                const float M = fmaxf(fmaxf(pm[0], pm[1]), fmaxf(pm[2], pm[3]));
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const float w = (pm[s] == -INFINITY) ? 0.f : expf(pm[s] - M);
+                    L += pl[s] * w;
+                    o += pa[s] * w;
+                }
+            } else {
+                float M = -INFINITY;
+                for (int s = 0; s < n_valid; ++s) M = fmaxf(M, a.part_m[row * a.n_splits + s]);
+                for (int s = 0; s < n_valid; ++s) {
+                    const float ms = a.part_m[row * a.n_splits + s];
+                    const float w = (ms == -INFINITY) ? 0.f : expf(ms - M);
+                    L += a.part_l[row * a.n_splits + s] * w;
+                    o += a.part_acc[(row * a.n_splits + s) * TQ_D + e] * w;
+                }
             }
         }
         s_o[g][e] = o;

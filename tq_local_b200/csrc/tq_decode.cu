@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(4 * TQ_D, 2) tq_step_prologue_kernel(TqQprepAr
 // the un-rotation matrix is read once for the G heads.
 template <typename T>
 __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs a) {
-    __shared__ float s_o[4][TQ_D];
+    __shared__ __align__(16) float s_o[4][TQ_D];
     __shared__ float s_part[4][4][TQ_D];  // [quarter of d][head][column]
     __shared__ float s_L[4];
     const int groups = (a.G + 3) >> 2;           // a block serves up to four heads of a KV row
@@ -382,22 +382,31 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
         const T res = tq_from_float<T>(v / fmaxf(s_L[g], 1e-8f));
         const int64_t row = R * a.G + h0 + g;  // = batch index * local query heads + local head
         if (a.gather_world > 0) {
-            const unsigned seq = a.gather_seq_ptr ? *a.gather_seq_ptr + 1u : a.gather_seq;
-            const long long buf = (seq & 1u) ? a.gather_out_stride : 0;
-            const int64_t bi = row / a.Hq, hl = row % a.Hq;
-            const int64_t dst = (bi * a.gather_heads_total + (int64_t)a.gather_rank * a.Hq + hl) * TQ_D + e;
-            for (int p = 0; p < a.gather_world; ++p)
-                reinterpret_cast<T *>(static_cast<char *>(a.gather_out[p]) + buf)[dst] = res;
+            reinterpret_cast<T *>(&s_o[0][0])[g * TQ_D + e] = res;  // staged: the peers get 16-byte stores below
         } else {
             ((T *)a.out)[row * TQ_D + e] = res;
         }
     }
     if (a.gather_world > 0) {
+        static_assert(sizeof(T) == 2 || sizeof(T) == 4, "");
+        __syncthreads();
+        // The block's heads are consecutive rows of one batch entry: one contiguous piece of every
+        // rank's gathered buffer.  Thread (p, i) stores 16-byte piece i of it into rank p's buffer.
+        const unsigned seq = a.gather_seq_ptr ? *a.gather_seq_ptr + 1u : a.gather_seq;
+        const long long buf = (seq & 1u) ? a.gather_out_stride : 0;
+        const int64_t row0 = R * a.G + h0;  // = batch index * local query heads + local head
+        const int64_t bi = row0 / a.Hq, hl = row0 % a.Hq;
+        const int64_t dst0 = (bi * a.gather_heads_total + (int64_t)a.gather_rank * a.Hq + hl) * TQ_D;  // elements
+        const int pieces = n_heads * TQ_D * (int)sizeof(T) / 16;
+        for (int w = tid; w < a.gather_world * pieces; w += blockDim.x) {
+            const int p = w / pieces, i = w % pieces;
+            uint4 *dst = reinterpret_cast<uint4 *>(static_cast<char *>(a.gather_out[p]) + buf + dst0 * sizeof(T));
+            dst[i] = reinterpret_cast<const uint4 *>(&s_o[0][0])[i];
+        }
         // the rank's last block tells every peer that this rank's rows of the step are in place
-        __threadfence_system();
         __syncthreads();
         if (tid == 0) {
-            const unsigned seq = a.gather_seq_ptr ? *a.gather_seq_ptr + 1u : a.gather_seq;
+            __threadfence_system();  // (cumulative: covers the block's stores ordered before the barrier)
             if (atomicAdd(a.gather_counter, 1u) == gridDim.x - 1) {  // every block has read the step number
                 *a.gather_counter = 0;
                 __threadfence_system();

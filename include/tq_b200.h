@@ -2,11 +2,16 @@
  * tq_b200.h — C ABI of the B200 (sm_100a) TurboQuant packed-KV library.
  *
  * Every entry point is extern "C", takes plain pointers and sizes, returns an
- * int32 status (0 = ok, negative = error, see TQ_ERR_*), never throws and —
- * except tq_ctx_create / tq_ctx_destroy — never allocates: the caller owns all
- * device buffers and passes the CUDA stream to launch on.  Kernels are
- * asynchronous on that stream.  A tq_ctx is bound to one device and may be used
- * from one host thread at a time.
+ * int32 status (0 = ok, negative = error, see TQ_ERR_*) and never throws.  The
+ * caller owns all device buffers and passes the CUDA stream to launch on; kernels
+ * are asynchronous on that stream.  The compute entry points (tq_pack, tq_decode_*,
+ * tq_dequant, tq_key_norm_sum, tq_gather_wait) allocate nothing.  The calls that
+ * allocate are: tq_ctx_create / tq_ctx_destroy (the device copy of the codec
+ * tables), tq_peer_buffer_create / tq_peer_buffer_destroy (device memory that other
+ * processes can map), and - only while tq_profile_enable is on - the decode calls,
+ * which then create the CUDA events they record.  A tq_ctx is bound to one device
+ * and may be used from one host thread at a time; one process may hold contexts on
+ * several devices.
  *
  * The functions replace these pieces of the reference (paths relative to the
  * reference project root):
@@ -249,6 +254,10 @@ size_t tq_static_scratch_bytes(void);
 int32_t tq_decode_attn_static(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
                               const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits, void *out,
                               tq_stream stream);
+
+/* How long tq_gather_wait polls for its peers before it gives up (milliseconds of the GPU's
+ * wall clock, 1 .. 60000; 2000 when never set).  The value is read when the wait is queued. */
+int32_t tq_set_wait_limit_ms(tq_ctx *ctx, int32_t limit_ms);
 
 /* Device-side status (no reference counterpart).  Kernels never spin without a limit: a
  * wait on an asynchronous copy that runs out sets a status word instead of hanging.  This

@@ -118,6 +118,7 @@ extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_de
     ctx->bits = c->bits;
     ctx->key_bits = kb;
     ctx->use_qjl = c->use_qjl ? 1 : 0;
+    ctx->wait_limit_ms = 2000;
     cudaDeviceProp prop;
     cudaError_t e = cudaGetDeviceProperties(&prop, device);
     if (e != cudaSuccess) {
@@ -169,7 +170,7 @@ extern "C" int32_t tq_ctx_destroy(tq_ctx *ctx) {
     return TQ_OK;
 }
 
-static int check_cache(const tq_ctx *ctx, const tq_cache_desc *c) {
+int tq_check_cache(const tq_ctx *ctx, const tq_cache_desc *c) {
     if (!c || !c->k_codes || !c->k_norms || !c->v_codes || !c->v_norms) return TQ_ERR_ARG;
     if (ctx->use_qjl && (!c->k_signs || !c->k_rnorms)) return TQ_ERR_ARG;
     if (c->batch <= 0 || c->kv_heads <= 0 || c->capacity <= 0) return TQ_ERR_ARG;
@@ -184,7 +185,7 @@ static int check_cache(const tq_ctx *ctx, const tq_cache_desc *c) {
 extern "C" int32_t tq_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,
                            const tq_cache_desc *cache, int32_t pos0, tq_stream stream) {
     if (!ctx || !k || !v || !k->data || !v->data) return TQ_ERR_ARG;
-    int rc = check_cache(ctx, cache);
+    int rc = tq_check_cache(ctx, cache);
     if (rc) return rc;
     if (n_tokens < 0 || pos0 < 0 || (int64_t)pos0 + n_tokens > cache->capacity) return TQ_ERR_ARG;
     if (k->dtype != v->dtype || k->dtype < 0 || k->dtype > 2) return TQ_ERR_ARG;
@@ -227,7 +228,7 @@ static int32_t decode_attn_impl(tq_ctx *ctx, const void *q, int32_t q_dtype, int
                                 const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits, void *workspace,
                                 size_t workspace_bytes, void *out, const TqStepExtras *extras, tq_stream stream) {
     if (!ctx || !q || !out || !workspace) return TQ_ERR_ARG;
-    int rc = check_cache(ctx, cache);
+    int rc = tq_check_cache(ctx, cache);
     if (rc) return rc;
     if (q_dtype < 0 || q_dtype > 2) return TQ_ERR_ARG;
     if (seq_len < 0 || seq_len > cache->capacity || n_tail < 0 || n_splits < 1) return TQ_ERR_ARG;
@@ -276,11 +277,18 @@ extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const vo
                                        int32_t dtype, int32_t q_heads, const tq_cache_desc *cache, int32_t pos,
                                        int32_t n_splits, void *workspace, size_t workspace_bytes, void *out_host,
                                        tq_stream stream) {
+    // every check comes before the first copy or launch: a call that fails leaves the cache and
+    // the workspace untouched
     if (!ctx || !q_host || !k_host || !v_host || !out_host || !workspace || !cache) return TQ_ERR_ARG;
-    if (dtype < 0 || dtype > 2 || pos < 0 || pos >= cache->capacity) return TQ_ERR_ARG;
-    if (cache->batch <= 0 || cache->kv_heads <= 0 || q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
-    if (workspace_bytes < tq_decode_step_workspace_bytes(cache->batch, q_heads, cache->kv_heads, n_splits))
-        return TQ_ERR_WORKSPACE;
+    int32_t rc = tq_check_cache(ctx, cache);
+    if (rc) return rc;
+    if (dtype < 0 || dtype > 2 || pos < 0 || pos >= cache->capacity || n_splits < 1) return TQ_ERR_ARG;
+    if (q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
+    if (q_heads / cache->kv_heads > TQ_MAX_GROUPS) return TQ_ERR_UNSUPPORTED;
+    if ((uintptr_t)workspace & 15) return TQ_ERR_ARG;
+    const size_t need = tq_decode_step_workspace_bytes(cache->batch, q_heads, cache->kv_heads, n_splits);
+    if (need == 0) return TQ_ERR_ARG;
+    if (workspace_bytes < need) return TQ_ERR_WORKSPACE;
     const size_t es = dtype == TQ_DTYPE_F32 ? 4 : 2;
     const size_t q_bytes = (size_t)cache->batch * q_heads * TQ_D * es;
     const size_t kv_bytes = (size_t)cache->batch * cache->kv_heads * TQ_D * es;
@@ -302,11 +310,9 @@ extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const vo
     }
     tq_dense_desc kd = {d_k, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
     tq_dense_desc vd = {d_v, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
-    int32_t rc = check_cache(ctx, cache);
-    if (rc) return rc;
     TqPackArgs append;
     TqStepExtras extras = {nullptr, nullptr, nullptr};
-    if (dtype != TQ_DTYPE_F32 && q_heads / cache->kv_heads <= TQ_MAX_GROUPS) {
+    if (dtype != TQ_DTYPE_F32) {
         // the tensor-core decode path encodes the new token in its own query-preparation launch
         tq_fill_pack_args(ctx, &kd, &vd, 1, cache, pos, &append);
         extras.append = &append;
@@ -328,12 +334,13 @@ extern "C" int32_t tq_decode_step_host_gather(tq_ctx *ctx, const void *q_host, c
     if (!ctx || !q_host || !k_host || !v_host || !out_host || !workspace || !cache || !gather) return TQ_ERR_ARG;
     if (pos < 0 || pos >= cache->capacity || n_splits < 1) return TQ_ERR_ARG;
     if (dtype != TQ_DTYPE_F16 && dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
-    int32_t rc = check_cache(ctx, cache);
+    int32_t rc = tq_check_cache(ctx, cache);
     if (rc) return rc;
     if (q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
     if (q_heads / cache->kv_heads > TQ_MAX_GROUPS) return TQ_ERR_UNSUPPORTED;
-    if (gather->world < 1 || gather->world > TQ_MAX_PEERS || gather->q_heads_total != q_heads * gather->world)
-        return TQ_ERR_ARG;
+    rc = tq_check_gather(gather);  // before any launch: the combine kernel stores through these pointers
+    if (rc) return rc;
+    if (gather->q_heads_total != q_heads * gather->world || (uintptr_t)workspace & 15) return TQ_ERR_ARG;
     if (workspace_bytes < tq_decode_workspace_bytes(cache->batch, q_heads, n_splits)) return TQ_ERR_WORKSPACE;
     // the kernels read and write the host buffers themselves: they must be page-locked and mapped
     void *d_q = device_view(q_host), *d_k = device_view(k_host), *d_v = device_view(v_host);
@@ -355,11 +362,13 @@ extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_
                                       int32_t n_splits, void *workspace, size_t workspace_bytes, void *out,
                                       const tq_gather_desc *gather, tq_stream stream) {
     if (!ctx || !q || !k_new || !v_new || !out || !workspace || !pos_dev) return TQ_ERR_ARG;
-    if (gather && (!gather->seq_dev || gather->world < 1 || gather->world > TQ_MAX_PEERS ||
-                   gather->q_heads_total != q_heads * gather->world))
-        return TQ_ERR_ARG;
-    int32_t rc = check_cache(ctx, cache);
+    int32_t rc = tq_check_cache(ctx, cache);
     if (rc) return rc;
+    if (gather) {  // validated before any launch: the combine kernel stores through these pointers
+        rc = tq_check_gather(gather);
+        if (rc) return rc;
+        if (!gather->seq_dev || gather->q_heads_total != q_heads * gather->world) return TQ_ERR_ARG;
+    }
     if (dtype < 0 || dtype > 2 || n_splits < 1) return TQ_ERR_ARG;
     if (q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
     if (dtype == TQ_DTYPE_F32 || q_heads / cache->kv_heads > TQ_MAX_GROUPS) return TQ_ERR_UNSUPPORTED;
@@ -381,7 +390,7 @@ extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_
 extern "C" int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,
                               int32_t n_tokens, const tq_dense_desc *out, tq_stream stream) {
     if (!ctx || !out || !out->data) return TQ_ERR_ARG;
-    int rc = check_cache(ctx, cache);
+    int rc = tq_check_cache(ctx, cache);
     if (rc) return rc;
     if (which < 0 || which > 1 || out->dtype < 0 || out->dtype > 2) return TQ_ERR_ARG;
     if (n_tokens < 0 || pos0 < 0 || (int64_t)pos0 + n_tokens > cache->capacity) return TQ_ERR_ARG;

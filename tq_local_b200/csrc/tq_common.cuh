@@ -11,6 +11,7 @@
 #include "../../include/tq_b200.h"
 
 #define TQ_D 128
+#define TQ_MAX_DEVICES 64  // devices one process may hold contexts on
 
 // Device-resident codec tables.  Matrices are [128][128] fp32, row-major.
 struct tq_ctx {
@@ -39,6 +40,7 @@ struct tq_ctx {
     size_t base_bytes;
     struct tq_prof *prof;  // measurement hooks, see tq_profile_enable
     int *error_flag;       // device word, set by a kernel whose bounded wait ran out
+    int wait_limit_ms;     // how long tq_gather_wait polls for a peer before it gives up (tq_set_wait_limit_ms)
     int64_t splits_cache_key;  // last (rows, length bucket) asked of tq_decode_suggest_splits
     int splits_cache_val;
 };
@@ -106,6 +108,12 @@ __device__ __forceinline__ float tq_warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+
+// Argument validators shared by every entry point that takes the descriptor (nothing is
+// launched before they pass): all stream pointers present and 16-byte aligned, strides
+// multiples of 8 tokens that do not overlap rows; every peer pointer and the counter present.
+int tq_check_cache(const tq_ctx *ctx, const tq_cache_desc *c);
+int tq_check_gather(const tq_gather_desc *g);
 
 // Entry points implemented in the other translation units.
 int32_t tq_launch_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,

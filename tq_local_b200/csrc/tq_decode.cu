@@ -418,11 +418,19 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
     }
 }
 
+__device__ __forceinline__ unsigned long long tq_global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+
 // Waits until the flags of all ranks show the step's sequence number (written by the peers'
-// combine kernels), for at most about two seconds; then, optionally, every block copies its
-// slice of this rank's gathered buffer of the step to `dst`.
+// combine kernels), for at most `limit_ns` nanoseconds of the GPU's wall clock; a wait that
+// runs out sets the status word to 5 and the kernel returns without copying.  Otherwise,
+// optionally, every block copies its slice of this rank's gathered buffer of the step to `dst`.
 __global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned seq_arg, const unsigned *seq_ptr,
-                                      int *error_flag, const uint4 *src0, long long stride, uint4 *dst, size_t n16) {
+                                      int *error_flag, unsigned long long limit_ns, const uint4 *src0, long long stride,
+                                      uint4 *dst, size_t n16) {
     // A step numbered on the device gets its number from the combine kernel's last block, so that
     // kernel has to be complete before the number is read; a host-numbered step may start polling early.
     if (seq_ptr) tq_grid_dependency_wait();
@@ -431,10 +439,10 @@ __global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned
     if (threadIdx.x == 0) s_failed = 0;
     __syncthreads();
     if ((int)threadIdx.x < world) {
-        const long long t0 = clock64();
+        const unsigned long long t0 = tq_global_ns();
         const volatile unsigned *f = flags + threadIdx.x;
         while ((int)(*f - seq) < 0) {  // (flags only grow; a peer may already be one step ahead)
-            if (clock64() - t0 > 4000000000ll) {
+            if (tq_global_ns() - t0 > limit_ns) {
                 atomicExch(error_flag, 5);
                 s_failed = 1;
                 break;
@@ -545,7 +553,7 @@ int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, c
     return TQ_OK;
 }
 
-int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, size_t bytes, void *out_final,
+int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limit_ms, size_t bytes, void *out_final,
                               cudaStream_t stream) {
     const size_t n16 = out_final ? bytes / 16 : 0;
     const int blocks = out_final ? (int)((n16 + 255) / 256 < 64 ? (n16 + 255) / 256 : 64) : 1;
@@ -556,6 +564,7 @@ int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, size_t b
     cudaError_t e = tq_launch_kernel(tq_gather_wait_kernel, dim3(blocks < 1 ? 1 : blocks), dim3(256), 0, stream, true,
                                      (const unsigned *)g->flags[g->rank], (int)g->world, (unsigned)g->seq,
                                      (const unsigned *)g->seq_dev, error_flag,
+                                     (unsigned long long)(limit_ms < 1 ? 1 : limit_ms) * 1000000ull,
                                      reinterpret_cast<const uint4 *>(g->out[g->rank]), (long long)g->out_stride,
                                      reinterpret_cast<uint4 *>(out_final), n16);
     TQ_CUDA_CHECK(e);

@@ -19,9 +19,10 @@
 // quad its own head:
 //   logits   S  [16 tok x (4 heads x {hi, lo})] = Kdeq[16 x 128] * {Qrot_hi, Qrot_lo}   f16 m16n8k16
 //            (the rotated query is split in two f16 terms, so its rounding does not show)
-//   QJL      S2 [16 tok x (4 heads x {hi, lo})] = -Bit[16 x 128] * {Qp_hi, Qp_lo}       s8 m16n8k32
-//            (sign bits become 0 / -1 bytes four at a time with a sign-replicating byte
-//            permute; the projected query is 16-bit fixed point in two s8 terms)
+//   QJL      S2 [16 tok x (4 heads x {hi, lo})] = Bit[16 x 128] * {Qp_hi, Qp_lo}        s8 m16n8k32
+//            (a mask keeps sign bit n of each of four bytes in place, so an operand byte is
+//            2^n or 0 and costs one logic instruction per four signs; the projected query is
+//            16-bit fixed point in two s8 terms, divided by 2^n behind bit n, n = 0..3)
 //   values   O^T[128 x (4 heads x {P, 0})] += Vdeq^T[128 x 16 tok] * P                   f16 m16n8k16
 // A operands are built in registers from the packed words.  The contraction order of an
 // MMA is free, so every lane gets codes that sit together in memory:
@@ -40,6 +41,23 @@
 #include "tq_decode_shared.cuh"
 #include "tq_mma_utils.cuh"
 #include "tq_step_blocks.cuh"
+
+// Build with -DTQ_TIMELINE to make every CTA record wall-clock stamps of its phases
+// (read back with tq_debug_stamps); compiled out otherwise.
+#ifdef TQ_TIMELINE
+__device__ unsigned long long g_stamps[160 * 16];
+#define TQ_STAMP(i)                                                                          \
+    do {                                                                                     \
+        if (threadIdx.x == 0 && blockIdx.x < 160 && (i) < 16) {                              \
+            unsigned long long t_;                                                           \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                           \
+            g_stamps[blockIdx.x * 16 + (i)] = t_;                                            \
+        }                                                                                    \
+    } while (0)
+extern "C" int tq_debug_stamps(unsigned long long *out) { return (int)cudaMemcpyFromSymbol(out, g_stamps, sizeof(g_stamps)); }
+#else
+#define TQ_STAMP(i) do {} while (0)
+#endif
 
 namespace {
 
@@ -74,6 +92,7 @@ struct Mma4Args {
     float *part_m, *part_l, *part_acc;
     const float *centers_k, *centers_v;
     int *error_flag;  // set to 1 when a bounded wait ran out
+    int device;       // host side only: the context's device
 };
 
 template <int KB, int VB, bool QJL> struct StageLayout {
@@ -189,6 +208,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         }
     }
     uint32_t *table = reinterpret_cast<uint32_t *>(smem + (kTableAddr - dyn_base));
+    TQ_STAMP(0);
+    int seg_no = 0;
 
     const int G = a.G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -236,6 +257,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     }
 
     __syncthreads();  // tables complete
+    TQ_STAMP(1);
 
     const float kA = 0.08838834764831845f * 1.4426950408889634f;  // (1/sqrt(128)) * log2(e)
     const float kB = kA * (1.2533141373155003f / (float)TQ_D);     // ... * sqrt(pi/2)/D
@@ -298,6 +320,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     }
     if (first_segment) {
         tq_grid_dependency_wait();
+        TQ_STAMP(2);
         for (int it = 0; it < n_first; ++it)
             if (deferred >> it & 1) issue(it);
         first_segment = false;
@@ -340,6 +363,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
             sign_bias[hl] = QJL ? __uint_as_float(__ldg(mine + 25)) : 0.f;
         }
     }
+    if (seg_no == 0) TQ_STAMP(3);
     float m_run[NH], l_run[NH];
 #pragma unroll
     for (int hl = 0; hl < NH; ++hl) m_run[hl] = -INFINITY, l_run[hl] = 0.f;
@@ -402,14 +426,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
             if (QJL) {
                 const uint32_t sa = reinterpret_cast<const uint32_t *>(spS + slotA * 16)[t];
                 const uint32_t sb = reinterpret_cast<const uint32_t *>(spS + slotB * 16)[t];
+                const uint32_t sa4 = sa >> 4, sb4 = sb >> 4;
                 int d2[4] = {0, 0, 0, 0};
                 int d2l[4] = {0, 0, 0, 0};  // wide: the lo-term products
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
-                    const uint32_t a0 = prmt(sa << (2 * n), 0u, 0xBA98u);
-                    const uint32_t a1 = prmt(sb << (2 * n), 0u, 0xBA98u);
-                    const uint32_t a2 = prmt(sa << (2 * n + 1), 0u, 0xBA98u);
-                    const uint32_t a3 = prmt(sb << (2 * n + 1), 0u, 0xBA98u);
+                    // sign bit n of every byte stays where it is (value 2^n or 0); the projected
+                    // query behind it was divided by 2^n when its fragment was built
+                    const uint32_t a0 = sa & (0x01010101u << n);
+                    const uint32_t a1 = sb & (0x01010101u << n);
+                    const uint32_t a2 = sa4 & (0x01010101u << n);
+                    const uint32_t a3 = sb4 & (0x01010101u << n);
                     mma_s8(d2, a0, a1, a2, a3, bp[n][0], bp[n][1]);
                     if (WIDE) mma_s8(d2l, a0, a1, a2, a3, bp[(WIDE ? 4 : 0) + n][0], bp[(WIDE ? 4 : 0) + n][1]);
                 }
@@ -513,10 +540,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         }
     }
     ring_pos += n_iter;
+    TQ_STAMP(5 + 3 * seg_no);
 
     // ---- merge the warps of the CTA and write this segment's partial.  The merge buffer
     // reuses the first rings' memory, which is idle here: every issued stage was consumed.
     __syncthreads();
+    TQ_STAMP(6 + 3 * seg_no);
     float *s_acc = reinterpret_cast<float *>(smem);   // [kWarps][4][128]
     float *s_m = s_acc + kWarps * 4 * TQ_D;           // [kWarps][4]
     float *s_l = s_m + kWarps * 4;
@@ -554,8 +583,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         }
     }
     __syncthreads();  // the merge buffer is free again before the next segment refills the rings
+    TQ_STAMP(7 + 3 * seg_no);
+    ++seg_no;
     }  // segment loop
     if (timed_out && lane == 0) atomicExch(a.error_flag, 1);
+    TQ_STAMP(14);
 }
 
 template <int KB, int VB, bool QJL> size_t mma4_smem_bytes() { return 227 * 1024; }
@@ -563,12 +595,14 @@ template <int KB, int VB, bool QJL> size_t mma4_smem_bytes() { return 227 * 1024
 template <int KB, int VB, bool QJL, bool WIDE>
 cudaError_t launch_mma4_variant(const Mma4Args &a, dim3 grid, cudaStream_t stream) {
     const size_t smem = mma4_smem_bytes<KB, VB, QJL>();
-    static bool configured = false;  // per instantiation
-    if (!configured) {
+    // the attribute belongs to the (kernel, device) pair: one flag per device of this instantiation
+    static bool configured[TQ_MAX_DEVICES] = {};
+    if (a.device < 0 || a.device >= TQ_MAX_DEVICES) return cudaErrorInvalidDevice;
+    if (!configured[a.device]) {
         cudaError_t e = cudaFuncSetAttribute(tq_decode_mma4_kernel<KB, VB, QJL, WIDE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured[a.device] = true;
     }
     return tq_launch_kernel(tq_decode_mma4_kernel<KB, VB, QJL, WIDE>, grid, dim3(kWarps * 32), smem, stream,
                             /*programmatic=*/true, a);
@@ -619,7 +653,11 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     a.part_m = w.part_m, a.part_l = w.part_l, a.part_acc = w.part_acc;
     a.centers_k = ctx->centers_k, a.centers_v = ctx->centers_v;
     a.error_flag = ctx->error_flag;
-    dim3 grid(len_ptr ? (unsigned)ctx->sm_count : (unsigned)((total + a.chunk - 1) / a.chunk));
+    a.device = ctx->device;
+    // Length on the device: the kernel plans for its own grid.  One CTA per SM, except that a
+    // single partial per row (n_splits == 1) means one CTA per row, however many rows there are.
+    const unsigned dev_grid = n_splits == 1 && a.rows > ctx->sm_count ? (unsigned)a.rows : (unsigned)ctx->sm_count;
+    dim3 grid(len_ptr ? dev_grid : (unsigned)((total + a.chunk - 1) / a.chunk));
     const int mode = ctx->use_qjl * 10 + ctx->bits;
     tq_prof_count(ctx, 3);
     tq_prof_begin(ctx, stream);

@@ -53,11 +53,9 @@ extern "C" size_t tq_static_scratch_bytes(void) { return kStaticScratchBytes; }
 extern "C" int32_t tq_decode_attn_static(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
                                          const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits, void *out,
                                          tq_stream stream) {
-    if (!ctx || !q || !out || !cache) return TQ_ERR_ARG;
-    if (!cache->k_codes || !cache->k_norms || !cache->v_codes || !cache->v_norms) return TQ_ERR_ARG;
-    if (ctx->use_qjl && (!cache->k_signs || !cache->k_rnorms)) return TQ_ERR_ARG;
-    if (cache->batch <= 0 || cache->kv_heads <= 0 || cache->capacity <= 0) return TQ_ERR_ARG;
-    if ((cache->stride_b & 7) || (cache->stride_h & 7) || cache->stride_h < cache->capacity) return TQ_ERR_ARG;
+    if (!ctx || !q || !out) return TQ_ERR_ARG;
+    int32_t rc = tq_check_cache(ctx, cache);  // the same descriptor checks as tq_decode_attn
+    if (rc) return rc;
     if (q_dtype < 0 || q_dtype > 2 || n_splits < 1) return TQ_ERR_ARG;
     if (seq_len <= 0 || seq_len > cache->capacity) return TQ_ERR_ARG;
     if (q_heads <= 0 || q_heads % cache->kv_heads) return TQ_ERR_ARG;
@@ -74,7 +72,7 @@ extern "C" int32_t tq_decode_attn_static(tq_ctx *ctx, const void *q, int32_t q_d
     TQ_CUDA_CHECK(cudaGetDevice(&current));
     if (current != ctx->device) return TQ_ERR_ARG;
     void *scratch = nullptr;
-    int32_t rc = static_scratch_for(current, &scratch);
+    rc = static_scratch_for(current, &scratch);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     if (q_dtype == TQ_DTYPE_F32)

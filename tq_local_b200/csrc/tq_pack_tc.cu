@@ -450,13 +450,15 @@ void tq_build_operand_image(const float *m, uint16_t *image) {
 }
 
 template <typename T, int BITS, bool QJL>
-static cudaError_t launch_tc(const PackTcArgs &a, int grid, cudaStream_t stream) {
+static cudaError_t launch_tc(const PackTcArgs &a, int grid, int device, cudaStream_t stream) {
     const int smem = 6 * kTermBytes + 1024;
-    static bool configured = false;
-    if (!configured) {
+    // the attribute belongs to the (kernel, device) pair: one flag per device of this instantiation
+    static bool configured[TQ_MAX_DEVICES] = {};
+    if (device < 0 || device >= TQ_MAX_DEVICES) return cudaErrorInvalidDevice;
+    if (!configured[device]) {
         cudaError_t e = cudaFuncSetAttribute(tq_pack_tc_kernel<T, BITS, QJL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured[device] = true;
     }
     tq_pack_tc_kernel<T, BITS, QJL><<<grid, kThreads, smem, stream>>>(a);
     return cudaGetLastError();
@@ -491,10 +493,10 @@ int32_t tq_launch_pack_tc(tq_ctx *ctx, const tq_dense_desc *x, int which, int32_
     cudaError_t e = cudaErrorInvalidValue;
 #define TQ_TC_CASE(T)                                                                                     \
     switch (bits) {                                                                                       \
-        case 1: e = qjl ? launch_tc<T, 1, true>(a, grid, stream) : cudaErrorInvalidValue; break;          \
-        case 2: e = qjl ? launch_tc<T, 2, true>(a, grid, stream) : launch_tc<T, 2, false>(a, grid, stream); break; \
-        case 3: e = qjl ? launch_tc<T, 3, true>(a, grid, stream) : launch_tc<T, 3, false>(a, grid, stream); break; \
-        case 4: e = qjl ? cudaErrorInvalidValue : launch_tc<T, 4, false>(a, grid, stream); break;         \
+        case 1: e = qjl ? launch_tc<T, 1, true>(a, grid, ctx->device, stream) : cudaErrorInvalidValue; break;          \
+        case 2: e = qjl ? launch_tc<T, 2, true>(a, grid, ctx->device, stream) : launch_tc<T, 2, false>(a, grid, ctx->device, stream); break; \
+        case 3: e = qjl ? launch_tc<T, 3, true>(a, grid, ctx->device, stream) : launch_tc<T, 3, false>(a, grid, ctx->device, stream); break; \
+        case 4: e = qjl ? cudaErrorInvalidValue : launch_tc<T, 4, false>(a, grid, ctx->device, stream); break;         \
         default: return TQ_ERR_UNSUPPORTED;                                                               \
     }
     if (x->dtype == TQ_DTYPE_F32) {

@@ -43,7 +43,7 @@ extern "C" int32_t tq_peer_buffer_destroy(void *dev_ptr) {
     return TQ_OK;
 }
 
-static int check_gather(const tq_gather_desc *g) {
+int tq_check_gather(const tq_gather_desc *g) {
     if (!g || g->world < 1 || g->world > TQ_MAX_PEERS || g->rank < 0 || g->rank >= g->world) return TQ_ERR_ARG;
     if ((g->seq == 0 && !g->seq_dev) || !g->counter || g->q_heads_total <= 0) return TQ_ERR_ARG;
     if (g->out_stride < 0 || (g->out_stride & 15) || ((uintptr_t)g->seq_dev & 3)) return TQ_ERR_ARG;
@@ -56,13 +56,11 @@ extern "C" int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_d
                                          const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits,
                                          void *workspace, size_t workspace_bytes, const tq_gather_desc *gather,
                                          tq_stream stream) {
-    if (!ctx || !q || !workspace || !cache) return TQ_ERR_ARG;
-    int rc = check_gather(gather);
+    if (!ctx || !q || !workspace) return TQ_ERR_ARG;
+    int rc = tq_check_gather(gather);
     if (rc) return rc;
-    if (!cache->k_codes || !cache->k_norms || !cache->v_codes || !cache->v_norms) return TQ_ERR_ARG;
-    if (ctx->use_qjl && (!cache->k_signs || !cache->k_rnorms)) return TQ_ERR_ARG;
-    if (cache->batch <= 0 || cache->kv_heads <= 0 || cache->capacity <= 0) return TQ_ERR_ARG;
-    if ((cache->stride_b & 7) || (cache->stride_h & 7) || cache->stride_h < cache->capacity) return TQ_ERR_ARG;
+    rc = tq_check_cache(ctx, cache);
+    if (rc) return rc;
     if (q_dtype != TQ_DTYPE_F16 && q_dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
     if (seq_len <= 0 || seq_len > cache->capacity || n_splits < 1) return TQ_ERR_ARG;
     if (q_heads <= 0 || q_heads % cache->kv_heads || q_heads / cache->kv_heads > TQ_MAX_GROUPS) return TQ_ERR_ARG;
@@ -77,12 +75,18 @@ extern "C" int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_d
 extern "C" int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, int32_t batch, int32_t dtype,
                                   void *out_final, tq_stream stream) {
     if (!ctx) return TQ_ERR_ARG;
-    int rc = check_gather(gather);
+    int rc = tq_check_gather(gather);
     if (rc) return rc;
     size_t bytes = 0;
     if (out_final) {
         if (batch <= 0 || (dtype != TQ_DTYPE_F16 && dtype != TQ_DTYPE_BF16) || ((uintptr_t)out_final & 15)) return TQ_ERR_ARG;
         bytes = (size_t)batch * gather->q_heads_total * TQ_D * 2;
     }
-    return tq_launch_gather_wait(gather, ctx->error_flag, bytes, out_final, (cudaStream_t)stream);
+    return tq_launch_gather_wait(gather, ctx->error_flag, ctx->wait_limit_ms, bytes, out_final, (cudaStream_t)stream);
+}
+
+extern "C" int32_t tq_set_wait_limit_ms(tq_ctx *ctx, int32_t limit_ms) {
+    if (!ctx || limit_ms < 1 || limit_ms > 60000) return TQ_ERR_ARG;
+    ctx->wait_limit_ms = limit_ms;
+    return TQ_OK;
 }

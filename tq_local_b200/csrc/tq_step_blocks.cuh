@@ -260,14 +260,16 @@ template <typename T> __device__ __forceinline__ void tq_qprep_block(const TqQpr
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
         if (lane == 0) {
-            // <qp, sign> = scale * (2 * sum_{bit set} x - sum x); the MMA yields -(sum over set bits)
+            // <qp, sign> = scale * (2 * sum_{bit set} x - sum x); the MMA yields the sum over set bits
             const float scale = amax > 0.f ? amax / 32000.0f : 0.f;
-            s_scale[warp] = -2.0f * scale;
+            s_scale[warp] = 2.0f * scale;
             s_bias[warp] = -scale * (float)isum;
         }
     }
     __syncthreads();
-    // G heads x 8 variants x 10 words: s8 hi / lo terms behind sign bits (7 - 2n - rr) + 8j, scale, bias
+    // G heads x 8 variants x 10 words: s8 hi / lo terms behind sign bits (n + 4 rr) + 8j, scale, bias.
+    // The decode kernel's operand byte for such a bit is 2^n (the bit is masked in place, not moved),
+    // so the term stored here is x / 2^n, rounded: at most three of the sixteen bits are given up.
     for (int w = tid; w < G * 8 * 10; w += blockDim.x) {
         const int variant = w / 10, k = w % 10;
         const int hcol = variant >> 3, part = (variant >> 2) & 1, t = variant & 3;
@@ -276,7 +278,7 @@ template <typename T> __device__ __forceinline__ void tq_qprep_block(const TqQpr
             const int n = k >> 1, rr = k & 1;
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
-                const int x16 = s_x[hcol][32 * t + (7 - 2 * n - rr) + 8 * jj];
+                const int x16 = (s_x[hcol][32 * t + (n + 4 * rr) + 8 * jj] + ((1 << n) >> 1)) >> n;
                 const int hi8 = (x16 + 128) >> 8;
                 const int lo8 = x16 - (hi8 << 8);
                 word |= (uint32_t)((part ? lo8 : hi8) & 0xff) << (8 * jj);

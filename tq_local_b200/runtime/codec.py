@@ -124,6 +124,27 @@ class Codec:
         ffi.check(ffi.lib().tq_device_status(self.handle, C.byref(v)), "tq_device_status")
         return v.value
 
+    _STATUS_TEXT = {
+        1: "a decode kernel's wait for its bulk copies ran out",
+        2: "a decode kernel's shared-memory layout did not fit and it did not run",
+        3: "the encoder's wait ran out",
+        4: "an append addressed a token past the cache's capacity and was dropped",
+        5: "the wait for a peer's attention outputs ran out (tq_gather_wait)",
+    }
+
+    def raise_on_device_status(self, where: str) -> None:
+        """Raise :class:`TQError` when a kernel of this context has reported a problem.  The
+        bounded waits only set the status word; results computed after that are not to be
+        trusted, so the generation loops call this wherever they synchronise anyway."""
+        status = self.device_status()
+        if status:
+            raise ffi.TQError(f"{where}: device status {status} ({self._STATUS_TEXT.get(status, 'unknown')}); "
+                              "the outputs of this context are not valid")
+
+    def set_wait_limit_ms(self, limit_ms: int) -> None:
+        """How long ``tq_gather_wait`` polls for its peers before giving up (default 2000 ms)."""
+        ffi.check(ffi.lib().tq_set_wait_limit_ms(self.handle, int(limit_ms)), "tq_set_wait_limit_ms")
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             ffi.lib().tq_ctx_destroy(self.handle)

@@ -95,6 +95,39 @@ def _prefill(model, inputs, cache=None):
         return model(**inputs, use_cache=True, **extra)
 
 
+def raise_on_device_status(layers, where: str) -> None:
+    """The kernels' bounded waits only set a status word when they give up (a peer that never
+    raised its flag, a bulk copy that never landed); what was computed after that is not valid.
+    Called wherever the generation loops synchronise anyway: reads the word of every codec the
+    layers use, agrees on it across the ranks of a sharded run (so that all of them raise, and
+    none is left waiting in a collective), and raises ``TQError`` if any kernel gave up."""
+    import torch
+
+    from tq_local_b200.runtime.ffi import TQError
+
+    codecs, shard = {}, None
+    for layer in layers:
+        codec = getattr(layer, "codec", None)
+        if codec is not None and getattr(codec, "handle", None):
+            codecs[id(codec)] = codec
+            shard = shard or getattr(layer, "shard", None)
+    status = max((c.device_status() for c in codecs.values()), default=0)
+    if shard is not None and shard.world_size > 1:
+        import torch.distributed as dist
+
+        device = next(iter(codecs.values())).device
+        if dist.get_backend(shard.group) == "gloo":
+            device = torch.device("cpu")
+        word = torch.tensor([status], dtype=torch.int32, device=device)
+        dist.all_reduce(word, op=dist.ReduceOp.MAX, group=shard.group)
+        status = int(word.item())
+    if status:
+        from tq_local_b200.runtime.codec import Codec
+
+        raise TQError(f"{where}: device status {status} ({Codec._STATUS_TEXT.get(status, 'unknown')}); "
+                      "the generated tokens are not valid")
+
+
 def _static_decode_eligible(model, packed_cache, mask) -> bool:
     """The replayable (CUDA-graph) decode loop needs every layer packed with quantised appends,
     a tensor-core shape, one GPU, and no padding in the prompt."""
@@ -188,12 +221,14 @@ class RecordedDecoder:
 
         if self.layers is not None:
             torch.cuda.synchronize()
-            for layer in self.layers:
+            layers = self.layers
+            for layer in layers:
                 layer.end_static_decode(self.length0 + self.done)
             self.layers = None
             if self.gather is not None:
                 self.gather.close()
                 self.gather = None
+            raise_on_device_status(layers, "RecordedDecoder.close")
 
     def __enter__(self):
         return self
@@ -213,6 +248,7 @@ def _graphed_greedy_steps(model, cache, first_token, n_steps, eos_tensor):
                 so_far = torch.cat((first_token, dec.tokens), dim=-1)
                 if bool(torch.isin(so_far, eos_tensor).any(dim=-1).all()):
                     break
+                raise_on_device_status(cache.layers, "recorded decode")  # (the EOS test synchronised already)
             dec.step()
         torch.cuda.synchronize()
         return dec.tokens.clone()
@@ -328,6 +364,9 @@ def greedy_decode_with_prefill_cache(
                 cache = out.past_key_values
                 next_token = torch.argmax(out.logits[:, -1, :], dim=-1, keepdim=True)
                 generated.append(next_token)
+            if packed_cache is not None and torch.cuda.is_available():
+                torch.cuda.synchronize()
+                raise_on_device_status(packed_cache.layers, "greedy decode")
         finally:
             if packed_cache is not None:
                 from tq_local_b200.adapters.transformers import disable_turboquant_attention

@@ -214,6 +214,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     const int G = a.G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    // the centres the tables are built from: requested first, ahead of the bulk copies below,
+    // so that these few bytes do not queue behind the ring's first fill
+    const float ck = a.centers_k[lane & 15], cv = a.centers_v[lane & 15];
 
     int N = a.N, n_pad = a.n_pad, chunk = a.chunk, stable_len = a.stable_len;
     if (a.len_ptr) {
@@ -235,17 +238,69 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     };
     const uint32_t full_u32 = bars_addr + gq * kStages * 8;
     const uint32_t empty_u32 = bars_addr + (kSlots + gq * kStages) * 8;
-    if (wq == 0 && lane == 0) {
-        for (int st = 0; st < kStages; ++st) mbar_init(full_u32 + st * 8, 1), mbar_init(empty_u32 + st * 8, kGroupWarps);
+    if (wq < kStages && lane == 0) {  // warp st of the group sets slot st up (and requests its first fill below)
+        mbar_init(full_u32 + wq * 8, 1), mbar_init(empty_u32 + wq * 8, kGroupWarps);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     uint32_t ring_pos = 0;  // slots this group has consumed since the kernel began
 
+    // ---- a segment = the part of one (batch, KV head) row inside this CTA's piece
+    constexpr int kCtaStep = kWarps * kStageTok;
+    struct Seg {
+        int bh, seg_len, t_end, grp_first, n_iter;
+        int64_t row0;
+    };
+    auto seg_at = [&](int64_t flat) {
+        Seg sg;
+        // (the flattened space nearly always fits 32 bits, whose division is several times cheaper)
+        sg.bh = flat_end <= 0xffffffffll ? (int)((uint32_t)flat / (uint32_t)n_pad) : (int)(flat / n_pad);
+        const int seg_lo = (int)(flat - (int64_t)sg.bh * n_pad);
+        sg.seg_len = (int)min((int64_t)(n_pad - seg_lo), flat_end - flat);
+        sg.row0 = (int64_t)(sg.bh / a.Hkv) * a.cache_sb + (int64_t)(sg.bh % a.Hkv) * a.cache_sh;
+        sg.t_end = min(N, seg_lo + sg.seg_len);
+        sg.grp_first = seg_lo + gq * kGroupTok;
+        sg.n_iter = sg.grp_first < sg.t_end ? (sg.t_end - sg.grp_first + kCtaStep - 1) / kCtaStep : 0;
+        return sg;
+    };
+    // one lane of the group: fill the ring slot of the segment's local iteration `it`
+    auto issue = [&](const Seg &sg, int it) {
+        const int base = sg.grp_first + it * kCtaStep;
+        int n = min(kGroupTok, sg.t_end - base);
+        n = (n + 7) & ~7;  // whole 16-byte pieces of the norm streams; rows stay inside the row's stride
+        const int st = (ring_pos + it) % kStages;
+        const uint32_t dst = slot_u32(st), bar = full_u32 + st * 8;
+        const int64_t r = sg.row0 + base;
+        const uint32_t total = n * (16 * KB + 16 * VB + 4 + (QJL ? 18 : 0));
+        mbar_expect_tx(bar, total);
+        tma_load_1d(dst + L::kK, a.k_codes + r * (16 * KB), n * 16 * KB, bar);
+        tma_load_1d(dst + L::kV, a.v_codes + r * (16 * VB), n * 16 * VB, bar);
+        tma_load_1d(dst + L::kKN, a.k_norms + r, n * 2, bar);
+        tma_load_1d(dst + L::kVN, a.v_norms + r, n * 2, bar);
+        if (QJL) {
+            tma_load_1d(dst + L::kS, a.k_signs + r * 16, n * 16, bar);
+            tma_load_1d(dst + L::kRN, a.k_rnorms + r, n * 2, bar);
+        }
+    };
+    // The kernel is launched as a programmatic dependent of the query-preparation kernel, which
+    // may also be appending this step's token: the first segment's ring slots that hold only
+    // older tokens are requested right here, before the tables are built and before the
+    // dependency wait; the others (`deferred`) after the wait.
+    // (Slot `it` is requested by warp `it` of the group, so the requests of a group run side by
+    // side; bit `it` of `deferred` is only ever set in that warp's lane 0.)
+    uint32_t deferred = 0;
+    static_assert(kStages <= kGroupWarps, "one warp per first slot");
+    if (wq < kStages && lane == 0 && flat_begin < flat_end) {
+        const Seg sg = seg_at(flat_begin);
+        if (wq < sg.n_iter) {
+            if (sg.grp_first + wq * kCtaStep + kGroupTok > stable_len) deferred = 1u << wq;
+            else issue(sg, wq);
+        }
+    }
+
     // ---- per-lane replicated f16x2 centre-pair tables (keys in the low half of each slot);
     // a warp fills one slot at a time, lane l writing words l and 32+l (no bank conflicts)
     {
-        const float ck = a.centers_k[lane & 15], cv = a.centers_v[lane & 15];
         constexpr int mk = (1 << KB) - 1, mv = (1 << VB) - 1;
         for (int e = warp; e < kEntries; e += kWarps) {
             uint32_t *slot = table + e * kSlotWords;
@@ -268,62 +323,27 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
 
     // ---- one segment per row this CTA touches
     for (int64_t flat = flat_begin; flat < flat_end;) {
-    const int bh = (int)(flat / n_pad);
-    const int seg_lo = (int)(flat - (int64_t)bh * n_pad);
-    const int seg_len = (int)min((int64_t)(n_pad - seg_lo), flat_end - flat);
-    flat += seg_len;
+    const Seg sg = seg_at(flat);
+    flat += sg.seg_len;
+    const int bh = sg.bh;
     const int split = blockIdx.x - (int)(((int64_t)bh * n_pad) / chunk);  // partial slot inside the row
-    const int b = bh / a.Hkv, h = bh % a.Hkv;
-    const int64_t q_row0 = ((int64_t)b * a.Hkv + h) * G;
-    const int64_t row0 = (int64_t)b * a.cache_sb + (int64_t)h * a.cache_sh;
-    const int t_begin = seg_lo;
-    const int t_end = min(N, seg_lo + seg_len);
-    const int grp_first = t_begin + gq * kGroupTok;
-    const int my_first = grp_first + wq * kStageTok;
-    constexpr int kCtaStep = kWarps * kStageTok;
-    const int n_iter = grp_first < t_end ? (t_end - grp_first + kCtaStep - 1) / kCtaStep : 0;
-
-    auto issue = [&](int it) {  // one lane of the group: fill the ring slot of local iteration `it`
-        const int base = grp_first + it * kCtaStep;
-        int n = min(kGroupTok, t_end - base);
-        n = (n + 7) & ~7;  // whole 16-byte pieces of the norm streams; rows stay inside the row's stride
-        const int st = (ring_pos + it) % kStages;
-        const uint32_t dst = slot_u32(st), bar = full_u32 + st * 8;
-        const int64_t r = row0 + base;
-        const uint32_t total = n * (16 * KB + 16 * VB + 4 + (QJL ? 18 : 0));
-        mbar_expect_tx(bar, total);
-        tma_load_1d(dst + L::kK, a.k_codes + r * (16 * KB), n * 16 * KB, bar);
-        tma_load_1d(dst + L::kV, a.v_codes + r * (16 * VB), n * 16 * VB, bar);
-        tma_load_1d(dst + L::kKN, a.k_norms + r, n * 2, bar);
-        tma_load_1d(dst + L::kVN, a.v_norms + r, n * 2, bar);
-        if (QJL) {
-            tma_load_1d(dst + L::kS, a.k_signs + r * 16, n * 16, bar);
-            tma_load_1d(dst + L::kRN, a.k_rnorms + r, n * 2, bar);
-        }
-    };
-    // The kernel is launched as a programmatic dependent of the query-preparation kernel, which
-    // may also be appending this step's token: ring stages that hold only older tokens are
-    // requested before the dependency wait, everything else after it.
-    // The first slots of a segment are requested by warp 0 of the group (the __syncthreads that
-    // ended the previous segment guarantees that the whole group is done with them).
+    const int64_t q_row0 = (int64_t)bh * G;
+    const int t_end = sg.t_end;
+    const int my_first = sg.grp_first + wq * kStageTok;
+    const int n_iter = sg.n_iter;
     const int n_first = min(n_iter, kStages);
-    uint32_t deferred = 0;
-    if (wq == 0 && lane == 0) {
-        // the ring area was last touched through ordinary loads/stores (previous segment's merge)
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        for (int it = 0; it < n_first; ++it) {
-            if (first_segment && grp_first + it * kCtaStep + kGroupTok > stable_len)
-                deferred |= 1u << it;
-            else
-                issue(it);
-        }
-    }
     if (first_segment) {
         tq_grid_dependency_wait();
         TQ_STAMP(2);
         for (int it = 0; it < n_first; ++it)
-            if (deferred >> it & 1) issue(it);
+            if (deferred >> it & 1) issue(sg, it);  // (only the issuing lane has bits set)
         first_segment = false;
+    } else if (wq == 0 && lane == 0) {
+        // The first slots of a later segment are requested by warp 0 of the group (the
+        // __syncthreads that ended the previous segment guarantees that the whole group is done
+        // with them); the ring area was last touched through ordinary loads/stores (the merge).
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        for (int it = 0; it < n_first; ++it) issue(sg, it);
     }
 
     // ---- B fragments: column g = (head g/2, part g%2), or head g in the wide variant
@@ -534,7 +554,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         if (lane == 0) {
             mbar_arrive(empty_u32 + st * 8);
             if (it + kStages < n_iter && wq == (it % kGroupWarps)) {
-                if (mbar_wait(empty_u32 + st * 8, use_parity)) issue(it + kStages);
+                if (mbar_wait(empty_u32 + st * 8, use_parity)) issue(sg, it + kStages);
                 else timed_out = true;
             }
         }
@@ -556,14 +576,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
 #pragma unroll
         for (int sft = 4; sft <= 16; sft <<= 1) l_all += __shfl_xor_sync(0xffffffffu, l_all, sft);
         if (g == 0) s_m[warp * 4 + t] = m_run[hl], s_l[warp * 4 + t] = l_all;
+        // A warp's 512 accumulators are laid out [mt][lane][2], so the 8-byte stores of a warp
+        // and the reads of 32 consecutive elements below both touch every bank once.
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            float *r = s_acc + (warp * 4 + t) * TQ_D + 16 * g + 2 * mt;
-            r[0] = o[mt][hl], r[1] = o[mt][2 + hl];
-        }
+        for (int mt = 0; mt < 8; ++mt)
+            *reinterpret_cast<float2 *>(s_acc + warp * 4 * TQ_D + mt * 64 + lane * 2) = make_float2(o[mt][hl], o[mt][2 + hl]);
         __syncthreads();
         for (int idx = threadIdx.x; idx < 4 * TQ_D; idx += blockDim.x) {
-            const int tt = idx / TQ_D, d = idx % TQ_D;
+            // element idx of that layout: accumulator tile mt of lane (gg, tt), column pair member j
+            const int mt = idx >> 6, gg = (idx & 63) >> 3, tt = (idx >> 1) & 3, j = idx & 1;
+            const int d = 16 * gg + 2 * mt + j;
             const int hh = WIDE ? 2 * tt + hl : tt;
             if (hh >= G) continue;
             float M = -INFINITY;
@@ -575,7 +597,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                 const float mw = s_m[w * 4 + tt];
                 const float sc = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
                 Lsum += s_l[w * 4 + tt] * sc;
-                A += s_acc[(w * 4 + tt) * TQ_D + d] * sc;
+                A += s_acc[w * 4 * TQ_D + idx] * sc;
             }
             const int64_t prow = (q_row0 + hh) * a.n_splits + split;
             a.part_acc[prow * TQ_D + d] = A;

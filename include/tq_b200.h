@@ -141,6 +141,15 @@ int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_he
                        const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
                        void *workspace, size_t workspace_bytes, void *out, tq_stream stream);
 
+/* tq_decode_attn for fp16 / bf16 queries without a dense tail, with the result written
+ * UNROUNDED as float32 [batch, q_heads, 128]: the same kernels, only the final cast to the query
+ * dtype is left out.  For callers that go on in fp32 and for measuring the kernels' own error
+ * apart from the rounding of the output (no reference counterpart: the reference's fused path
+ * always casts to the query dtype, src/turboquant/runtime/triton_kernels.py:368). */
+int32_t tq_decode_attn_f32out(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                              const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits,
+                              void *workspace, size_t workspace_bytes, float *out, tq_stream stream);
+
 /* One whole decode step for callers whose tensors live in HOST memory (pinned for the copies
  * to be asynchronous): copy the query and the new token's key / value to the device, append
  * the token at position `pos` of every cache row, attend over pos + 1 tokens, copy the

@@ -9,17 +9,33 @@ import pytest
 import torch
 
 from conftest import LAYER_CASES, load_layer_case
-from helpers import (assert_codes_match, fp16_ulp_diff, load_into_store, make_codec, oracle_params, rel_inf,
+from helpers import (assert_codes_match, check_packed, fp16_ulp_diff, load_into_store, make_codec, oracle_params, rel_inf,
                      store_to_layer)
 from oracle import tq_oracle as O
 
 pytestmark = pytest.mark.gpu
 
-# Output tolerances, relative to the largest reference magnitude (inf-norm): 1e-5 for fp32,
-# 2e-3 for 16-bit caches.  The kernel writes its result in the query dtype, so when it is
-# compared with an fp32 reference the half-ulp of that final rounding (2^-9 for bf16,
-# 2^-12 for fp16, relative to the element) is added on top.
+# Output tolerances, relative to the largest reference magnitude (inf-norm): 1e-5 for fp32 and
+# 2e-3 for 16-bit caches.  For 16-bit caches the bound is asserted, with nothing added, on the
+# kernels' UNROUNDED result (tq_decode_attn_f32out: same kernels, final cast left out), and the
+# usual output must be exactly that result rounded to the query dtype.  Where the ROUNDED output
+# is compared with an fp32 reference, the half-ulp of that last rounding (2^-9 for bf16, 2^-12
+# for fp16) comes on top (TOL).
+KERNEL_TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-3, torch.float16: 2e-3}
 TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-3 + 2.0 ** -9, torch.float16: 2e-3 + 2.0 ** -12}
+WORST = {}  # (variant, dtype) -> worst unrounded error seen in this run (printed by the last test)
+
+
+def check_unrounded(store, q_dev, got, fused32, groups, **kw):
+    """The kernels' own error, apart from the rounding of the output: <= 2e-3, nothing added."""
+    if q_dev.dtype == torch.float32:
+        return
+    raw = store.decode_attn_f32(q_dev, **kw)
+    err = rel_inf(raw, fused32)
+    key = ("wide" if groups > 4 else "narrow", str(q_dev.dtype).replace("torch.", ""))
+    WORST[key] = max(WORST.get(key, 0.0), err)
+    assert err <= KERNEL_TOL[q_dev.dtype], (key, err)
+    assert torch.equal(raw.to(q_dev.dtype), got), "the usual output is the unrounded one, rounded once"
 
 
 def _golden_layer(g, p, tag) -> O.PackedLayer:
@@ -28,58 +44,6 @@ def _golden_layer(g, p, tag) -> O.PackedLayer:
                          g.t(f"{tag}_v_norms", f16),
                          g.t(f"{tag}_k_signs") if p.use_qjl else None,
                          g.t(f"{tag}_k_rnorms", f16) if p.use_qjl else None)
-
-
-def _check_packed(store, ref: O.PackedLayer, k, v, p, what):
-    n = ref.seq_len
-    assert store.length == n
-    k, v = k[:, :, :n], v[:, :, :n]
-    exact_k = assert_codes_match(store.k_codes[:, :, :n], ref.k_codes, k, p.rot_k, p.bnd_k, p.key_bits, what + " keys")
-    assert_codes_match(store.v_codes[:, :, :n], ref.v_codes, v, p.rot_v, p.bnd_v, p.bits, what + " values")
-    assert fp16_ulp_diff(store.k_norms[:, :, :n].cpu(), ref.k_norms) <= 1
-    assert fp16_ulp_diff(store.v_norms[:, :, :n].cpu(), ref.v_norms) <= 1
-    if p.use_qjl:
-        # Signs and residual norms are compared on vectors whose codes match exactly.  The residual
-        # is taken against the reconstruction ROUNDED to the cache dtype (packed_qmse_cache.py:
-        # 295-297), so two things decide how far fp32 summation order can move it:
-        #  * an element of the fp32 reconstruction that sits on a rounding edge of that dtype
-        #    becomes the other neighbour, a jump of one ulp of that element ("rounding edge", the
-        #    same rule as "within 1e-6 of a decision boundary" for the codes);
-        #  * a vector whose fp16 norm landed on the other side of an fp16 rounding edge (allowed
-        #    above) is reconstructed 2^-11 larger or smaller, which re-rounds many elements.
-        # Sign flips are accepted where the reference's projected residual is within 5e-3 of zero
-        # plus what the vector's rounding edges can move it; residual norms may differ by one fp16
-        # ulp plus the same reach.  Norm-edge vectors only get loose bounds.
-        *_, proj = O.encode_keys_prod(k.contiguous(), p)
-        proj = proj.reshape(-1, 128).abs()
-        got = torch.from_numpy(O.unpack_codes(store.k_signs[:, :, :n].reshape(-1, 16).cpu().numpy(), 1, 128))
-        want = torch.from_numpy(O.unpack_codes(ref.k_signs.reshape(-1, 16).numpy(), 1, 128))
-        same_norm = (store.k_norms[:, :, :n].cpu().reshape(-1).view(torch.int16) ==
-                     ref.k_norms.reshape(-1).view(torch.int16))
-        rnorm = ref.k_rnorms.reshape(-1).float()
-        if ref.dtype == torch.float32:
-            edge_ulp = torch.zeros_like(proj)
-        else:
-            idx = torch.from_numpy(O.unpack_codes(ref.k_codes.reshape(-1, ref.k_codes.shape[-1]).numpy(),
-                                                  p.key_bits, 128))
-            norm = ref.k_norms.reshape(-1).float().unsqueeze(1)
-            rec = (p.cen_k[idx] @ p.rot_k) * norm
-            q = rec.to(ref.dtype).float()
-            ulp = (torch.nextafter(q.to(ref.dtype), torch.tensor(float("inf"), dtype=ref.dtype)).float() - q).abs()
-            on_edge = ((rec - q).abs() - ulp / 2).abs() < 1e-6 * norm  # fp32 summation error ~ 1e-7 |k|
-            edge_ulp = on_edge * ulp
-        reach = (edge_ulp @ p.qjl.abs().T) / rnorm.unsqueeze(1)  # how far each projection can move
-        flips = (got != want) & exact_k.unsqueeze(1)
-        judged = flips & same_norm.unsqueeze(1)
-        assert (proj[judged] <= 5e-3 + 1.05 * reach[judged]).all(), what + ": QJL sign flips away from zero"
-        assert (proj[flips] < 0.1).all() and flips.float().mean() < 1e-3
-        rn_got = store.k_rnorms[:, :, :n].cpu().reshape(-1).float()
-        ok = exact_k & same_norm
-        fp16_ulp = torch.maximum(rnorm, torch.tensor(2.0 ** -14)).log2().floor().exp2() * 2.0 ** -10
-        assert ((rn_got - rnorm).abs()[ok] <= (1.01 * fp16_ulp + 1.05 * edge_ulp.sum(dim=1))[ok]).all()
-        edge = exact_k & ~same_norm
-        assert ((rn_got - rnorm).abs()[edge] <= 1e-2 * rnorm[edge]).all()
-        assert (~same_norm).float().mean() < 2e-3
 
 
 @pytest.mark.parametrize("case", LAYER_CASES)
@@ -95,11 +59,11 @@ def test_pack_and_append_match_reference(setup_golden, case):
     kd, vd = k.cuda(), v.cuda()
     store = PackedStore(codec, g.i("B"), g.i("Hkv"), capacity=S)  # forces a capacity growth on append
     store.pack(kd[:, :, :S], vd[:, :, :S])
-    _check_packed(store, _golden_layer(g, p, "prefill"), k, v, p, case + " prefill")
+    check_packed(store, _golden_layer(g, p, "prefill"), k, v, p, case + " prefill")
     assert store.storage_bytes() == g.i("prefill_storage_bytes")
     for t in range(n_app):
         store.pack(kd[:, :, S + t:S + t + 1], vd[:, :, S + t:S + t + 1])
-    _check_packed(store, _golden_layer(g, p, "appended"), k, v, p, case + " appended")
+    check_packed(store, _golden_layer(g, p, "appended"), k, v, p, case + " appended")
     assert store.storage_bytes() == g.i("appended_storage_bytes")
 
 
@@ -151,6 +115,7 @@ def test_decode_attention_matches_reference(setup_golden, case, tag):
         assert got.dtype == q.dtype and tuple(got.shape) == (g.i("B"), g.i("Hq"), 1, 128)
         # (1) against the reference's fused identity, at the headline tolerance
         assert rel_inf(got, fused32) <= TOL[g.dtype]
+        check_unrounded(store, q.cuda(), got, fused32, groups, splits=splits)
         # (2) against dequantise-then-attend: exact-to-tolerance for fp32 caches; for 16-bit caches
         # the reference rounds the dequantised K/V to the cache dtype, which no rotated-space
         # kernel (its own Triton one included) reproduces, so allow that measured gap on top.
@@ -224,13 +189,14 @@ def test_seeded_layer_against_oracle(setup_golden, bits, qjl, dtype, B, Hq, Hkv,
     assert Hkv == 1 or not kd.is_contiguous()
     store.pack(kd, vd)
     ref = O.pack_layer(k, v, p)
-    _check_packed(store, ref, k, v, p, f"seeded b{bits} qjl{qjl}")
+    check_packed(store, ref, k, v, p, f"seeded b{bits} qjl{qjl}")
     mine = store_to_layer(store, p, dtype)  # attention parity is judged on the GPU's own codes
     groups = Hq // Hkv
     fused32 = O.attend_rotated_space(q, mine, groups)
     want32 = O.attend_dequant(q, mine, groups)
     got = store.decode_attn(q.cuda())
     assert rel_inf(got, fused32) <= TOL[dtype]
+    check_unrounded(store, q.cuda(), got, fused32, groups)
     gap = rel_inf(fused32, want32) if dtype != torch.float32 else 0.0
     assert rel_inf(got, want32) <= TOL[dtype] + gap
     # split count must not change the answer beyond rounding
@@ -274,7 +240,7 @@ def test_zero_vectors_and_append_equivalence(setup_golden):
         assert torch.equal(x[:, :, :20], y[:, :, :20])
     assert float(a.k_norms[0, 1, 5]) == 1.0 and float(a.v_norms[1, 0, 7]) == 1.0
     ref = O.pack_layer(k, v, p)
-    _check_packed(a, ref, k, v, p, "zero-vector case")
+    check_packed(a, ref, k, v, p, "zero-vector case")
 
 
 def test_argument_errors(setup_golden):
@@ -420,3 +386,12 @@ def test_decode_step_dev_drops_appends_past_capacity_and_reports_it(setup_golden
         assert torch.equal(a, b)  # nothing was written
     assert torch.isfinite(out.float()).all()
     # the status word is sticky by design; a fresh context starts clean
+
+
+def test_zz_report_worst_unrounded_error():
+    """Runs last in this file: the worst error of the unrounded outputs seen above, per kernel
+    variant (G <= 4 "narrow", G > 4 "wide") and dtype, all of which passed the 2e-3 bound."""
+    assert WORST, "no 16-bit case ran"
+    for key in sorted(WORST):
+        print(f"worst unrounded attention error {key}: {WORST[key]:.3e}")
+        assert WORST[key] <= 2e-3

@@ -127,6 +127,7 @@ struct TqStepExtras {
     const struct TqPackArgs *append;  // encode and append the step's new token in the query-preparation launch
     const int *len_ptr;               // the sequence length lives in device memory
     const tq_gather_desc *gather;     // KV-head shard: write the outputs into every rank's gathered buffer
+    float *out_f32;                   // write the result unrounded (fp32) here instead of `out`
 };
 int tq_mma4_tokens_per_cta_step();
 int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,

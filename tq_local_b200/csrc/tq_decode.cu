@@ -383,6 +383,8 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
         const int64_t row = R * a.G + h0 + g;  // = batch index * local query heads + local head
         if (a.gather_world > 0) {
             reinterpret_cast<T *>(&s_o[0][0])[g * TQ_D + e] = res;  // staged: the peers get 16-byte stores below
+        } else if (a.out_f32) {
+            a.out_f32[row * TQ_D + e] = v / fmaxf(s_L[g], 1e-8f);
         } else {
             ((T *)a.out)[row * TQ_D + e] = res;
         }
@@ -629,7 +631,7 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
     c.len_ptr = nullptr, c.len_add = 0, c.capacity = 0, c.plan_rows = 0, c.plan_ctas = 0, c.plan_step = 0;
     c.gather_world = 0;
     c.rot_v = ctx->rot_v;
-    c.q = q, c.out = out;
+    c.q = q, c.out = out, c.out_f32 = nullptr;
     c.n_tail = n_tail;
     c.tail_k = n_tail ? tail_k->data : nullptr;
     c.tail_v = n_tail ? tail_v->data : nullptr;

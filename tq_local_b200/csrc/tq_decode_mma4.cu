@@ -713,7 +713,8 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
         }
     }
     c.rot_v = ctx->rot_v;
-    c.q = q, c.out = out;
+    c.q = q, c.out = out, c.out_f32 = extras ? extras->out_f32 : nullptr;
+    if (c.out_f32 && (gather || n_tail)) return TQ_ERR_UNSUPPORTED;
     c.n_tail = n_tail;
     c.tail_k = n_tail ? tail_k->data : nullptr;
     c.tail_v = n_tail ? tail_v->data : nullptr;

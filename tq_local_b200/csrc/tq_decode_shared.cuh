@@ -26,6 +26,7 @@ struct CombineArgs {
     const float *rot_v;  // R_v[d][e]
     const void *q;       // original-dtype query, for the dense tail
     void *out;
+    float *out_f32;      // when set (grouped combine only), the result goes here as fp32 and `out` is not written
     int n_tail;
     const void *tail_k, *tail_v;
     int64_t tk_sb, tk_sh, tk_st, tv_sb, tv_sh, tv_st;

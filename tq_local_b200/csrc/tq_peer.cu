@@ -67,7 +67,7 @@ extern "C" int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_d
     if (gather->q_heads_total != q_heads * gather->world) return TQ_ERR_ARG;
     if (((uintptr_t)q | (uintptr_t)workspace) & 15) return TQ_ERR_ARG;
     if (workspace_bytes < tq_decode_workspace_bytes(cache->batch, q_heads, n_splits)) return TQ_ERR_WORKSPACE;
-    const TqStepExtras extras = {nullptr, nullptr, gather};
+    const TqStepExtras extras = {nullptr, nullptr, gather, nullptr};
     return tq_launch_decode_mma4(ctx, q, q_dtype, q_heads, cache, seq_len, nullptr, nullptr, 0, n_splits, workspace,
                                  /*out=*/nullptr, &extras, (cudaStream_t)stream);
 }

@@ -148,6 +148,25 @@ class PackedStore:
                       "tq_decode_attn")
         return out
 
+    def decode_attn_f32(self, q: torch.Tensor, *, seq_len: int | None = None, splits: int | None = None) -> torch.Tensor:
+        """``decode_attn`` for a 16-bit query with the result left unrounded: float32
+        [B, Hq, 1, 128] (``tq_decode_attn_f32out``)."""
+        b, hq = int(q.shape[0]), int(q.shape[1])
+        if q.shape[-1] != 128 or q.numel() != b * hq * 128 or b != self.batch:
+            raise ValueError(f"expected a single-token query [B={self.batch}, Hq, 1, 128], got {tuple(q.shape)}")
+        qc = q.reshape(b, hq, 128)
+        if not qc.is_contiguous():
+            qc = qc.contiguous()
+        n = self.length if seq_len is None else int(seq_len)
+        splits = self.suggest_splits(n) if splits is None else int(splits)
+        ws = self._get_workspace(hq, splits)
+        out = torch.empty(b, hq, 1, 128, dtype=torch.float32, device=q.device)
+        with torch.cuda.device(self.codec.device):
+            ffi.check(ffi.lib().tq_decode_attn_f32out(self.codec.handle, qc.data_ptr(), tq_dtype(q.dtype), hq,
+                                                      C.byref(self._desc), n, splits, ws.data_ptr(), ws.numel(),
+                                                      out.data_ptr(), self._stream_ptr()), "tq_decode_attn_f32out")
+        return out
+
     def decode_attn_gather(self, q: torch.Tensor, gather, *, seq_len: int | None = None,
                            splits: int | None = None) -> torch.Tensor:
         """``decode_attn`` for a KV-head shard with the exchange fused in: ``q`` holds this rank's

@@ -204,3 +204,88 @@ def test_streaming_prefill_packs_layer_by_layer_with_the_same_result(setup_golde
     assert [l.storage_bytes() for l in cache.layers] == [l.storage_bytes() for l in want.layers]
     assert torch.equal(cache.layers[1].store.k_codes[:, :, :64], want.layers[1].store.k_codes[:, :, :64])
     assert cache.layers[1].get_seq_length() == 64
+
+
+def test_prompt_pass_in_row_blocks_equals_the_single_pass(capsys):
+    """``prefill_block_tokens``: a streaming prompt pass that takes the batch two sequences at a
+    time must leave exactly the packed cache, the norm-guard decisions and the tokens of the pass
+    that takes the whole batch at once."""
+    import turboquant
+
+    model = _tiny_model(torch.bfloat16)
+    ids = torch.randint(0, 512, (5, 64), device="cuda", generator=torch.Generator("cuda").manual_seed(5))
+    captured, outs = {}, {}
+    for name, block in (("single", 1 << 30), ("blocks", 128)):  # 128 tokens = two 64-token sequences per block
+        turboquant.activate(model, StubTokenizer(), quiet=True, bits=4, verify=False, cuda_graph=False,
+                            prefill_block_tokens=block)
+        outs[name] = model.generate(ids, max_new_tokens=6)
+        captured[name] = turboquant.last_telemetry(model)
+        turboquant.deactivate(model, quiet=True)
+    assert torch.equal(outs["single"], outs["blocks"])
+    for key in ("dense_kv_bytes", "packed_actual_bytes", "prompt_tokens", "completion_tokens"):
+        assert captured["single"][key] == captured["blocks"][key], key
+
+
+def test_row_block_prefill_fills_the_same_cache_and_keeps_norm_guard_layers_dense():
+    """Layer level: K/V handed over in row blocks give byte-identical packed streams (packed layer)
+    and the same dense tensors (norm-guarded layer) as one hand-over of the whole batch."""
+    from tq_local_b200.runtime.packed_qmse_cache import _auto_norm_threshold, build_streaming_prefill_cache
+
+    B, Hkv, S = 5, 2, 96
+    k_lo, v_lo, _ = O.synth_kvq(B, 4, Hkv, S, 128, seed=41, dtype=torch.bfloat16)
+    k_hi, v_hi, _ = O.synth_kvq(B, 4, Hkv, S, 128, seed=42, dtype=torch.bfloat16, norm_mode="asym")
+    thr = _auto_norm_threshold(4, 128)
+    kw = dict(bits=4, use_qjl_keys=True, quantize_decode=True, norm_guard=True, reserve_tokens=8)
+    whole = build_streaming_prefill_cache(2, **kw)
+    whole.layers[0].update(k_lo.cuda(), v_lo.cuda())
+    whole.layers[1].update(k_hi.cuda(), v_hi.cuda())
+    blocks = build_streaming_prefill_cache(2, **kw)
+    for b0 in range(0, B, 2):
+        for layer, (k, v) in zip(blocks.layers, ((k_lo, v_lo), (k_hi, v_hi))):
+            assert layer.get_seq_length() == 0  # every block's prompt starts at position 0
+            layer.begin_prefill_block(b0, B, thr)
+            layer.update(k[b0:b0 + 2].cuda(), v[b0:b0 + 2].cuda())
+    assert all(layer.finish_prefill(S, thr) for layer in blocks.layers)
+    a, b = whole.layers[0], blocks.layers[0]
+    assert not a._force_dense and not b._force_dense and b.get_seq_length() == S
+    for x, y in zip(a.store.streams(), b.store.streams()):
+        assert torch.equal(x[:, :, :S], y[:, :, :S])
+    a, b = whole.layers[1], blocks.layers[1]
+    assert a._force_dense and b._force_dense and b.get_seq_length() == S
+    assert torch.equal(a._dense_keys, b._dense_keys) and torch.equal(a._dense_values, b._dense_values)
+    assert a.storage_bytes() == b.storage_bytes()
+
+
+def test_long_prompt_batch_16_by_32768_through_activate_on_two_layers():
+    """The full-model workload's prompt shape (batch 16 x 32768 random token ids, Llama-3.1-8B layer
+    dimensions, vocabulary 128256) through ``activate()`` -> ``generate()`` on a two-layer model:
+    the prompt pass runs in row blocks, so neither [16, 32768, vocab] logits (134 GB) nor the
+    activations of the whole batch are ever held; then greedy tokens through the recorded step."""
+    import turboquant
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=2,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=131072,
+                      tie_word_embeddings=False)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device("cuda"):
+            model = LlamaForCausalLM(cfg).eval()
+    finally:
+        torch.set_default_dtype(old)
+    B, S, new = 16, 32768, 12
+    ids = torch.randint(0, 128256, (B, S), device="cuda", generator=torch.Generator("cuda").manual_seed(7))
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    turboquant.activate(model, StubTokenizer(), quiet=True, bits=4, use_qjl_keys=True, verify=False)
+    out = model.generate(ids, max_new_tokens=new)
+    tel = turboquant.last_telemetry(model)
+    turboquant.deactivate(model, quiet=True)
+    assert tuple(out.shape) == (B, S + new) and torch.equal(out[:, :S], ids)
+    assert tel["prompt_tokens"] == S and tel["packed_actual_bytes"] == 2 * 134 * B * 8 * S
+    # four sequences (131072 tokens) per block: activations of a block stay far below what the
+    # whole batch would need (the MLP intermediates alone would be 45 GB)
+    assert torch.cuda.max_memory_allocated() - base < 40e9

@@ -8,7 +8,7 @@ point.  Names, keyword arguments, defaults, the attributes stashed on the model
 (``_tq_state``, ``_tq_tokenizer``, ``_tq_last_output``) and the exceptions raised are the
 reference's.
 
-Host-side extensions: ``activate(..., verify=..., shard=..., cuda_graph=...)`` (skip the
+Host-side extensions: ``activate(..., verify=..., shard=..., cuda_graph=..., prefill_block_tokens=...)`` (skip the
 per-call reconstruction report; shard KV heads over a process group; record the decode step in a
 CUDA graph and replay it per token — on by default when every layer qualifies), and the patched
 ``generate`` returns every batch row (``[B, prompt + new]``) instead of row 0 only.
@@ -221,12 +221,13 @@ class _TurboQuantState:
     verify: bool = True
     shard: Any = None
     use_cuda_graph: bool | None = None
+    prefill_block_tokens: int | None = None
 
 
 def activate(model, tokenizer=None, *, bits: int = 4, rotation_seed: int = 0, num_outlier_channels: int = 0,
              outlier_extra_bits: int = 1, use_qjl_keys: bool = True, quantize_decode: bool = True,
              norm_guard: bool = True, quiet: bool = False, verify: bool = True, shard=None,
-             cuda_graph: bool | None = None) -> None:
+             cuda_graph: bool | None = None, prefill_block_tokens: int | None = None) -> None:
     """Make ``model.generate()`` decode greedily over a TurboQuant packed KV cache.
 
     ``bits`` 2-4; ``use_qjl_keys`` selects Q_prod keys (``bits-1`` Lloyd-Max bits + a 1-bit QJL
@@ -252,7 +253,7 @@ def activate(model, tokenizer=None, *, bits: int = 4, rotation_seed: int = 0, nu
                              outlier_extra_bits=outlier_extra_bits, use_qjl_keys=use_qjl_keys,
                              quantize_decode=quantize_decode, norm_guard=norm_guard,
                              original_generate=model.generate, verify=verify, shard=shard,
-                             use_cuda_graph=cuda_graph)
+                             use_cuda_graph=cuda_graph, prefill_block_tokens=prefill_block_tokens)
     model._tq_state = state
     model._tq_tokenizer = tokenizer
 
@@ -272,7 +273,8 @@ def activate(model, tokenizer=None, *, bits: int = 4, rotation_seed: int = 0, nu
             variant="qmse_packed", qmse_bits=tq.bits, rotation_seed=tq.rotation_seed,
             num_outlier_channels=tq.num_outlier_channels, outlier_extra_bits=tq.outlier_extra_bits,
             use_qjl_keys=tq.use_qjl_keys, quantize_decode=tq.quantize_decode, norm_guard=tq.norm_guard,
-            verify=tq.verify, shard=tq.shard, use_cuda_graph=tq.use_cuda_graph)
+            verify=tq.verify, shard=tq.shard, use_cuda_graph=tq.use_cuda_graph,
+            prefill_block_tokens=tq.prefill_block_tokens)
         model._tq_last_output = output
         return torch.cat([input_ids, output.completion_ids.to(input_ids.device)], dim=1)
 

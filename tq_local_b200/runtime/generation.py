@@ -28,6 +28,7 @@ from tq_local_b200.runtime.memory_accounting import (
     turboquant_mse_packed_bytes,
 )
 from tq_local_b200.runtime.packed_qmse_cache import (
+    _auto_norm_threshold,
     build_packed_mse_cache,
     build_streaming_prefill_cache,
     packed_cache_storage_breakdown,
@@ -37,6 +38,9 @@ from tq_local_b200.runtime.packed_qmse_cache import (
 )
 
 _EOS_POLL_STEPS = 8
+# A streaming prompt pass runs at most this many prompt tokens through the model at a time (whole
+# sequences: batch rows are taken in blocks), which bounds the activations of a long-prompt batch.
+PREFILL_BLOCK_TOKENS = 131072
 _GRAPH_WARMUP_STEPS = 2  # eager steps in static mode before the decode step is recorded
 
 
@@ -126,6 +130,36 @@ def raise_on_device_status(layers, where: str) -> None:
 
         raise TQError(f"{where}: device status {status} ({Codec._STATUS_TEXT.get(status, 'unknown')}); "
                       "the generated tokens are not valid")
+
+
+def _prefill_in_row_blocks(model, inputs, packed_cache, threshold: float, rows_per_block: int):
+    """The prompt pass of a streaming prefill, ``rows_per_block`` sequences at a time: every block
+    runs the whole model with its own dense attention (exactly what the reference's single prompt
+    pass computes for those rows, generation.py:91) while each layer packs the block's K/V into its
+    rows of the packed cache.  Neither the logits of the whole prompt ([B, S, vocab]) nor a dense
+    cache of the whole model nor the activations of the whole batch ever exist.  Returns the last
+    position's logits [B, vocab]."""
+    import sys
+
+    import torch
+
+    ids = inputs["input_ids"]
+    batch, n_tokens = int(ids.shape[0]), int(ids.shape[1])
+    last = []
+    for b0 in range(0, batch, rows_per_block):
+        block = {k: (v[b0:b0 + rows_per_block] if torch.is_tensor(v) and v.dim() >= 1 and v.shape[0] == batch else v)
+                 for k, v in inputs.items()}
+        for layer in packed_cache.layers:
+            layer.begin_prefill_block(b0, batch, threshold)
+        out = _prefill(model, block, packed_cache)
+        last.append(out.logits[:, -1, :].clone())
+        del out
+    agree = [layer.finish_prefill(n_tokens, threshold) for layer in packed_cache.layers]
+    if not all(agree):
+        odd = [i for i, ok in enumerate(agree) if not ok]
+        print(f"[TurboQuant] norm_guard: layers {odd} were decided on the first block of sequences; the mean key "
+              "norm of the whole batch falls on the other side of the threshold", file=sys.stderr)
+    return torch.cat(last, dim=0)
 
 
 def _static_decode_eligible(model, packed_cache, mask) -> bool:
@@ -271,6 +305,7 @@ def greedy_decode_with_prefill_cache(
     verify: bool = True,
     shard=None,
     use_cuda_graph: bool | None = None,
+    prefill_block_tokens: int | None = None,
 ) -> GenerationOutput:
     import torch
 
@@ -299,12 +334,23 @@ def greedy_decode_with_prefill_cache(
                 outlier_extra_bits=outlier_extra_bits, use_qjl_keys=use_qjl_keys, quantize_decode=quantize_decode,
                 norm_guard=norm_guard, reserve_tokens=max_new_tokens, shard=shard)
             quant_seconds += time.monotonic() - t0
-            outputs = _prefill(model, inputs, packed_cache)
+            ids = inputs["input_ids"]
+            block_tokens = PREFILL_BLOCK_TOKENS if prefill_block_tokens is None else int(prefill_block_tokens)
+            rows_per_block = max(1, block_tokens // max(int(ids.shape[1]), 1))
+            if rows_per_block < int(ids.shape[0]):
+                threshold = _auto_norm_threshold(qmse_bits, head_dim) if norm_guard else float("inf")
+                last_logits = _prefill_in_row_blocks(model, inputs, packed_cache, threshold, rows_per_block)
+                cache = packed_cache
+            else:
+                outputs = _prefill(model, inputs, packed_cache)
+                cache, last_logits = outputs.past_key_values, outputs.logits[:, -1, :]
+                del outputs
         else:
             outputs = _prefill(model, inputs)
-        cache = outputs.past_key_values
-        next_token = torch.argmax(outputs.logits[:, -1, :], dim=-1, keepdim=True)
-        del outputs
+            cache, last_logits = outputs.past_key_values, outputs.logits[:, -1, :]
+            del outputs
+        next_token = torch.argmax(last_logits, dim=-1, keepdim=True)
+        del last_logits
         estimate = actual = recon = None
         if streaming:
             report_streamed_norm_guard(packed_cache, qmse_bits, head_dim)

@@ -92,6 +92,15 @@ class _GrowingDense:
         self.length += n
         return self.view()
 
+    def write_rows(self, x: torch.Tensor, b0: int, total_batch: int, reserve: int = 0) -> None:
+        """Batch rows ``[b0, b0 + x.shape[0])`` of a buffer for ``total_batch`` rows, tokens
+        ``[0, x.shape[2])``; ``length`` is left for the caller to set once every row is in."""
+        n = int(x.shape[2])
+        if self.buf is None:
+            self.buf = torch.empty(total_batch, x.shape[1], max(n + reserve, 16), x.shape[3], dtype=x.dtype,
+                                   device=x.device)
+        self.buf[b0:b0 + x.shape[0], :, :n] = x
+
     def view(self) -> torch.Tensor | None:
         return None if self.buf is None else self.buf[:, :, :self.length]
 
@@ -138,6 +147,9 @@ class PackedMSELayer(CacheLayerMixin):
         self._kv_heads_total: int | None = None
         self._static_pos: torch.Tensor | None = None  # see begin_static_decode
         self._stream_threshold: float | None = None   # see build_streaming_prefill_cache
+        self._window: tuple[int, int] | None = None   # (first batch row, total batch) of a prompt pass run in row blocks
+        self._window_dense: bool | None = None        # the norm-guard decision of such a pass (taken on its first block)
+        self._window_norm = [0.0, 0]                  # running (sum of block means x rows, rows) of such a pass
         self._prefill_shape: tuple[int, ...] | None = None
         self._static_kv: tuple[torch.Tensor, torch.Tensor] | None = None
         self._static_gather = None
@@ -284,6 +296,9 @@ class PackedMSELayer(CacheLayerMixin):
             # dense under the norm guard) and hand the dense tensors back for the prompt's own
             # attention; nothing dense outlives the layer's forward pass.
             threshold, self._stream_threshold = self._stream_threshold, None
+            if self._window is not None:
+                self._update_prefill_block(key_states, value_states, threshold)
+                return key_states, value_states
             self._prefill_shape = tuple(key_states.shape)
             dense = threshold != float("inf") and float(key_norm_mean(key_states).item()) > threshold
             self.initialize_from_dense(key_states, value_states, force_dense=dense)
@@ -302,6 +317,55 @@ class PackedMSELayer(CacheLayerMixin):
             return key_states, value_states
         return (torch.cat((prev_k, self.shard.local_kv(key_states)), dim=-2),
                 torch.cat((prev_v, self.shard.local_kv(value_states)), dim=-2))
+
+    def _update_prefill_block(self, key_states, value_states, threshold: float) -> None:
+        """Streaming prefill of a prompt pass that runs the batch a few rows at a time: this is the
+        prompt's K/V of rows ``[b0, b0 + kb)``.  The norm-guard decision of the layer is taken on
+        the first block (the reference takes it on the whole batch at once,
+        packed_qmse_cache.py:918-929; key norms are a property of the layer, not of the sequence)
+        and the running mean over all blocks is kept so that ``finish_prefill`` can tell if the
+        whole-batch rule would have decided otherwise."""
+        b0, total = self._window
+        kb, _, n, _ = key_states.shape
+        if threshold != float("inf"):
+            mean = float(key_norm_mean(key_states).item())
+            self._window_norm[0] += mean * kb
+            self._window_norm[1] += kb
+            if self._window_dense is None:
+                self._window_dense = mean > threshold
+        elif self._window_dense is None:
+            self._window_dense = False
+        self._prefill_shape = (total, *key_states.shape[1:])
+        if self._window_dense:
+            self.device, self.dtype = key_states.device, key_states.dtype
+            self._dense_k.write_rows(key_states, b0, total, self.reserve_tokens)
+            self._dense_v.write_rows(value_states, b0, total, self.reserve_tokens)
+            self._force_dense = True
+            self.is_initialized = True
+            return
+        if not self.is_initialized:
+            self.lazy_initialization(key_states, value_states)
+        local_k, local_v = self.shard.local_kv(key_states), self.shard.local_kv(value_states)
+        if self.store is None:
+            self.store = PackedStore(self.codec, total, int(local_k.shape[1]), int(n) + self.reserve_tokens)
+            self._kv_heads_total = int(key_states.shape[1])
+        self.store.pack_rows(local_k, local_v, b0, 0)
+
+    def begin_prefill_block(self, b0: int, total_batch: int, threshold: float) -> None:
+        """Arm the layer for the prompt K/V of batch rows starting at ``b0`` (of ``total_batch``)."""
+        self._window = (int(b0), int(total_batch))
+        self._stream_threshold = threshold
+
+    def finish_prefill(self, n_tokens: int, threshold: float) -> bool:
+        """All row blocks are in: the cache now holds ``n_tokens`` tokens per row.  Returns whether
+        the whole-batch norm-guard rule agrees with the decision taken on the first block."""
+        self._window, self._stream_threshold = None, None
+        if self._force_dense:
+            self._dense_k.length = self._dense_v.length = int(n_tokens)
+        elif self.store is not None:
+            self.store.length = int(n_tokens)
+        s, rows = self._window_norm
+        return rows == 0 or ((s / rows) > threshold) == bool(self._window_dense)
 
     def _update_lazy(self, key_states, value_states):
         """Store the new token without touching history (reference: packed_qmse_cache.py:626-679):

@@ -109,6 +109,31 @@ class PackedStore:
                                         self.length, self._stream_ptr()), "tq_pack")
         self.length += n
 
+    def pack_rows(self, k: torch.Tensor, v: torch.Tensor, b0: int, pos0: int = 0) -> None:
+        """Quantise ``k`` / ``v`` [kb, Hkv, T, 128] into batch rows ``[b0, b0 + kb)`` at token positions
+        ``[pos0, pos0 + T)`` without touching ``length``: a prompt pass that runs a few sequences
+        at a time fills the cache row block by row block and sets ``length`` when it is done."""
+        kb, n = int(k.shape[0]), int(k.shape[2])
+        if k.shape != v.shape or k.dtype != v.dtype or k.shape[1] != self.kv_heads:
+            raise ValueError("key and value tensors must have the same shape and dtype and this cache's KV heads")
+        if b0 < 0 or b0 + kb > self.batch or pos0 < 0 or pos0 + n > self.capacity:
+            raise ValueError(f"rows [{b0}, {b0 + kb}) x tokens [{pos0}, {pos0 + n}) do not fit a cache of "
+                             f"{self.batch} rows x {self.capacity} tokens")
+        if n == 0 or kb == 0:
+            return
+        if k.stride(-1) != 1:
+            k = k.contiguous()
+        if v.stride(-1) != 1:
+            v = v.contiguous()
+        ptr = lambda t: None if t is None else t[b0:].data_ptr()
+        desc = ffi.CacheDesc(ptr(self.k_codes), ptr(self.k_norms), ptr(self.k_signs), ptr(self.k_rnorms),
+                             ptr(self.v_codes), ptr(self.v_norms), kb, self.kv_heads, self.capacity,
+                             self.kv_heads * self.capacity, self.capacity)
+        kd, vd = dense_desc(k), dense_desc(v)
+        with torch.cuda.device(self.codec.device):
+            ffi.check(ffi.lib().tq_pack(self.codec.handle, C.byref(kd), C.byref(vd), n, C.byref(desc), pos0,
+                                        self._stream_ptr()), "tq_pack")
+
     def suggest_splits(self, seq_len: int | None = None) -> int:
         n = self.length if seq_len is None else seq_len
         return int(ffi.lib().tq_decode_suggest_splits(self.codec.handle, self.batch, self.kv_heads, max(n, 1)))

@@ -16,7 +16,16 @@ exchange is one NCCL all-gather of the per-head attention outputs per step.
 The metric is packed-cache bytes attended per second (134 B per cached token per KV head).
 ``value`` times the step with everything resident in HBM; ``e2e`` adds, per step, the
 host->device copy of the step's inputs (query + the new token's K/V, pinned memory), the
-in-place append of that token, and the device->host copy of the attention output.
+in-place append of that token, and the device->host copy of the attention output (at N > 1
+every rank reads back its own heads; the gathered output stays on the devices).
+
+The same line carries a ``model`` block: decode tokens/s of a random-init Llama-3.1-8B (32
+layers, bf16) under the library's attention backend at 32768-token context, batch 16, after
+a real prompt pass (``prefill_seconds``); at N > 1 the KV heads are sharded, once with the batch
+fixed at 16 (``strong``) and once with 16 sequences per GPU (``weak``, caches filled with packed
+synthetic K/V).  ``--no-model-block`` leaves it out; ``--gpu-comparator`` adds timings of the
+reference's own GPU path (its Triton kernel at batch 1 and its chunked PyTorch path) on the
+same GPU when the reference package has been installed into ``oracle/_ref`` (oracle/make_ref.py).
 """
 
 from __future__ import annotations
@@ -46,11 +55,13 @@ def bytes_per_unit(bits: int, use_qjl: bool) -> int:
     return 16 * key_bits + 2 + (16 + 2 if use_qjl else 0) + 16 * bits + 2
 
 
-# DRAM bytes (read + write) per unit of the main decode kernel, from the ncu capture of the
-# batch-4 case summarised in profiles/decode_mma4_b4_ctx32768.md: 140.74 MB read +
-# 3.6 MB written for 1 048 576 units of 134 B.  Every packed byte is read once, so traffic
-# grows in proportion to the units of a launch.
-NCU_TRAFFIC_BYTES_PER_UNIT = (140.74e6 + 3.6e6) / 1048576
+# DRAM bytes (read + write) per unit of the main decode kernel: dram__bytes_read.sum +
+# dram__bytes_write.sum of one ncu capture of the CURRENT kernel build on the batch-4 case
+# (1 048 576 units of 134 B).  Every packed byte is read once, so traffic grows in proportion to
+# the units of a launch.  A constant taken from that capture, not measured by this run: it is
+# re-captured whenever the kernel changes, and the line says so (``traffic_kind``).
+NCU_TRAFFIC = {"read_bytes": 140.74e6, "write_bytes": 3.6e6, "units": 1048576}
+NCU_TRAFFIC_BYTES_PER_UNIT = (NCU_TRAFFIC["read_bytes"] + NCU_TRAFFIC["write_bytes"]) / NCU_TRAFFIC["units"]
 
 
 def measured_peak():
@@ -116,13 +127,41 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------
-# CPU arm: the reference algorithm (oracle port) on the host cores
+# CPU arm: the reference's own CPU code when it is installed, else this repository's port of it
 # ----------------------------------------------------------------------------
 
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+
+
+def load_reference():
+    """The UNMODIFIED reference package from ``oracle/_ref`` (installed by oracle/make_ref.py), or
+    None.  It is imported under its own name ``turboquant``; this repository's drop-in package of
+    the same name is never imported by the benchmark."""
+    if not os.path.isfile(os.path.join(REF_DIR, "turboquant", "runtime", "packed_qmse_cache.py")):
+        return None
+    if REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
+    for name in [m for m in sys.modules if m == "turboquant" or m.startswith("turboquant.")]:
+        mod_file = getattr(sys.modules[name], "__file__", "") or ""
+        if not mod_file.startswith(REF_DIR):
+            del sys.modules[name]
+    try:
+        import turboquant.runtime.attention as ref_attention
+        import turboquant.runtime.packed_qmse_cache as ref_cache
+    except Exception as exc:  # noqa: BLE001
+        print(f"[bench] the reference package in oracle/_ref does not import ({exc!r})", file=sys.stderr)
+        return None
+    if not (ref_cache.__file__ or "").startswith(REF_DIR):
+        return None
+    return ref_cache, ref_attention
+
+
 def cpu_reference_run(steps: int, warmup: int, sample_batch: int = 1):
-    """Times the oracle's chunked decode attention (the reference's CPU path,
-    src/turboquant/runtime/attention.py:215-304) over a bounded sample of the workload:
-    ``sample_batch`` sequence(s) x 8 KV heads x 32768 tokens, all host threads."""
+    """Times chunked decode attention over the packed cache on the host cores (the reference's
+    CPU path, src/turboquant/runtime/attention.py:215-304) over a bounded sample of the workload:
+    ``sample_batch`` sequence(s) x 8 KV heads x 32768 tokens, all host threads.  Runs the
+    reference's own code when it is installed in ``oracle/_ref`` (``kind: "reference"``), else
+    this repository's restatement of it (``kind: "port"``)."""
     import torch
 
     from oracle import tq_oracle as O
@@ -133,40 +172,73 @@ def cpu_reference_run(steps: int, warmup: int, sample_batch: int = 1):
     dtype = getattr(torch, w["dtype"])
     groups = w["q_heads"] // w["kv_heads"]
     k, v, q = O.synth_kvq(sample_batch, w["q_heads"], w["kv_heads"], w["context"], HEAD_DIM, seed=0, dtype=dtype)
-    p = O.QuantParams.build(HEAD_DIM, w["bits"], w["use_qjl"], seed=0)
+    ref = load_reference()
     t0 = time.perf_counter()
-    layer = O.pack_layer(k, v, p)
+    if ref is not None:
+        ref_cache, ref_attention = ref
+        layer = ref_cache.PackedMSELayer(bits=w["bits"], seed=0, use_qjl_keys=w["use_qjl"], quantize_decode=True)
+        layer.initialize_from_dense(k, v)
+        attend = lambda: ref_attention.chunked_turboquant_attention(q, layer, n_kv_groups=groups)
+        kind, what = "reference", "the reference's PackedMSELayer + chunked_turboquant_attention on CPU tensors"
+    else:
+        p = O.QuantParams.build(HEAD_DIM, w["bits"], w["use_qjl"], seed=0)
+        layer = O.pack_layer(k, v, p)
+        attend = lambda: O.attend_chunked(q, layer, groups)
+        kind, what = "port", "this repository's restatement of the reference's chunked dequantise-then-attend"
     pack_s = time.perf_counter() - t0
     del k, v
-    for _ in range(warmup):
-        O.attend_chunked(q, layer, groups)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        O.attend_chunked(q, layer, groups)
-    dt = (time.perf_counter() - t0) / max(steps, 1)
+    with torch.inference_mode():
+        for _ in range(warmup):
+            attend()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            attend()
+        dt = (time.perf_counter() - t0) / max(steps, 1)
     nbytes = bytes_per_unit(w["bits"], w["use_qjl"]) * sample_batch * w["kv_heads"] * w["context"]
     return {
-        "value": nbytes / dt / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+        "value": nbytes / dt / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": kind,
         "sample": (f"{sample_batch} of {w['batch_per_gpu']} sequences x {w['kv_heads']} KV heads x {w['context']} "
-                   f"tokens, {steps} decode steps after {warmup} warm-up (chunked dequantise-then-attend)"),
+                   f"tokens, {steps} decode steps after {warmup} warm-up; {what}"),
         "ms_per_step": dt * 1e3, "pack_seconds": pack_s,
         "pack_vectors_per_s": 2 * sample_batch * w["kv_heads"] * w["context"] / pack_s,
     }
 
 
+def run_self(extra_args: list[str], timeout: float = 900.0):
+    """Runs this script in a child process (single GPU, no distributed environment) and returns the
+    JSON object of its last output line.  The reference package shares the import name
+    ``turboquant`` and the attention-backend name with this library, so everything that imports
+    it runs in a process of its own."""
+    env = {k: v for k, v in os.environ.items()
+           if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT", "LOCAL_WORLD_SIZE",
+                        "GROUP_RANK", "ROLE_RANK", "TORCHELASTIC_RUN_ID")}
+    try:
+        proc = subprocess.run([sys.executable, os.path.abspath(__file__), *extra_args], capture_output=True, text=True,
+                              timeout=timeout, env=env)
+        lines = [ln for ln in proc.stdout.strip().splitlines() if ln.startswith("{")]
+        if proc.returncode != 0 or not lines:
+            return {"unavailable": f"child exited {proc.returncode}: {proc.stderr.strip()[-300:]}"}
+        return json.loads(lines[-1])
+    except Exception as exc:  # noqa: BLE001
+        return {"unavailable": repr(exc)[:300]}
+
+
 def run_reference_arm(args) -> None:
+    """``--impl reference``: K steps after W warm-up steps, each step one decode step of one
+    sequence of the workload (a bounded sample: the metric is normalised by bytes)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 8)), max(1, min(args.warmup, 2))
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
     r = cpu_reference_run(steps, warmup)
     w = WORKLOAD
     line = {
         "impl": "reference", "metric": "packed_kv_decode_attn_hbm_gbs", "value": r["value"], "unit": "GB/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": w["name"], "batch": 1, "q_heads": w["q_heads"], "kv_heads": w["kv_heads"],
-                   "context": w["context"], "bits": w["bits"], "mode": "Q_prod", "bytes_per_token_head": 134},
+        "config": {"workload": w["name"], "global_batch": 1, "q_heads": w["q_heads"], "kv_heads": w["kv_heads"],
+                   "context": w["context"], "bits": w["bits"], "mode": "Q_prod", "bytes_per_token_head": 134,
+                   "sample": "1 of the workload's 8 sequences per step"},
         "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": r["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -277,6 +349,19 @@ def run_gpu_arm(args) -> None:
             if args.gather == "p2p":
                 raise SystemExit("--gather p2p: the peer gather is not usable on this box")
 
+    # One-off, untimed: the fused gather must give, bit for bit, what an NCCL all-gather of the plain
+    # decode outputs gives (the only multi-GPU correctness evidence a run on this box can carry).
+    gather_check = None
+    if world > 1 and peer is not None:
+        view = store.decode_attn_gather(q, peer, seq_len=n_ctx, splits=splits)
+        store.decode_attn(q, seq_len=n_ctx, splits=splits, out=out)
+        dist.all_gather_into_tensor(gathered, out)
+        want = gathered.view(world, batch, hq, HEAD_DIM).permute(1, 0, 2, 3).reshape(batch, world * hq, 1, HEAD_DIM)
+        torch.cuda.synchronize()
+        same = torch.tensor([1.0 if torch.equal(view, want) else 0.0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        gather_check = "bitexact" if same.item() > 0 else "MISMATCH"
+
     def step():
         if peer is not None:  # the combine kernel writes every rank's gathered buffer itself
             store.decode_attn_gather(q, peer, seq_len=n_ctx, splits=splits)
@@ -332,11 +417,11 @@ def run_gpu_arm(args) -> None:
     h_q = torch.randn(batch, hq, 1, HEAD_DIM).to(dtype).pin_memory()
     h_k = (torch.randn(batch, hkv, 1, HEAD_DIM)).to(dtype).pin_memory()
     h_v = (torch.randn(batch, hkv, 1, HEAD_DIM)).to(dtype).pin_memory()
-    h_out = torch.empty(batch, hq * world, 1, HEAD_DIM, **pin)
+    h_out = torch.empty(batch, hq, 1, HEAD_DIM, **pin)  # N > 1: this rank's heads (the gathered output stays on the devices)
     d_q, d_k, d_v = torch.empty_like(q), torch.empty(batch, hkv, 1, HEAD_DIM, dtype=dtype, device=dev), \
         torch.empty(batch, hkv, 1, HEAD_DIM, dtype=dtype, device=dev)
     h2d = h_q.numel() * h_q.element_size() + h_k.numel() * h_k.element_size() + h_v.numel() * h_v.element_size()
-    d2h = (gathered if world > 1 else out).numel() * out.element_size()
+    d2h = out.numel() * out.element_size()
 
     h_out1 = torch.empty(batch, hq, 1, HEAD_DIM, **pin)
     host_step = store.bind_host_step(h_q, h_k, h_v, h_out1) if world == 1 else None
@@ -355,8 +440,7 @@ def run_gpu_arm(args) -> None:
             store.pack(d_k, d_v)
             store.decode_attn(d_q, splits=splits, out=out)
             dist.all_gather_into_tensor(gathered, out)
-            h_out.view(batch, world, hq, HEAD_DIM).copy_(
-                gathered.view(world, batch, hq, HEAD_DIM).transpose(0, 1), non_blocking=True)
+            h_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the host needs the result before the next token
 
     e2e_steps = 0 if args.skip_e2e else steps
@@ -424,8 +508,10 @@ def run_gpu_arm(args) -> None:
                 "frac": (achieved / peak) if achieved else None, "peak_source": f"of {peak_src}",
                 "kernel": "tq_decode main kernel (streams the packed cache)",
                 "kernel_ms": main_ms / max(main_n, 1),
-                "traffic": NCU_TRAFFIC_BYTES_PER_UNIT * batch * hkv * n_ctx if w["bits"] == 4 else None,
-                "traffic_source": "ncu dram read+write of the batch-4 capture in profiles/, scaled by units",
+                "traffic": NCU_TRAFFIC_BYTES_PER_UNIT * batch * hkv * n_ctx if w["bits"] == 4 and hq // hkv <= 4 else None,
+                "traffic_kind": ("constant: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
+                                 "kernel build on the batch-4 case, scaled by the units of a launch; not measured by "
+                                 "this run"),
             },
             "e2e": None if args.skip_e2e else {
                 "value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
@@ -437,60 +523,47 @@ def run_gpu_arm(args) -> None:
             "pack": {"seconds": pack_s, "vectors_per_s": 2 * batch * hkv * n_ctx / pack_s},
             "dense_sdpa": dense,
         }
+        if gather_check is not None:
+            line["gather_check"] = gather_check
         if world == 1 and not args.no_cpu_baseline:
-            cb = cpu_reference_run(steps=3, warmup=1)
-            line["cpu_baseline"] = {k_: cb[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line))
+            cb = run_self(["--impl", "reference", "--steps", "3", "--warmup", "1"]).get("cpu_baseline")
+            line["cpu_baseline"] = cb if cb else {"unavailable": "the CPU arm did not run"}
+    else:
+        line = None
     if peer is not None:
         peer.close()
+    # free the layer workload before the whole-model block and the comparator
+    del store, q, out, gathered
+    torch.cuda.empty_cache()
+    if args.gpu_comparator and world == 1 and rank == 0:
+        line["gpu_comparator"] = run_self(["--gpu-comparator-only"])
+    if not args.no_model_block:
+        try:
+            block = model_block(args, torch, dist, world, rank, local_rank, dev)
+        except Exception as exc:  # noqa: BLE001  (the headline line must still be printed)
+            if world > 1:
+                raise
+            block = {"unavailable": repr(exc)[:300]}
+        if rank == 0:
+            line["model"] = block
+    if rank == 0:
+        print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
 # ----------------------------------------------------------------------------
-# Whole-model decode: random-init Llama-3.1-8B over a packed 32k-token cache
+# Whole-model decode: random-init Llama-3.1-8B over 32k-token packed caches
 # ----------------------------------------------------------------------------
 
 MODEL_WORKLOAD = dict(name="llama3.1-8b-random-init-decode", batch=16, context=32768, layers=32, hidden=4096,
                       intermediate=14336, q_heads=32, kv_heads=8, vocab=128256, bits=4, use_qjl=True)
 
 
-def run_model_arm(args) -> None:
-    """Decode tokens/s of a whole model step: random-init Llama-3.1-8B (bf16), batch 16, every
-    layer's cache holding 32768 packed tokens per sequence (4-bit Q_prod), greedy decoding through
-    the library's attention backend with the model step replayed from a CUDA graph.  The caches
-    are filled with packed synthetic K/V (the prompt pass is not part of a decode-rate figure).
-    At N > 1 the weights are replicated and the KV heads are sharded (outputs exchanged by the
-    fused peer gather inside the recorded step); the batch stays 16 (``--model-scaling strong``) or
-    grows with N (``weak``)."""
-    import torch
-    import torch.distributed as dist
+def build_model(torch, w, dev):
     from transformers import LlamaConfig, LlamaForCausalLM
-    from transformers.cache_utils import Cache
 
-    from tq_local_b200.adapters.transformers import disable_turboquant_attention, enable_turboquant_attention
-    from tq_local_b200.runtime.generation import RecordedDecoder
-    from tq_local_b200.runtime.packed_qmse_cache import PackedMSELayer
-    from tq_local_b200.runtime.sharding import HeadShard
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    w = dict(MODEL_WORKLOAD)
-    if args.batch_per_gpu:
-        w["batch"] = args.batch_per_gpu
-    if args.model_scaling == "weak":
-        w["batch"] *= world  # every GPU then streams the same packed bytes as one GPU does at N = 1
-    if args.context:
-        w["context"] = args.context
-    if args.layers:
-        w["layers"] = args.layers
-    steps, warmup = args.steps, max(args.warmup, 3)
     cfg = LlamaConfig(vocab_size=w["vocab"], hidden_size=w["hidden"], intermediate_size=w["intermediate"],
                       num_hidden_layers=w["layers"], num_attention_heads=w["q_heads"],
                       num_key_value_heads=w["kv_heads"], head_dim=HEAD_DIM, max_position_embeddings=131072,
@@ -500,37 +573,73 @@ def run_model_arm(args) -> None:
     torch.set_default_dtype(torch.bfloat16)
     try:
         with torch.device(dev):
-            model = LlamaForCausalLM(cfg).eval()
+            return LlamaForCausalLM(cfg).eval()
     finally:
         torch.set_default_dtype(old_dtype)
-    shard = HeadShard.from_process_group() if world > 1 else HeadShard()
+
+
+def model_decode_run(torch, dist, model, w, shard, world, rank, local_rank, dev, steps, warmup, batch, real_prefill):
+    """Decode tokens/s of the whole model at ``batch`` sequences x ``w['context']`` tokens: the packed
+    caches come from a real prompt pass over random token ids (``real_prefill``: a streaming prefill in
+    row blocks, timed as ``prefill_seconds``) or are filled with packed synthetic K/V; then greedy
+    decoding through the library's attention backend, the model step replayed from a CUDA graph
+    (KV-head shards exchange their outputs through the fused peer gather inside the recorded step).
+    Timed with CUDA events over ``steps`` steps after ``warmup``, maximum over the ranks."""
+    from transformers.cache_utils import Cache
+
+    from tq_local_b200.adapters.transformers import disable_turboquant_attention, enable_turboquant_attention
+    from tq_local_b200.runtime import generation
+    from tq_local_b200.runtime.packed_qmse_cache import PackedMSELayer, build_streaming_prefill_cache
+
     gen = torch.Generator(device=dev).manual_seed(99)
-    B, N = w["batch"], w["context"]
-    layers = []
+    B, N = batch, w["context"]
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    prefill_s = None
     with torch.inference_mode():
-        for _ in range(w["layers"]):
-            k = synth_on_device(torch, (B, w["kv_heads"], N, HEAD_DIM), gen, torch.bfloat16)
-            v = synth_on_device(torch, (B, w["kv_heads"], N, HEAD_DIM), gen, torch.bfloat16)
-            layer = PackedMSELayer(bits=w["bits"], use_qjl_keys=w["use_qjl"], quantize_decode=True,
-                                   reserve_tokens=steps + warmup + 8, shard=shard)
-            layer.initialize_from_dense(k, v)
-            layers.append(layer)
-            del k, v
-        cache = Cache(layers=layers)
+        if real_prefill:
+            ids = torch.randint(0, w["vocab"], (B, N), device=dev, generator=gen)
+            cache = build_streaming_prefill_cache(w["layers"], w["bits"], head_dim=HEAD_DIM, use_qjl_keys=w["use_qjl"],
+                                                  quantize_decode=True, norm_guard=True,
+                                                  reserve_tokens=steps + warmup + 8, shard=shard)
+            rows = max(1, generation.PREFILL_BLOCK_TOKENS // N)
+            fence()
+            t0 = time.perf_counter()
+            last = generation._prefill_in_row_blocks(model, {"input_ids": ids}, cache,
+                                                     generation._auto_norm_threshold(w["bits"], HEAD_DIM), rows)
+            first = torch.argmax(last, dim=-1, keepdim=True)
+            fence()
+            prefill_s = time.perf_counter() - t0
+            if world > 1:
+                t = torch.tensor([prefill_s], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                prefill_s = float(t.item())
+            layers = cache.layers
+            del ids, last
+        else:
+            layers = []
+            for _ in range(w["layers"]):
+                k = synth_on_device(torch, (B, w["kv_heads"], N, HEAD_DIM), gen, torch.bfloat16)
+                v = synth_on_device(torch, (B, w["kv_heads"], N, HEAD_DIM), gen, torch.bfloat16)
+                layer = PackedMSELayer(bits=w["bits"], use_qjl_keys=w["use_qjl"], quantize_decode=True,
+                                       reserve_tokens=steps + warmup + 8, shard=shard)
+                layer.initialize_from_dense(k, v)
+                layers.append(layer)
+                del k, v
+            cache = Cache(layers=layers)
+            first = torch.randint(0, w["vocab"], (B, 1), device=dev, generator=gen)
+        dense_layers = sum(1 for layer in layers if layer._force_dense)
         old_impl = enable_turboquant_attention(model, cache)
-        first = torch.randint(0, w["vocab"], (B, 1), device=dev, generator=gen)
         sampler = ClockSampler(local_rank)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        def fence():
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-
         try:
             q_heads = w["q_heads"]
             if all(layer.supports_static_decode(q_heads) for layer in layers):
-                # (sharded layers exchange their outputs through the fused peer gather inside the step)
-                with RecordedDecoder(model, cache, first, warmup + steps) as dec:
+                with generation.RecordedDecoder(model, cache, first, warmup + steps) as dec:
                     for _ in range(warmup):
                         dec.step()
                     fence()
@@ -570,28 +679,157 @@ def run_model_arm(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
+    unit = bytes_per_unit(w["bits"], w["use_qjl"])
+    packed_bytes = unit * B * w["kv_heads"] * N * (w["layers"] - dense_layers)
+    weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
+    status = max((layer.codec.device_status() for layer in layers if layer.codec is not None), default=0)
+    result = {
+        "tok_per_s": B * 1e3 / ms, "ms_per_step": ms, "global_batch": B, "steps": steps, "warmup": warmup,
+        "prefill_seconds": prefill_s,
+        "prefill": ("real prompt pass over random token ids, streamed into the packed cache in row blocks"
+                    if real_prefill else "caches filled with packed synthetic K/V (no prompt pass)"),
+        "decode_step": "CUDA graph replay" if recorded else "eager",
+        "packed_kv_bytes_per_step": packed_bytes, "weight_bytes": weight_bytes,
+        "hbm_gbs_lower_bound": (packed_bytes / world + weight_bytes) / (ms * 1e-3) / 1e9,
+        "tokens_checksum": int(tokens.sum().item()), "device_status": status, "clocks": clocks,
+    }
+    del cache, layers
+    torch.cuda.empty_cache()
+    return result
+
+
+def model_block(args, torch, dist, world, rank, local_rank, dev):
+    """The ``model`` block of the benchmark line (see the module docstring)."""
+    from tq_local_b200.runtime.sharding import HeadShard
+
+    w = dict(MODEL_WORKLOAD)
+    if args.context:
+        w["context"] = args.context
+    if args.layers:
+        w["layers"] = args.layers
+    steps, warmup = max(4, min(args.steps, 32)), 3
+    shard = HeadShard.from_process_group() if world > 1 else HeadShard()
+    model = build_model(torch, w, dev)
+    block = {"workload": w["name"], "context": w["context"], "layers": w["layers"], "metric": "decode_tok_per_s_32k_ctx",
+             "unit": "tok/s", "parallelism": f"kv-head-shard{world}, weights replicated" if world > 1 else "single"}
+    block["strong"] = model_decode_run(torch, dist, model, w, shard, world, rank, local_rank, dev, steps, warmup,
+                                       w["batch"], real_prefill=not args.synthetic_prefill)
+    block["strong"]["scaling"] = "strong (batch 16 in total)"
+    if world > 1:
+        block["weak"] = model_decode_run(torch, dist, model, w, shard, world, rank, local_rank, dev, steps, warmup,
+                                         w["batch"] * world, real_prefill=False)
+        block["weak"]["scaling"] = "weak (16 sequences per GPU)"
+    else:
+        block["weak"] = dict(block["strong"], scaling="weak (16 sequences per GPU; the same run at one GPU)")
+    del model
+    torch.cuda.empty_cache()
+    return block
+
+
+def run_model_arm(args) -> None:
+    """``--workload model``: the whole-model figure alone, as a line of its own."""
+    import torch
+    import torch.distributed as dist
+
+    from tq_local_b200.runtime.sharding import HeadShard
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    w = dict(MODEL_WORKLOAD)
+    if args.batch_per_gpu:
+        w["batch"] = args.batch_per_gpu
+    if args.model_scaling == "weak":
+        w["batch"] *= world  # every GPU then streams the same packed bytes as one GPU does at N = 1
+    if args.context:
+        w["context"] = args.context
+    if args.layers:
+        w["layers"] = args.layers
+    steps, warmup = args.steps, max(args.warmup, 3)
+    shard = HeadShard.from_process_group() if world > 1 else HeadShard()
+    model = build_model(torch, w, dev)
+    r = model_decode_run(torch, dist, model, w, shard, world, rank, local_rank, dev, steps, warmup, w["batch"],
+                         real_prefill=not args.synthetic_prefill and args.model_scaling == "strong")
     if rank == 0:
-        unit = bytes_per_unit(w["bits"], w["use_qjl"])
-        packed_bytes = unit * B * w["kv_heads"] * N * w["layers"]
-        weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
         line = {
-            "metric": "decode_tok_per_s_32k_ctx", "value": B * 1e3 / ms, "unit": "tok/s", "n_gpus": world,
-            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": args.model_scaling,
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": w["name"], "global_batch": B, "context": N, "layers": w["layers"],
+            "metric": "decode_tok_per_s_32k_ctx", "value": r["tok_per_s"], "unit": "tok/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "scaling": args.model_scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "global_batch": w["batch"], "context": w["context"], "layers": w["layers"],
                        "q_heads": w["q_heads"], "kv_heads": w["kv_heads"], "bits": w["bits"], "mode": "Q_prod",
                        "parallelism": f"kv-head-shard{world}, weights replicated" if world > 1 else "single",
-                       "decode_step": "CUDA graph replay" if recorded else "eager"},
-            "packed_kv_bytes_per_step": packed_bytes, "weight_bytes": weight_bytes,
-            "hbm_gbs_lower_bound": (packed_bytes / world + weight_bytes) / (ms * 1e-3) / 1e9,
-            "tokens_checksum": int(tokens.sum().item()),
-            "clocks": clocks,
+                       "decode_step": r["decode_step"], "prefill": r["prefill"]},
         }
+        line.update({k: r[k] for k in ("prefill_seconds", "packed_kv_bytes_per_step", "weight_bytes",
+                                       "hbm_gbs_lower_bound", "tokens_checksum", "device_status", "clocks")})
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------
+# The reference's own GPU path on the same GPU (comparator only; never on the product's path)
+# ----------------------------------------------------------------------------
+
+def gpu_comparator(torch, dev, steps: int = 10):
+    """Times the reference's fused Triton decode attention (batch 1: the only shape it serves,
+    src/turboquant/runtime/triton_kernels.py:238-368) and its chunked PyTorch path on the GPU
+    (batch 8, src/turboquant/runtime/attention.py:215-304) at the workload's shape, with the
+    reference package from ``oracle/_ref``.  CUDA events, 3 warm-up calls."""
+    ref = load_reference()
+    if ref is None:
+        return {"unavailable": "the reference package is not installed in oracle/_ref (python oracle/make_ref.py)"}
+    ref_cache, ref_attention = ref
+    import turboquant.runtime.triton_kernels as ref_tk
+
+    w = WORKLOAD
+    dtype = getattr(torch, w["dtype"])
+    groups = w["q_heads"] // w["kv_heads"]
+    gen = torch.Generator(device=dev).manual_seed(4321)
+    unit = bytes_per_unit(w["bits"], w["use_qjl"])
+    out = {}
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, batch in (("triton_fused_batch1", 1), ("chunked_pytorch_batch8", w["batch_per_gpu"])):
+        try:
+            with torch.inference_mode():
+                layer = ref_cache.PackedMSELayer(bits=w["bits"], seed=0, use_qjl_keys=w["use_qjl"], quantize_decode=True)
+                k = synth_on_device(torch, (batch, w["kv_heads"], w["context"], HEAD_DIM), gen, dtype)
+                v = synth_on_device(torch, (batch, w["kv_heads"], w["context"], HEAD_DIM), gen, dtype)
+                layer.initialize_from_dense(k, v)
+                del k, v
+                q = torch.randn(batch, w["q_heads"], 1, HEAD_DIM, generator=gen, device=dev).to(dtype)
+                if name.startswith("triton"):
+                    call = lambda: ref_tk.fused_attention(q, layer, groups)
+                    if call() is None:
+                        out[name] = {"unavailable": "fused_attention returned None (Triton path not taken)"}
+                        continue
+                else:
+                    call = lambda: ref_attention.chunked_turboquant_attention(q, layer, n_kv_groups=groups)
+                for _ in range(3):
+                    call()
+                torch.cuda.synchronize()
+                ev0.record()
+                for _ in range(steps):
+                    call()
+                ev1.record()
+                torch.cuda.synchronize()
+                ms = ev0.elapsed_time(ev1) / steps
+                nbytes = unit * batch * w["kv_heads"] * w["context"]
+                out[name] = {"ms_per_step": ms, "packed_gbs": nbytes / (ms * 1e-3) / 1e9, "batch": batch,
+                             "what": ("the reference's fused_attention (Triton tile kernel + host-side reduce)"
+                                      if name.startswith("triton") else
+                                      "the reference's chunked_turboquant_attention on CUDA tensors (what it runs "
+                                      "for batch > 1)")}
+                del layer
+                torch.cuda.empty_cache()
+        except Exception as exc:  # noqa: BLE001
+            out[name] = {"unavailable": repr(exc)[:300]}
+    return out
 
 
 def main() -> None:
@@ -616,10 +854,21 @@ def main() -> None:
                     help="N > 1: how the per-head outputs are exchanged: p2p = stores into the peers' buffers fused "
                          "into the combine kernel, nccl = NCCL all-gather, auto = p2p with a fall-back to nccl")
     ap.add_argument("--model-scaling", default="strong", choices=["strong", "weak"],
-                    help="model workload at N > 1: strong = batch 16 in total (BASELINE config 5), weak = 16 per GPU")
+                    help="model workload at N > 1: strong = batch 16 in total, weak = 16 sequences per GPU")
     ap.add_argument("--layers", type=int, default=None, help="model workload: override the layer count (smoke runs)")
+    ap.add_argument("--no-model-block", action="store_true",
+                    help="layer workload: leave the whole-model block out of the line (profiling captures)")
+    ap.add_argument("--synthetic-prefill", action="store_true",
+                    help="model workload: fill the caches with packed synthetic K/V instead of running the prompt pass")
+    ap.add_argument("--gpu-comparator", action="store_true",
+                    help="N = 1: also time the reference's own GPU path (needs oracle/_ref, see oracle/make_ref.py)")
+    ap.add_argument("--gpu-comparator-only", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.gpu_comparator_only:
+        import torch
+
+        print(json.dumps(gpu_comparator(torch, torch.device("cuda", 0))))
+    elif args.impl == "reference":
         run_reference_arm(args)
     elif args.workload == "model":
         run_model_arm(args)

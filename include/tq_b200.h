@@ -98,6 +98,12 @@ typedef struct {
     int32_t capacity; /* tokens allocated per (b, h) row */
     int64_t stride_b; /* in tokens */
     int64_t stride_h; /* in tokens */
+    const int32_t *seq_start; /* optional DEVICE array [batch]: the decode calls attend tokens
+                                 [seq_start[b], seq_len) of batch entry b instead of [0, seq_len)
+                                 - a left-padded batch, the only mask shape a decoder-only generation
+                                 loop produces; NULL = every row from token 0.  What the reference's
+                                 chunked path gets by adding the attention-mask slice to its logits
+                                 (src/turboquant/runtime/attention.py:253-255,278-283). */
 } tq_cache_desc;
 
 /* A dense [batch, heads, tokens, 128] tensor with arbitrary outer strides (in elements);
@@ -220,6 +226,10 @@ struct tq_gather_desc {
     uint32_t *seq_dev;              /* optional local device word holding the LAST completed sequence number
                                        (zero-initialised): the step then takes its number from the device, the
                                        combine kernel advances it, and a recorded launch sequence can be replayed */
+    int32_t out_local_only;         /* non-zero: the copy that tq_gather_wait / tq_decode_step_host_gather make for the
+                                       caller (out_final / out_host) holds only THIS rank's heads
+                                       [batch, q_heads_total / world, 128] instead of the whole gathered output; the
+                                       gathered buffers themselves are always complete */
 };
 
 int32_t tq_peer_buffer_create(size_t bytes, void **dev_ptr, void *handle64_out);
@@ -236,7 +246,7 @@ int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
                               tq_stream stream);
 /* tq_decode_step_host for a KV-head shard: q_host [batch, q_heads, 128] and k_host / v_host
  * [batch, kv_heads, 128] are this rank's heads, out_host receives the gathered output of all
- * ranks [batch, q_heads_total, 128].  All four buffers must be page-locked host memory mapped
+ * ranks [batch, q_heads_total, 128] (or, with gather->out_local_only, this rank's heads only).  All four buffers must be page-locked host memory mapped
  * into the device's address space (or device memory); 16-bit dtypes only.  Queues the append,
  * the attention, the exchange and the wait. */
 int32_t tq_decode_step_host_gather(tq_ctx *ctx, const void *q_host, const void *k_host, const void *v_host,

@@ -1,5 +1,6 @@
-"""CPU: the reference arm of bench.py (the oracle port on host cores) prints one JSON line with
-the keys the measurement contract asks for, and the GPU arm refuses to run without a device."""
+"""CPU: the reference arm of bench.py (the reference's own CPU code when it is installed under
+oracle/_ref, else this repository's restatement of it) prints one JSON line with the keys the
+measurement contract asks for, and the GPU arm refuses to run without a device."""
 
 from __future__ import annotations
 
@@ -28,9 +29,35 @@ def test_reference_arm_prints_the_contract_line():
         assert key in line, key
     assert line["vs_baseline"] is None and line["config"]["workload"]
     cb = line["cpu_baseline"]
-    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == line["value"] and cb["sample"]
+    installed = os.path.isfile(os.path.join(ROOT, "oracle", "_ref", "turboquant", "runtime", "packed_qmse_cache.py"))
+    assert cb["kind"] == ("reference" if installed else "port")
+    assert cb["cores"] >= 1 and cb["value"] == line["value"] and cb["sample"]
+    assert line["steps"] == 1 and line["warmup"] == 1  # K and W are honoured as given
     assert line["e2e"] == {"value": line["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert line["value"] > 0
+
+
+def test_port_and_reference_agree_on_the_output():
+    """The two CPU arms compute the same attention (the port is a restatement of the reference):
+    checked on a small layer when the reference package is installed.  Runs in a child process:
+    the reference shares its import name with this repository's drop-in package."""
+    if not os.path.isfile(os.path.join(ROOT, "oracle", "_ref", "turboquant", "runtime", "packed_qmse_cache.py")):
+        return
+    code = """
+import sys, torch
+sys.path.insert(0, %r)
+import bench
+from oracle import tq_oracle as O
+ref_cache, ref_attention = bench.load_reference()
+k, v, q = O.synth_kvq(1, 8, 2, 300, 128, seed=3, dtype=torch.bfloat16)
+layer = ref_cache.PackedMSELayer(bits=4, seed=0, use_qjl_keys=True, quantize_decode=True)
+layer.initialize_from_dense(k, v)
+theirs = ref_attention.chunked_turboquant_attention(q, layer, n_kv_groups=4)
+mine = O.attend_chunked(q, O.pack_layer(k, v, O.QuantParams.build(128, 4, True, seed=0)), 4)
+print("SAME" if torch.equal(theirs, mine) else "DIFFERENT")
+""" % ROOT
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "SAME" in out.stdout, out.stdout[-500:] + out.stderr[-1500:]
 
 
 def test_reference_arm_other_ranks_stay_silent():

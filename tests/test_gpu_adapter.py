@@ -289,3 +289,82 @@ def test_long_prompt_batch_16_by_32768_through_activate_on_two_layers():
     # four sequences (131072 tokens) per block: activations of a block stay far below what the
     # whole batch would need (the MLP intermediates alone would be 45 GB)
     assert torch.cuda.max_memory_allocated() - base < 40e9
+
+
+def test_attention_masks_on_the_packed_path():
+    """The cache layer turns a left-padding mask (2-D, 4-D boolean or 4-D additive) into per-row
+    start offsets; ``chunked_turboquant_attention`` accepts the mask and un-stored new tokens."""
+    from tq_local_b200.runtime.attention import chunked_turboquant_attention
+    from tq_local_b200.runtime.packed_qmse_cache import PackedMSELayer, is_left_padding_mask, leading_masked_tokens
+
+    B, Hq, Hkv, N = 3, 8, 2, 90
+    k, v, q = O.synth_kvq(B, Hq, Hkv, N + 2, 128, seed=51, dtype=torch.bfloat16)
+    layer = PackedMSELayer(bits=4, use_qjl_keys=True, quantize_decode=True, reserve_tokens=4)
+    layer.initialize_from_dense(k[:, :, :N].cuda(), v[:, :, :N].cuda())
+    pads = [0, 7, 33]
+    m2 = torch.ones(B, N, dtype=torch.long)
+    for b, n in enumerate(pads):
+        m2[b, :n] = 0
+    assert is_left_padding_mask(m2.cuda()) and not is_left_padding_mask(torch.flip(m2, dims=[1]).cuda())
+    assert leading_masked_tokens(m2.cuda()).tolist() == pads
+    m4_bool = m2.bool()[:, None, None, :].cuda()
+    m4_add = torch.where(m4_bool, 0.0, torch.finfo(torch.bfloat16).min).to(torch.bfloat16)
+    assert leading_masked_tokens(m4_bool).tolist() == pads and leading_masked_tokens(m4_add).tolist() == pads
+    qd = q.cuda()
+    plain = layer.attend(qd).clone()
+    masked = [layer.attend(qd, m).clone() for m in (m2.cuda(), m4_bool, m4_add)]
+    assert torch.equal(masked[0], masked[1]) and torch.equal(masked[0], masked[2])
+    assert torch.equal(masked[0][0], plain[0]) and not torch.equal(masked[0][2], plain[2])
+    assert torch.equal(layer.attend(qd), plain)  # a call without a mask is unrestricted again
+    assert torch.equal(chunked_turboquant_attention(qd, layer, n_kv_groups=4, attention_mask=m4_bool), masked[0])
+    # per-row oracle: row b attends tokens [pad_b, N)
+    p = O.QuantParams.build(128, 4, True, seed=0, rot_v=layer.codec.rot_v, rot_k=layer.codec.rot_k)
+    s = layer.store
+    for b, n in enumerate(pads):
+        c = lambda t: t[b:b + 1, :, n:N].contiguous().cpu()
+        mine = O.PackedLayer(p, torch.bfloat16, c(s.k_codes), c(s.k_norms), c(s.v_codes), c(s.v_norms),
+                             c(s.k_signs), c(s.k_rnorms))
+        want = O.attend_rotated_space(q[b:b + 1], mine, 4)
+        assert float((masked[0][b:b + 1].float().cpu() - want).abs().max() / want.abs().max()) <= 2e-3 + 2.0 ** -9
+    # un-stored new tokens are attended dense, after the cache, and nothing is stored
+    before = [t.clone() for t in s.streams()]
+    got = chunked_turboquant_attention(qd, layer, new_key=k[:, :, N:].cuda(), new_value=v[:, :, N:].cuda(), n_kv_groups=4)
+    want = s.decode_attn(qd, tail_k=k[:, :, N:].cuda(), tail_v=v[:, :, N:].cuda())
+    assert torch.equal(got, want) and s.length == N and not torch.equal(got, plain)
+    for a, b_ in zip(before, s.streams()):
+        assert torch.equal(a, b_)
+    # a bound mask stays in force for calls without one (the generation loop binds the prompt's mask)
+    layer.bind_attention_mask(m2.cuda())
+    assert torch.equal(layer.attend(qd), masked[0])
+    layer.bind_attention_mask(None)
+    assert torch.equal(layer.attend(qd), plain)
+
+
+def test_generate_with_a_left_padded_batch_matches_the_unpadded_prompt():
+    """A short prompt left-padded into a batch must generate what it generates alone: the padding is
+    masked in the prompt pass (the model's own attention) and in every packed decode step, eager
+    and recorded.  (RoPE is relative, so the shifted positions of the padded row do not matter.)"""
+    import turboquant
+
+    model = _tiny_model(torch.float32)
+    gen = torch.Generator("cuda").manual_seed(9)
+    long_ids = torch.randint(1, 512, (1, 48), device="cuda", generator=gen)
+    short_ids = torch.randint(1, 512, (1, 29), device="cuda", generator=gen)
+    batch = torch.cat((long_ids, torch.cat((torch.zeros(1, 19, dtype=torch.long, device="cuda"), short_ids), dim=1)))
+    mask = torch.ones_like(batch)
+    mask[1, :19] = 0
+    for graph in (False, True):
+        turboquant.activate(model, StubTokenizer(), quiet=True, bits=4, use_qjl_keys=False, verify=False, cuda_graph=graph)
+        alone = model.generate(short_ids, max_new_tokens=12)[:, 29:]
+        both = model.generate(batch, attention_mask=mask, max_new_tokens=12)
+        unmasked = model.generate(batch, max_new_tokens=12)
+        turboquant.deactivate(model, quiet=True)
+        assert int(both[1, 48]) == int(alone[0, 0])  # first token: dense prompt pass with the mask
+        assert (both[1, 48:] == alone[0]).float().mean() >= 0.9, (graph, both[1, 48:], alone[0])
+        assert not torch.equal(unmasked[1, 48:], both[1, 48:])  # attending the padding changes the text
+    with pytest.raises(ValueError):
+        turboquant.activate(model, StubTokenizer(), quiet=True, bits=4, verify=False)
+        try:
+            model.generate(batch, attention_mask=torch.flip(mask, dims=[1]), max_new_tokens=4)
+        finally:
+            turboquant.deactivate(model, quiet=True)

@@ -395,3 +395,53 @@ def test_zz_report_worst_unrounded_error():
     for key in sorted(WORST):
         print(f"worst unrounded attention error {key}: {WORST[key]:.3e}")
         assert WORST[key] <= 2e-3
+
+
+@pytest.mark.parametrize("bits,qjl,dtype,Hq,Hkv", [
+    (4, True, torch.bfloat16, 8, 2),    # tensor-core kernel, four heads per KV head
+    (4, True, torch.bfloat16, 14, 2),   # wide variant
+    (3, True, torch.float16, 4, 2),
+    (4, False, torch.float32, 8, 2),    # fp32-exact kernel
+])
+def test_left_padded_rows_attend_from_their_first_real_token(setup_golden, bits, qjl, dtype, Hq, Hkv):
+    """``seq_start``: row b attends tokens [start_b, N).  Checked against the oracle's attention
+    over each row's own slice of the cache; starts fall on, next to and far from the kernel's
+    512-token steps, and one row has no padding."""
+    from tq_local_b200.runtime.packed_store import PackedStore
+
+    p = oracle_params(bits, qjl, setup_golden)
+    codec = make_codec(bits, qjl, setup_golden)
+    starts = [0, 5, 511, 512, 700, 1499]
+    B, N = len(starts), 1500
+    k, v, q = O.synth_kvq(B, Hq, Hkv, N, 128, seed=77, dtype=dtype)
+    store = PackedStore(codec, B, Hkv, capacity=N + 8)
+    store.pack(k.cuda(), v.cuda())
+    groups = Hq // Hkv
+    for splits in (1, 4):
+        store.set_seq_start(None)
+        unmasked = store.decode_attn(q.cuda(), splits=splits).clone()
+        store.set_seq_start(torch.tensor(starts, dtype=torch.int32, device="cuda"))
+        got = store.decode_attn(q.cuda(), splits=splits)
+        raw = got if dtype == torch.float32 else store.decode_attn_f32(q.cuda(), splits=splits)
+        for b, s0 in enumerate(starts):
+            sl = lambda t: None if t is None else t[b:b + 1, :, s0:N].contiguous().cpu()
+            mine = O.PackedLayer(p, dtype, sl(store.k_codes), sl(store.k_norms), sl(store.v_codes), sl(store.v_norms),
+                                 sl(store.k_signs), sl(store.k_rnorms))
+            want = O.attend_rotated_space(q[b:b + 1], mine, groups)
+            assert rel_inf(raw[b:b + 1], want) <= KERNEL_TOL[dtype], (b, s0, splits)
+        assert torch.equal(got[0], unmasked[0])  # the unpadded row is untouched by the others' offsets
+    store.set_seq_start(None)
+    assert torch.equal(store.decode_attn(q.cuda(), splits=4), unmasked)
+    # the device-length step honours the offsets too
+    if dtype != torch.float32:
+        store.set_seq_start(torch.tensor(starts, dtype=torch.int32, device="cuda"))
+        ref_store = PackedStore(codec, B, Hkv, capacity=N + 8)
+        ref_store.pack(k.cuda(), v.cuda())
+        ref_store.set_seq_start(torch.tensor(starts, dtype=torch.int32, device="cuda"))
+        k1, v1, _ = O.synth_kvq(B, Hq, Hkv, 1, 128, seed=78, dtype=dtype)
+        ref_store.pack(k1.cuda(), v1.cuda())
+        want = ref_store.decode_attn(q.cuda())
+        pos = torch.tensor([N], dtype=torch.int32, device="cuda")
+        got = store.decode_step_dev(q.cuda(), k1.cuda(), v1.cuda(), pos)
+        assert rel_inf(got, want.float().cpu()) <= 2.0 ** -7
+    assert codec.device_status() == 0

@@ -111,8 +111,9 @@ def enable_turboquant_attention(model, packed_cache: Cache) -> str | None:
     """Route the model's attention through the packed cache: set the attention implementation
     to ``"turboquant"``, hang each ``PackedMSELayer`` on its ``self_attn._tq_cache_layer`` and
     switch the layers to lazy updates.  Returns the previous implementation name."""
-    import tq_local_b200.runtime.attention  # noqa: F401  (registers the backend)
+    from tq_local_b200.runtime.attention import _register_attention_backend
 
+    _register_attention_backend()  # (again on every switch: another package may have taken the name since import)
     layers = _get_model_layers(model)
     if layers is None:
         raise RuntimeError("Cannot locate model decoder layers for TurboQuant attention wiring.")

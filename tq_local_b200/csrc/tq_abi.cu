@@ -179,6 +179,7 @@ int tq_check_cache(const tq_ctx *ctx, const tq_cache_desc *c) {
     const uintptr_t all = (uintptr_t)c->k_codes | (uintptr_t)c->k_norms | (uintptr_t)c->v_codes |
                           (uintptr_t)c->v_norms | (uintptr_t)c->k_signs | (uintptr_t)c->k_rnorms;
     if (all & 15) return TQ_ERR_ARG;
+    if ((uintptr_t)c->seq_start & 3) return TQ_ERR_ARG;
     return TQ_OK;
 }
 

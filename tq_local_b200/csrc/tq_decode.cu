@@ -22,6 +22,7 @@ struct ExactArgs {
     const uint16_t *v_norms;
     int64_t cache_sb, cache_sh;
     int Hkv, G, N, n_splits;
+    const int *seq_start;  // per batch entry: first token attended (null: 0)
     const float *qrot;   // [B*Hq][128]
     const float *qproj;  // [B*Hq][128]
     float *part_m, *part_l, *part_acc;
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(kExactWarps * 32) tq_decode_exact_kernel(Exact
     const int c_begin = split * chunks_per_split;
     const int c_end = min(chunks, c_begin + chunks_per_split);
     const int64_t row0 = (int64_t)b * a.cache_sb + (int64_t)h * a.cache_sh;
+    const int t_lo = a.seq_start ? a.seq_start[b] : 0;        // tokens before it are masked (left padding)
     const float hs = 0.08838834764831845f;                    // 1/sqrt(128)
     const float qjl_scale = 1.2533141373155003f / (float)TQ_D;  // sqrt(pi/2)/D
 
@@ -80,8 +82,8 @@ __global__ void __launch_bounds__(kExactWarps * 32) tq_decode_exact_kernel(Exact
     for (int c = c_begin + warp; c < c_end; c += kExactWarps) {
         const int base = c * 32;
         const int tok = base + lane;
-        const bool valid = tok < a.N;
-        const int64_t row = row0 + (valid ? tok : base);
+        const bool valid = tok < a.N && tok >= t_lo;
+        const int64_t row = row0 + (tok < a.N ? tok : base);
         // ---- phase A: one token per lane, all G logits
         uint32_t kw[4 * KB + 1];
         {
@@ -432,7 +434,7 @@ __device__ __forceinline__ unsigned long long tq_global_ns() {
 // optionally, every block copies its slice of this rank's gathered buffer of the step to `dst`.
 __global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned seq_arg, const unsigned *seq_ptr,
                                       int *error_flag, unsigned long long limit_ns, const uint4 *src0, long long stride,
-                                      uint4 *dst, size_t n16) {
+                                      uint4 *dst, size_t n16, size_t row_len16, size_t row_stride16, size_t src_off16) {
     // A step numbered on the device gets its number from the combine kernel's last block, so that
     // kernel has to be complete before the number is read; a host-numbered step may start polling early.
     if (seq_ptr) tq_grid_dependency_wait();
@@ -455,9 +457,11 @@ __global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned
     }
     __syncthreads();
     if (!dst || s_failed) return;
+    // dst is dense; piece i of it is piece (i % row_len16) of source row (i / row_len16), rows being
+    // row_stride16 apart and starting src_off16 into the buffer (a whole-buffer copy is one row)
     const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(src0) + ((seq & 1u) ? stride : 0));
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
-        dst[i] = src[i];
+        dst[i] = src[(i / row_len16) * row_stride16 + src_off16 + i % row_len16];
 }
 
 // The decode kernels run with the largest shared-memory carve-out.  The small kernels around
@@ -555,9 +559,21 @@ int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, c
     return TQ_OK;
 }
 
-int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limit_ms, size_t bytes, void *out_final,
-                              cudaStream_t stream) {
-    const size_t n16 = out_final ? bytes / 16 : 0;
+int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limit_ms, int32_t batch, size_t elem_bytes,
+                              void *out_final, cudaStream_t stream) {
+    // out_final: the whole gathered output [batch, q_heads_total, 128], or (out_local_only) this
+    // rank's heads of it [batch, q_heads_total / world, 128]
+    size_t n16 = 0, row_len16 = 1, row_stride16 = 0, src_off16 = 0;
+    if (out_final) {
+        const size_t head16 = TQ_D * elem_bytes / 16;
+        const size_t heads_local = (size_t)g->q_heads_total / g->world;
+        if (g->out_local_only) {
+            row_len16 = heads_local * head16, row_stride16 = (size_t)g->q_heads_total * head16;
+            src_off16 = (size_t)g->rank * heads_local * head16, n16 = (size_t)batch * row_len16;
+        } else {
+            n16 = (size_t)batch * g->q_heads_total * head16, row_len16 = n16;
+        }
+    }
     const int blocks = out_final ? (int)((n16 + 255) / 256 < 64 ? (n16 + 255) / 256 : 64) : 1;
     // Launched as a programmatic dependent: with a host-side step number it begins polling while the
     // combine kernel that raises this rank's own flag is still finishing (harmless: the flags carry
@@ -568,7 +584,7 @@ int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limi
                                      (const unsigned *)g->seq_dev, error_flag,
                                      (unsigned long long)(limit_ms < 1 ? 1 : limit_ms) * 1000000ull,
                                      reinterpret_cast<const uint4 *>(g->out[g->rank]), (long long)g->out_stride,
-                                     reinterpret_cast<uint4 *>(out_final), n16);
+                                     reinterpret_cast<uint4 *>(out_final), n16, row_len16, row_stride16, src_off16);
     TQ_CUDA_CHECK(e);
     return TQ_OK;
 }
@@ -604,6 +620,7 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
     a.v_codes = cache->v_codes, a.v_norms = cache->v_norms;
     a.cache_sb = cache->stride_b, a.cache_sh = cache->stride_h;
     a.Hkv = cache->kv_heads, a.G = q_heads / cache->kv_heads, a.N = seq_len, a.n_splits = n_splits;
+    a.seq_start = cache->seq_start;
     a.qrot = w.qrot, a.qproj = w.qproj;
     a.part_m = w.part_m, a.part_l = w.part_l, a.part_acc = w.part_acc;
     a.centers_k = ctx->centers_k, a.centers_v = ctx->centers_v;

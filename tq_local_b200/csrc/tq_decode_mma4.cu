@@ -82,6 +82,7 @@ struct Mma4Args {
     int rows;    // batch * kv_heads
     int n_pad;   // N rounded up to the CTA step: rows are laid end to end in units of n_pad tokens
     int chunk;   // tokens of that flattened (row, token) space per CTA
+    const int *seq_start;  // per batch entry: first token attended (null: 0)
     int stable_len;  // tokens [0, stable_len) of every row were written before the preceding kernel began
     // Length kept on the device (launch sequences replayed from a CUDA graph): when len_ptr is
     // set, N = min(*len_ptr + len_add, capacity), stable_len = *len_ptr, and n_pad / chunk are
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     // ---- a segment = the part of one (batch, KV head) row inside this CTA's piece
     constexpr int kCtaStep = kWarps * kStageTok;
     struct Seg {
-        int bh, seg_len, t_end, grp_first, n_iter;
+        int bh, seg_len, t_lo, t_end, grp_first, n_iter;
         int64_t row0;
     };
     auto seg_at = [&](int64_t flat) {
@@ -259,7 +260,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         sg.seg_len = (int)min((int64_t)(n_pad - seg_lo), flat_end - flat);
         sg.row0 = (int64_t)(sg.bh / a.Hkv) * a.cache_sb + (int64_t)(sg.bh % a.Hkv) * a.cache_sh;
         sg.t_end = min(N, seg_lo + sg.seg_len);
-        sg.grp_first = seg_lo + gq * kGroupTok;
+        // a left-padded row attends tokens [t_lo, N): CTA steps that lie wholly before t_lo are left out
+        sg.t_lo = a.seq_start ? a.seq_start[sg.bh / a.Hkv] : 0;
+        const int first_tok = min(max(seg_lo, sg.t_lo / kCtaStep * kCtaStep), seg_lo + sg.seg_len);
+        sg.grp_first = first_tok + gq * kGroupTok;
         sg.n_iter = sg.grp_first < sg.t_end ? (sg.t_end - sg.grp_first + kCtaStep - 1) / kCtaStep : 0;
         return sg;
     };
@@ -328,7 +332,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     const int bh = sg.bh;
     const int split = blockIdx.x - (int)(((int64_t)bh * n_pad) / chunk);  // partial slot inside the row
     const int64_t q_row0 = (int64_t)bh * G;
-    const int t_end = sg.t_end;
+    const int t_end = sg.t_end, t_lo = sg.t_lo;
     const int my_first = sg.grp_first + wq * kStageTok;
     const int n_iter = sg.n_iter;
     const int n_first = min(n_iter, kStages);
@@ -398,7 +402,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         const uint8_t *slot = smem + (slot_u32(st) - dyn_base);
         if (base < t_end) {  // (a warp whose tokens all lie past the end only takes part in the hand-shake)
         if (!mbar_wait(full_u32 + st * 8, use_parity)) timed_out = true;
-        const bool tail = base + kStageTok > t_end;
+        // `tail`: some of the warp's 32 tokens lie outside [t_lo, t_end) and get masked one by one;
+        // a warp with all 32 before t_lo (only in a row's first step) has waited and now skips the math
+        const bool tail = base + kStageTok > t_end || base < t_lo;
+        if (base + kStageTok > t_lo) {
         // this warp's 32 tokens inside the slot
         const uint8_t *spK = slot + L::kK + wq * kStageTok * 16 * KB;
         const uint8_t *spV = slot + L::kV + wq * kStageTok * 16 * VB;
@@ -471,9 +478,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
             }
 #pragma unroll
             for (int hl = 0; hl < NH; ++hl) {
-                if (tail) {  // rows past the range hold stale bytes
-                    if (base + slotA >= t_end) lgA[hl] = -INFINITY;
-                    if (base + slotB >= t_end) lgB[hl] = -INFINITY;
+                if (tail) {  // rows past the range hold stale bytes, rows before it are masked
+                    if (base + slotA >= t_end || base + slotA < t_lo) lgA[hl] = -INFINITY;
+                    if (base + slotB >= t_end || base + slotB < t_lo) lgB[hl] = -INFINITY;
                 }
                 // (lanes whose head >= G see a zero query: their state is never read)
                 lg[i][0][hl] = lgA[hl], lg[i][1][hl] = lgB[hl];
@@ -547,6 +554,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                 mma_f16(o[mt], a0, a1, a2, a3, pb[i][0], pb[i][1]);
             }
         }
+        }  // at least one token at or after t_lo
         }  // base < t_end
         // ------------------------------------------------------------ hand the slot back; the warps of the
         // group take turns to wait until all of them have done so and to request the refill
@@ -669,6 +677,7 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     const TqPlan plan = tq_make_plan(seq_len, a.rows, ctx->sm_count, n_splits, step);
     a.n_pad = plan.n_pad, a.chunk = plan.chunk;
     const int64_t total = (int64_t)a.rows * a.n_pad;
+    a.seq_start = cache->seq_start;
     a.stable_len = append ? append->pos0 : seq_len;
     a.len_ptr = len_ptr, a.len_add = append ? 1 : 0, a.capacity = cache->capacity;
     a.frag = frag;

@@ -42,8 +42,8 @@ struct DecodeWorkspace {
 };
 
 DecodeWorkspace tq_carve_workspace(void *workspace, int64_t rows, int n_splits);
-int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limit_ms, size_t bytes, void *out_final,
-                              cudaStream_t stream);
+int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limit_ms, int32_t batch, size_t elem_bytes,
+                              void *out_final, cudaStream_t stream);
 int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
                         cudaStream_t stream);
 // Query preparation for the tensor-core kernel; with `append` the same launch also encodes and

@@ -77,12 +77,11 @@ extern "C" int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, int
     if (!ctx) return TQ_ERR_ARG;
     int rc = tq_check_gather(gather);
     if (rc) return rc;
-    size_t bytes = 0;
     if (out_final) {
         if (batch <= 0 || (dtype != TQ_DTYPE_F16 && dtype != TQ_DTYPE_BF16) || ((uintptr_t)out_final & 15)) return TQ_ERR_ARG;
-        bytes = (size_t)batch * gather->q_heads_total * TQ_D * 2;
+        if (gather->q_heads_total % gather->world) return TQ_ERR_ARG;
     }
-    return tq_launch_gather_wait(gather, ctx->error_flag, ctx->wait_limit_ms, bytes, out_final, (cudaStream_t)stream);
+    return tq_launch_gather_wait(gather, ctx->error_flag, ctx->wait_limit_ms, batch, 2, out_final, (cudaStream_t)stream);
 }
 
 extern "C" int32_t tq_set_wait_limit_ms(tq_ctx *ctx, int32_t limit_ms) {

@@ -46,7 +46,7 @@ class CacheDesc(C.Structure):
         ("k_codes", C.c_void_p), ("k_norms", C.c_void_p), ("k_signs", C.c_void_p),
         ("k_rnorms", C.c_void_p), ("v_codes", C.c_void_p), ("v_norms", C.c_void_p),
         ("batch", C.c_int32), ("kv_heads", C.c_int32), ("capacity", C.c_int32),
-        ("stride_b", C.c_int64), ("stride_h", C.c_int64),
+        ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("seq_start", C.c_void_p),
     ]
 
 
@@ -64,7 +64,7 @@ class GatherDesc(C.Structure):
     _fields_ = [
         ("world", C.c_int32), ("rank", C.c_int32), ("q_heads_total", C.c_int32), ("seq", C.c_uint32),
         ("out", C.c_void_p * TQ_MAX_PEERS), ("out_stride", C.c_int64), ("flags", C.c_void_p * TQ_MAX_PEERS),
-        ("counter", C.c_void_p), ("seq_dev", C.c_void_p),
+        ("counter", C.c_void_p), ("seq_dev", C.c_void_p), ("out_local_only", C.c_int32),
     ]
 
 

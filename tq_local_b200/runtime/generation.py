@@ -29,6 +29,7 @@ from tq_local_b200.runtime.memory_accounting import (
 )
 from tq_local_b200.runtime.packed_qmse_cache import (
     _auto_norm_threshold,
+    is_left_padding_mask,
     build_packed_mse_cache,
     build_streaming_prefill_cache,
     packed_cache_storage_breakdown,
@@ -162,17 +163,16 @@ def _prefill_in_row_blocks(model, inputs, packed_cache, threshold: float, rows_p
     return torch.cat(last, dim=0)
 
 
-def _static_decode_eligible(model, packed_cache, mask) -> bool:
-    """The replayable (CUDA-graph) decode loop needs every layer packed with quantised appends,
-    a tensor-core shape, one GPU, and no padding in the prompt."""
+def _static_decode_eligible(model, packed_cache) -> bool:
+    """The replayable (CUDA-graph) decode loop needs every layer packed with quantised appends and
+    a tensor-core shape.  (A left-padded prompt is fine: the layers carry the per-row start
+    offsets that ``bind_attention_mask`` derived from the prompt's mask.)"""
     import torch
 
     if packed_cache is None or not torch.cuda.is_available():
         return False
     q_heads = int(getattr(model.config, "num_attention_heads", 0))
-    if not q_heads or not all(layer.supports_static_decode(q_heads) for layer in packed_cache.layers):
-        return False
-    return mask is None or bool(mask.all())
+    return bool(q_heads) and all(layer.supports_static_decode(q_heads) for layer in packed_cache.layers)
 
 
 class RecordedDecoder:
@@ -378,6 +378,16 @@ def greedy_decode_with_prefill_cache(
                 torch.cuda.synchronize()
             quant_seconds += time.monotonic() - t0
 
+            # Padding: a decoder-only batch is padded on the left.  The packed layers take the
+            # per-row start offset from the prompt's mask once (it does not change while decoding).
+            prompt_mask = inputs.get("attention_mask")
+            if prompt_mask is not None and not bool(prompt_mask.all()):
+                if not is_left_padding_mask(prompt_mask):
+                    raise ValueError("TurboQuant attends left-padded batches only: every row of attention_mask "
+                                     "must be zeros followed by ones (tokenizer.padding_side = 'left')")
+                for layer in packed_cache.layers:
+                    layer.bind_attention_mask(prompt_mask)
+
             from tq_local_b200.adapters.transformers import enable_turboquant_attention
 
             old_impl = enable_turboquant_attention(model, packed_cache)
@@ -395,7 +405,7 @@ def greedy_decode_with_prefill_cache(
             if use_cuda_graph is None:
                 use_cuda_graph = variant == "qmse_packed" and max_new_tokens > 8
             graphed = False
-            if use_cuda_graph and max_new_tokens > 1 and _static_decode_eligible(model, packed_cache, mask):
+            if use_cuda_graph and max_new_tokens > 1 and _static_decode_eligible(model, packed_cache):
                 if eos_tensor is None or not bool(torch.isin(next_token, eos_tensor).any(dim=-1).all()):
                     generated.append(_graphed_greedy_steps(model, cache, next_token, max_new_tokens - 1, eos_tensor))
                 graphed = True

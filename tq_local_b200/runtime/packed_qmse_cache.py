@@ -70,6 +70,29 @@ class PackedQJL:
                    + self.residual_norms.numel() * self.residual_norms.element_size())
 
 
+def leading_masked_tokens(mask: torch.Tensor) -> torch.Tensor:
+    """Per batch row, how many key positions are masked before the first kept one (int32 [B], no
+    host synchronisation).  ``mask`` is [B, S] (non-zero / True = keep) or [B, 1, Sq, S] (bool
+    keep-mask, or additive float where kept positions are 0 and masked ones very negative; the
+    last query row is looked at)."""
+    if mask.dim() == 4:
+        row = mask[:, 0, -1, :]
+        keep = row if row.dtype == torch.bool else row > -1.0
+    elif mask.dim() == 2:
+        keep = mask if mask.dtype == torch.bool else mask != 0
+    else:
+        raise ValueError(f"expected a [B, S] or [B, 1, Sq, S] attention mask, got {tuple(mask.shape)}")
+    return (torch.cumsum(keep.to(torch.int32), dim=-1) == 0).sum(dim=-1, dtype=torch.int32).contiguous()
+
+
+def is_left_padding_mask(mask: torch.Tensor) -> bool:
+    """Whether a 2-D mask [B, S] is zeros followed by ones in every row with at least one kept
+    position (one host synchronisation; the generation loop asks once per call)."""
+    keep = mask if mask.dtype == torch.bool else mask != 0
+    seen = torch.cumsum(keep.to(torch.int32), dim=-1) > 0
+    return bool(((seen == keep).all(dim=-1) & keep.any(dim=-1)).all())
+
+
 class _GrowingDense:
     """Dense [B, H, T, D] buffer with spare capacity: amortised O(1) append along T."""
 
@@ -147,6 +170,7 @@ class PackedMSELayer(CacheLayerMixin):
         self._kv_heads_total: int | None = None
         self._static_pos: torch.Tensor | None = None  # see begin_static_decode
         self._stream_threshold: float | None = None   # see build_streaming_prefill_cache
+        self._mask_bound = False                      # see bind_attention_mask
         self._window: tuple[int, int] | None = None   # (first batch row, total batch) of a prompt pass run in row blocks
         self._window_dense: bool | None = None        # the norm-guard decision of such a pass (taken on its first block)
         self._window_norm = [0.0, 0]                  # running (sum of block means x rows, rows) of such a pass
@@ -390,12 +414,35 @@ class PackedMSELayer(CacheLayerMixin):
         return torch.cat((pk, dk), dim=-2), torch.cat((pv, dv), dim=-2)
 
     # ---------------------------------------------------------------- attention
-    def attend(self, query_states: torch.Tensor) -> torch.Tensor:
+    def bind_attention_mask(self, mask: torch.Tensor | None) -> None:
+        """Fix which cached tokens every batch row attends for the decode steps that follow: ``mask``
+        is the prompt's 2-D mask [B, S] (1 / True = attend) of a LEFT-padded batch, or a 4-D mask
+        [B, 1, Sq, Skv] (bool keep-mask or additive float) of the same shape of padding; row ``b``
+        then attends tokens from its first kept position on.  ``None`` removes the restriction.
+        While a mask is bound, per-call masks handed to ``attend`` are not looked at (the padding
+        of a batch does not change during generation)."""
+        if self.store is None or self._force_dense:
+            return
+        if mask is None:
+            self.store.set_seq_start(None)
+            self._mask_bound = False
+            return
+        self.store.set_seq_start(leading_masked_tokens(mask))
+        self._mask_bound = True
+
+    def attend(self, query_states: torch.Tensor, attention_mask: torch.Tensor | None = None) -> torch.Tensor:
         """Decode attention of ``query_states`` [B, Hq, Sq, D] over this layer's cache, returning
         [B, Hq, Sq, D] in the query dtype.  ``Sq > 1`` is served one query position at a
-        time with causal visibility (the new tokens were appended before attention)."""
+        time with causal visibility (the new tokens were appended before attention).  An
+        ``attention_mask`` (see ``bind_attention_mask`` for the accepted forms) restricts every
+        row to the tokens after its left padding, which is what the reference's chunked path does
+        by adding the mask to its logits (attention.py:253-255,278-283)."""
         if self.store is None or self._force_dense:
             raise RuntimeError("attend() needs a packed (non-dense) layer")
+        if attention_mask is not None and not self._mask_bound:
+            self.store.set_seq_start(leading_masked_tokens(attention_mask))
+        elif attention_mask is None and not self._mask_bound and self.store._seq_start is not None:
+            self.store.set_seq_start(None)
         if self._static_pos is not None:
             k_new, v_new = self._static_kv
             # (sharded: the combine kernel writes every rank's gathered buffer, the result is complete)
@@ -417,6 +464,27 @@ class PackedMSELayer(CacheLayerMixin):
                                              tail_v=tail_v[:, :, :n_tail - behind])
             outs.append(out)
         out = outs[0] if sq == 1 else torch.cat(outs, dim=2)
+        return self.shard.gather_heads(out)
+
+    def attend_with_new_tokens(self, query_states: torch.Tensor, new_key: torch.Tensor, new_value: torch.Tensor,
+                               attention_mask: torch.Tensor | None = None) -> torch.Tensor:
+        """``attend`` over the cache plus ``new_key`` / ``new_value`` [B, Hkv, T, D], tokens that are
+        not stored (and are not stored by this call): they are attended un-quantised after the
+        cached ones, as the reference's chunked path does with its ``new_key`` argument
+        (attention.py:286-297).  Every query position sees all T new tokens."""
+        if self.store is None or self._force_dense:
+            raise RuntimeError("attend_with_new_tokens() needs a packed (non-dense) layer")
+        if attention_mask is not None and not self._mask_bound:
+            self.store.set_seq_start(leading_masked_tokens(attention_mask))
+        q_local = self.shard.local_q(query_states, self._kv_heads_total)
+        tail_k, tail_v = self.shard.local_kv(new_key), self.shard.local_kv(new_value)
+        if self._dense_k.length:
+            tail_k = torch.cat((self._dense_k.view(), tail_k), dim=2)
+            tail_v = torch.cat((self._dense_v.view(), tail_v), dim=2)
+        tail_k, tail_v = tail_k.to(query_states.dtype), tail_v.to(query_states.dtype)
+        outs = [self.store.decode_attn(q_local[:, :, i:i + 1], tail_k=tail_k, tail_v=tail_v)
+                for i in range(int(query_states.shape[2]))]
+        out = outs[0] if len(outs) == 1 else torch.cat(outs, dim=2)
         return self.shard.gather_heads(out)
 
     # ---------------------------------------------------------------- dequantisation

@@ -35,6 +35,7 @@ class PackedStore:
         self.codec = codec
         self.batch, self.kv_heads = int(batch), int(kv_heads)
         self.length = 0
+        self._seq_start: torch.Tensor | None = None  # see set_seq_start
         self._alloc(max(8, _round_up(int(capacity), 8)))
         self._workspace: torch.Tensor | None = None
         self._step_plan = None
@@ -60,9 +61,21 @@ class PackedStore:
             self.k_rnorms.data_ptr() if self.k_rnorms is not None else None,
             self.v_codes.data_ptr(), self.v_norms.data_ptr(),
             b, h, capacity, h * capacity, capacity,
+            self._seq_start.data_ptr() if self._seq_start is not None else None,
         )
         self._desc_ref = C.byref(self._desc)
         self._step_plan = None
+
+    def set_seq_start(self, seq_start: torch.Tensor | None) -> None:
+        """Per-row first attended token (int32 [batch] on the cache's device): the decode calls then
+        attend tokens ``[seq_start[b], length)`` of batch entry ``b`` - a left-padded batch.  ``None``
+        (the default) attends every row from token 0."""
+        if seq_start is not None:
+            if seq_start.dtype != torch.int32 or seq_start.device != self.codec.device or \
+                    tuple(seq_start.shape) != (self.batch,) or not seq_start.is_contiguous():
+                raise ValueError(f"seq_start must be a contiguous int32 tensor [{self.batch}] on {self.codec.device}")
+        self._seq_start = seq_start
+        self._desc.seq_start = seq_start.data_ptr() if seq_start is not None else None
 
     def streams(self) -> list[torch.Tensor]:
         return [t for t in (self.k_codes, self.k_norms, self.k_signs, self.k_rnorms, self.v_codes, self.v_norms)
@@ -128,7 +141,7 @@ class PackedStore:
         ptr = lambda t: None if t is None else t[b0:].data_ptr()
         desc = ffi.CacheDesc(ptr(self.k_codes), ptr(self.k_norms), ptr(self.k_signs), ptr(self.k_rnorms),
                              ptr(self.v_codes), ptr(self.v_norms), kb, self.kv_heads, self.capacity,
-                             self.kv_heads * self.capacity, self.capacity)
+                             self.kv_heads * self.capacity, self.capacity, None)
         kd, vd = dense_desc(k), dense_desc(v)
         with torch.cuda.device(self.codec.device):
             ffi.check(ffi.lib().tq_pack(self.codec.handle, C.byref(kd), C.byref(vd), n, C.byref(desc), pos0,
@@ -257,20 +270,26 @@ class PackedStore:
     def decode_step_host_gather(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, out: torch.Tensor,
                                 gather, splits: int | None = None) -> torch.Tensor:
         """``decode_step_host`` for a KV-head shard: ``q`` / ``k_new`` / ``v_new`` hold this rank's
-        heads, ``out`` [B, Hq_total, 1, 128] receives the gathered output of all ranks.  All four
-        must be pinned host tensors; ``gather`` is a host-sequenced ``PeerGather``."""
+        heads, ``out`` [B, Hq_total, 1, 128] receives the gathered output of all ranks, or, when it
+        has this rank's shape [B, Hq, 1, 128], this rank's heads only (the device-side gathered
+        buffer ``gather.last_view()`` is complete either way).  All four must be pinned host
+        tensors; ``gather`` is a host-sequenced ``PeerGather``."""
         for t in (q, k_new, v_new, out):
             if t.device.type != "cpu" or not t.is_contiguous() or not t.is_pinned():
                 raise ValueError("decode_step_host_gather takes contiguous pinned host tensors")
         b, hq = int(q.shape[0]), int(q.shape[1])
         if b != self.batch or k_new.shape[1] != self.kv_heads or q.dtype != k_new.dtype or out.dtype != q.dtype:
             raise ValueError("shape or dtype mismatch")
-        if tuple(out.shape) != tuple(gather.shape):
-            raise ValueError(f"out must have the gathered shape {gather.shape}")
+        local_shape = (b, hq, 1, 128)
+        if tuple(out.shape) not in (tuple(gather.shape), local_shape):
+            raise ValueError(f"out must have the gathered shape {gather.shape} or this rank's shape {local_shape}")
         self.reserve(self.length + 1)
         splits = self.suggest_splits(self.length + 1) if splits is None else int(splits)
         ws = self._get_workspace(hq, splits)
         desc, _ = gather.next_desc()
+        # (an `out` of this rank's shape asks for this rank's heads only; every rank's gathered
+        # device buffer is complete either way)
+        desc.out_local_only = int(tuple(out.shape) == local_shape and tuple(gather.shape) != local_shape)
         with torch.cuda.device(self.codec.device):
             ffi.check(ffi.lib().tq_decode_step_host_gather(
                 self.codec.handle, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), tq_dtype(q.dtype), hq,

@@ -174,6 +174,10 @@ class PeerGather:
         d.seq = self.seq
         return d, self._views[self.seq & 1]
 
+    def last_view(self) -> torch.Tensor:
+        """This rank's gathered output [batch, q_heads_total, 1, 128] of the latest host-numbered step."""
+        return self._views[self.seq & 1]
+
     def static_desc(self):
         """Descriptor for steps numbered on the device (the same for every step)."""
         if self.seq_dev is None:

@@ -633,6 +633,8 @@ def model_decode_run(torch, dist, model, w, shard, world, rank, local_rank, dev,
             cache = Cache(layers=layers)
             first = torch.randint(0, w["vocab"], (B, 1), device=dev, generator=gen)
         dense_layers = sum(1 for layer in layers if layer._force_dense)
+        for layer in layers:
+            layer.bind_attention_mask(None, lock=True)  # no padding: the layers need not look at per-call masks
         old_impl = enable_turboquant_attention(model, cache)
         sampler = ClockSampler(local_rank)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

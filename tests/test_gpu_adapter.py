@@ -327,12 +327,12 @@ def test_attention_masks_on_the_packed_path():
         want = O.attend_rotated_space(q[b:b + 1], mine, 4)
         assert float((masked[0][b:b + 1].float().cpu() - want).abs().max() / want.abs().max()) <= 2e-3 + 2.0 ** -9
     # un-stored new tokens are attended dense, after the cache, and nothing is stored
-    before = [t.clone() for t in s.streams()]
+    before = [t[:, :, :N].clone() for t in s.streams()]
     got = chunked_turboquant_attention(qd, layer, new_key=k[:, :, N:].cuda(), new_value=v[:, :, N:].cuda(), n_kv_groups=4)
     want = s.decode_attn(qd, tail_k=k[:, :, N:].cuda(), tail_v=v[:, :, N:].cuda())
     assert torch.equal(got, want) and s.length == N and not torch.equal(got, plain)
     for a, b_ in zip(before, s.streams()):
-        assert torch.equal(a, b_)
+        assert torch.equal(a, b_[:, :, :N])
     # a bound mask stays in force for calls without one (the generation loop binds the prompt's mask)
     layer.bind_attention_mask(m2.cuda())
     assert torch.equal(layer.attend(qd), masked[0])

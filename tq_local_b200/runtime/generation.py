@@ -381,12 +381,13 @@ def greedy_decode_with_prefill_cache(
             # Padding: a decoder-only batch is padded on the left.  The packed layers take the
             # per-row start offset from the prompt's mask once (it does not change while decoding).
             prompt_mask = inputs.get("attention_mask")
-            if prompt_mask is not None and not bool(prompt_mask.all()):
-                if not is_left_padding_mask(prompt_mask):
-                    raise ValueError("TurboQuant attends left-padded batches only: every row of attention_mask "
-                                     "must be zeros followed by ones (tokenizer.padding_side = 'left')")
-                for layer in packed_cache.layers:
-                    layer.bind_attention_mask(prompt_mask)
+            if prompt_mask is not None and bool(prompt_mask.all()):
+                prompt_mask = None
+            if prompt_mask is not None and not is_left_padding_mask(prompt_mask):
+                raise ValueError("TurboQuant attends left-padded batches only: every row of attention_mask "
+                                 "must be zeros followed by ones (tokenizer.padding_side = 'left')")
+            for layer in packed_cache.layers:
+                layer.bind_attention_mask(prompt_mask, lock=True)
 
             from tq_local_b200.adapters.transformers import enable_turboquant_attention
 

@@ -414,21 +414,19 @@ class PackedMSELayer(CacheLayerMixin):
         return torch.cat((pk, dk), dim=-2), torch.cat((pv, dv), dim=-2)
 
     # ---------------------------------------------------------------- attention
-    def bind_attention_mask(self, mask: torch.Tensor | None) -> None:
+    def bind_attention_mask(self, mask: torch.Tensor | None, lock: bool | None = None) -> None:
         """Fix which cached tokens every batch row attends for the decode steps that follow: ``mask``
         is the prompt's 2-D mask [B, S] (1 / True = attend) of a LEFT-padded batch, or a 4-D mask
         [B, 1, Sq, Skv] (bool keep-mask or additive float) of the same shape of padding; row ``b``
         then attends tokens from its first kept position on.  ``None`` removes the restriction.
-        While a mask is bound, per-call masks handed to ``attend`` are not looked at (the padding
-        of a batch does not change during generation)."""
+        While the binding is locked (``lock``; default: locked exactly when a mask is given),
+        per-call masks handed to ``attend`` are not looked at: the padding of a batch does not
+        change during generation, so a generation loop binds once - also for an unpadded batch -
+        and spares every layer and step the look at the mask the model passes down."""
         if self.store is None or self._force_dense:
             return
-        if mask is None:
-            self.store.set_seq_start(None)
-            self._mask_bound = False
-            return
-        self.store.set_seq_start(leading_masked_tokens(mask))
-        self._mask_bound = True
+        self.store.set_seq_start(None if mask is None else leading_masked_tokens(mask))
+        self._mask_bound = (mask is not None) if lock is None else bool(lock)
 
     def attend(self, query_states: torch.Tensor, attention_mask: torch.Tensor | None = None) -> torch.Tensor:
         """Decode attention of ``query_states`` [B, Hq, Sq, D] over this layer's cache, returning
@@ -439,10 +437,11 @@ class PackedMSELayer(CacheLayerMixin):
         by adding the mask to its logits (attention.py:253-255,278-283)."""
         if self.store is None or self._force_dense:
             raise RuntimeError("attend() needs a packed (non-dense) layer")
-        if attention_mask is not None and not self._mask_bound:
-            self.store.set_seq_start(leading_masked_tokens(attention_mask))
-        elif attention_mask is None and not self._mask_bound and self.store._seq_start is not None:
-            self.store.set_seq_start(None)
+        if not self._mask_bound and self._static_pos is None:  # (a recorded step keeps the offsets it was given)
+            if attention_mask is not None:
+                self.store.set_seq_start(leading_masked_tokens(attention_mask))
+            elif self.store._seq_start is not None:
+                self.store.set_seq_start(None)
         if self._static_pos is not None:
             k_new, v_new = self._static_kv
             # (sharded: the combine kernel writes every rank's gathered buffer, the result is complete)

@@ -203,10 +203,12 @@ int32_t tq_key_norm_sum(const tq_dense_desc *k, int32_t batch, int32_t heads, in
  * single-GPU).  Rank r serves kv_heads / world KV heads and their query heads; the only exchange
  * per decode step is the per-head attention outputs.  tq_decode_attn_gather fuses that exchange
  * into the combine kernel: every block stores its finished rows straight into the gathered-output
- * buffer of EVERY rank (plain stores to peer memory over NVLink), the last block of a rank raises
- * that rank's flag in every peer, and tq_gather_wait (one small kernel, stream-ordered before the
- * consumer of the gathered output) waits - with a time limit, reporting through tq_device_status
- * (5) instead of hanging - until all ranks' flags show the step's sequence number.
+ * buffer of EVERY rank (plain stores to peer memory over NVLink) and then, after a system-scope
+ * fence, adds the number of rows it stored to this rank's word in every rank's flag block.
+ * tq_gather_wait (one small kernel, stream-ordered before the consumer of the gathered output)
+ * waits - with a time limit, reporting through tq_device_status (5) instead of hanging - until
+ * every rank's word has reached step * batch * (q_heads_total / world): all rows of the step are
+ * in place.  The words only ever grow, so a descriptor serves steps 1, 2, 3, ... of ONE shape.
  *
  * Buffers come from tq_peer_buffer_create (device memory that other processes on the box can
  * map): exchange the 64-byte handles by any host-side means and map the peers' buffers with
@@ -221,11 +223,11 @@ struct tq_gather_desc {
     uint32_t seq;                   /* step sequence number: 1, 2, 3, ... (the same on all ranks); unused with seq_dev */
     void *out[TQ_MAX_PEERS];        /* out[r]: the first of rank r's two gathered-output buffers (as mapped here) */
     int64_t out_stride;             /* bytes from a rank's first buffer to its second; step s uses buffer s & 1 */
-    uint32_t *flags[TQ_MAX_PEERS];  /* flags[r]: rank r's flag block (as mapped here); entry [rank] is ours */
-    uint32_t *counter;              /* local scratch word, zero between calls */
+    uint32_t *flags[TQ_MAX_PEERS];  /* flags[r]: rank r's flag block (as mapped here); word [rank] counts OUR rows there */
+    uint32_t *counter;              /* local scratch word, zero between calls (used by tq_gather_wait with seq_dev) */
     uint32_t *seq_dev;              /* optional local device word holding the LAST completed sequence number
-                                       (zero-initialised): the step then takes its number from the device, the
-                                       combine kernel advances it, and a recorded launch sequence can be replayed */
+                                       (zero-initialised): the step then takes its number from the device,
+                                       tq_gather_wait advances it, and a recorded launch sequence can be replayed */
     int32_t out_local_only;         /* non-zero: the copy that tq_gather_wait / tq_decode_step_host_gather make for the
                                        caller (out_final / out_host) holds only THIS rank's heads
                                        [batch, q_heads_total / world, 128] instead of the whole gathered output; the

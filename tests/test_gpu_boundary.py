@@ -54,7 +54,7 @@ def test_gather_wait_runs_out_reports_status_5_and_returns(setup_golden):
     codec = make_codec(4, True, setup_golden)
     codec.set_wait_limit_ms(50)
     B, Hq = 1, 8
-    desc, keep = _local_gather_desc(q_heads_total=Hq, seq=7, batch=B)  # flags are all zero: step 7 never arrives
+    desc, keep = _local_gather_desc(q_heads_total=Hq, seq=7, batch=B)  # the row counts are all zero: step 7 never arrives
     final = torch.full((B, Hq, 1, 128), 3.0, dtype=torch.bfloat16, device="cuda")
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     t0 = time.perf_counter()
@@ -83,7 +83,7 @@ def test_gather_wait_passes_when_the_flag_is_there(setup_golden):
     codec = make_codec(4, True, setup_golden)
     codec.set_wait_limit_ms(50)
     desc, (out, flags, counter) = _local_gather_desc(q_heads_total=8, seq=2, batch=1)
-    flags[0] = 2
+    flags[0] = 2 * 1 * 8  # this rank's rows of steps 1 and 2 (batch 1 x 8 heads each) are in
     out[0].fill_(1.5)  # step 2 uses buffer 2 & 1 = 0
     final = torch.zeros(1, 8, 1, 128, dtype=torch.bfloat16, device="cuda")
     rc = ffi.lib().tq_gather_wait(codec.handle, C.byref(desc), 1, tq_dtype(torch.bfloat16), final.data_ptr(),

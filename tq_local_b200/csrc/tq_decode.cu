@@ -407,17 +407,14 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
             uint4 *dst = reinterpret_cast<uint4 *>(static_cast<char *>(a.gather_out[p]) + buf + dst0 * sizeof(T));
             dst[i] = reinterpret_cast<const uint4 *>(&s_o[0][0])[i];
         }
-        // the rank's last block tells every peer that this rank's rows of the step are in place
+        // Every block reports its own rows: after a system-scope fence (cumulative over the block's
+        // stores, which the barrier ordered before it) it adds its row count to this rank's word in
+        // every peer's flag block.  A peer has all of this rank's rows of step s once that word has
+        // reached s * (rows per step); no block waits for another, no counter round trip.
         __syncthreads();
         if (tid == 0) {
-            __threadfence_system();  // (cumulative: covers the block's stores ordered before the barrier)
-            if (atomicAdd(a.gather_counter, 1u) == gridDim.x - 1) {  // every block has read the step number
-                *a.gather_counter = 0;
-                __threadfence_system();
-                for (int p = 0; p < a.gather_world; ++p)
-                    *reinterpret_cast<volatile unsigned *>(a.gather_flags[p] + a.gather_rank) = seq;
-                if (a.gather_seq_ptr) *const_cast<unsigned *>(a.gather_seq_ptr) = seq;
-            }
+            __threadfence_system();
+            for (int p = 0; p < a.gather_world; ++p) atomicAdd_system(a.gather_flags[p] + a.gather_rank, (unsigned)n_heads);
         }
     }
 }
@@ -428,40 +425,53 @@ __device__ __forceinline__ unsigned long long tq_global_ns() {
     return t;
 }
 
-// Waits until the flags of all ranks show the step's sequence number (written by the peers'
-// combine kernels), for at most `limit_ns` nanoseconds of the GPU's wall clock; a wait that
-// runs out sets the status word to 5 and the kernel returns without copying.  Otherwise,
-// optionally, every block copies its slice of this rank's gathered buffer of the step to `dst`.
-__global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned seq_arg, const unsigned *seq_ptr,
-                                      int *error_flag, unsigned long long limit_ns, const uint4 *src0, long long stride,
-                                      uint4 *dst, size_t n16, size_t row_len16, size_t row_stride16, size_t src_off16) {
-    // A step numbered on the device gets its number from the combine kernel's last block, so that
-    // kernel has to be complete before the number is read; a host-numbered step may start polling early.
+// Waits until every rank's word of this rank's flag block has reached step * rows_per_step (the
+// peers' combine kernels add the rows they have stored), for at most `limit_ns` nanoseconds of the
+// GPU's wall clock; a wait that runs out sets the status word to 5 and the kernel returns without
+// copying.  Otherwise, optionally, every block copies its slice of this rank's gathered buffer of
+// the step to `dst`.  A step numbered on the device (seq_ptr: the number of the last completed
+// step) is number *seq_ptr + 1; the last block to finish stores it back, after every block has
+// read it.
+__global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned seq_arg, unsigned *seq_ptr,
+                                      unsigned rows_per_step, unsigned *counter, int *error_flag,
+                                      unsigned long long limit_ns, const uint4 *src0, long long stride, uint4 *dst,
+                                      size_t n16, size_t row_len16, size_t row_stride16, size_t src_off16) {
+    // (the combine kernel of a device-numbered step reads the same word: it must be complete
+    // before this kernel may advance it; a host-numbered step may start polling early)
     if (seq_ptr) tq_grid_dependency_wait();
-    const unsigned seq = seq_ptr ? *seq_ptr : seq_arg;
+    const unsigned seq = seq_ptr ? *seq_ptr + 1u : seq_arg;
+    const unsigned target = seq * rows_per_step;
     __shared__ int s_failed;
     if (threadIdx.x == 0) s_failed = 0;
     __syncthreads();
     if ((int)threadIdx.x < world) {
         const unsigned long long t0 = tq_global_ns();
         const volatile unsigned *f = flags + threadIdx.x;
-        while ((int)(*f - seq) < 0) {  // (flags only grow; a peer may already be one step ahead)
-            if (tq_global_ns() - t0 > limit_ns) {
+        unsigned polls = 0;
+        while ((int)(*f - target) < 0) {  // (the words only grow; a peer may already be a step ahead)
+            if ((++polls & 63u) == 0 && tq_global_ns() - t0 > limit_ns) {
                 atomicExch(error_flag, 5);
                 s_failed = 1;
                 break;
             }
-            __nanosleep(200);
         }
         __threadfence_system();
     }
     __syncthreads();
-    if (!dst || s_failed) return;
-    // dst is dense; piece i of it is piece (i % row_len16) of source row (i / row_len16), rows being
-    // row_stride16 apart and starting src_off16 into the buffer (a whole-buffer copy is one row)
-    const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(src0) + ((seq & 1u) ? stride : 0));
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
-        dst[i] = src[(i / row_len16) * row_stride16 + src_off16 + i % row_len16];
+    if (dst && !s_failed) {
+        // dst is dense; piece i of it is piece (i % row_len16) of source row (i / row_len16), rows being
+        // row_stride16 apart and starting src_off16 into the buffer (a whole-buffer copy is one row)
+        const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(src0) + ((seq & 1u) ? stride : 0));
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+            dst[i] = src[(i / row_len16) * row_stride16 + src_off16 + i % row_len16];
+    }
+    if (seq_ptr && !s_failed) {
+        __syncthreads();
+        if (threadIdx.x == 0 && atomicAdd(counter, 1u) == gridDim.x - 1) {
+            *counter = 0;
+            *seq_ptr = seq;
+        }
+    }
 }
 
 // The decode kernels run with the largest shared-memory carve-out.  The small kernels around
@@ -581,7 +591,8 @@ int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limi
     // rank's flag, this rank's included.
     cudaError_t e = tq_launch_kernel(tq_gather_wait_kernel, dim3(blocks < 1 ? 1 : blocks), dim3(256), 0, stream, true,
                                      (const unsigned *)g->flags[g->rank], (int)g->world, (unsigned)g->seq,
-                                     (const unsigned *)g->seq_dev, error_flag,
+                                     (unsigned *)g->seq_dev, (unsigned)(batch * (g->q_heads_total / g->world)),
+                                     (unsigned *)g->counter, error_flag,
                                      (unsigned long long)(limit_ms < 1 ? 1 : limit_ms) * 1000000ull,
                                      reinterpret_cast<const uint4 *>(g->out[g->rank]), (long long)g->out_stride,
                                      reinterpret_cast<uint4 *>(out_final), n16, row_len16, row_stride16, src_off16);

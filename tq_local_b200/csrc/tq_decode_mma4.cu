@@ -714,7 +714,7 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     c.gather_world = 0;
     if (gather) {
         c.gather_world = gather->world, c.gather_rank = gather->rank, c.gather_heads_total = gather->q_heads_total;
-        c.gather_seq = gather->seq, c.gather_counter = gather->counter;
+        c.gather_seq = gather->seq;
         c.gather_seq_ptr = gather->seq_dev, c.gather_out_stride = gather->out_stride;
         for (int p = 0; p < TQ_MAX_PEERS; ++p) {
             c.gather_out[p] = p < gather->world ? gather->out[p] : nullptr;

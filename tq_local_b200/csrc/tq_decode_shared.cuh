@@ -15,14 +15,13 @@ struct CombineArgs {
     const int *len_ptr;
     int len_add, capacity, plan_rows, plan_ctas, plan_step;
     // Peer gather (KV-head sharding): when gather_world > 0 the finished rows go to every rank's
-    // gathered buffer instead of `out`, and the last block raises this rank's flag in every peer.
+    // gathered buffer instead of `out`, and every block adds its row count to this rank's word in every peer.
     int gather_world, gather_rank, gather_heads_total;
     unsigned gather_seq;
-    const unsigned *gather_seq_ptr;  // when set, the step number is *gather_seq_ptr + 1 and the last block stores it back
+    const unsigned *gather_seq_ptr;  // when set, the step number is *gather_seq_ptr + 1 (the wait kernel stores it back)
     long long gather_out_stride;     // bytes between a rank's two gathered buffers (step s uses buffer s & 1)
     void *gather_out[TQ_MAX_PEERS];
     unsigned *gather_flags[TQ_MAX_PEERS];
-    unsigned *gather_counter;
     const float *rot_v;  // R_v[d][e]
     const void *q;       // original-dtype query, for the dense tail
     void *out;

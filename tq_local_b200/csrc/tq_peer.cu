@@ -77,10 +77,8 @@ extern "C" int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, int
     if (!ctx) return TQ_ERR_ARG;
     int rc = tq_check_gather(gather);
     if (rc) return rc;
-    if (out_final) {
-        if (batch <= 0 || (dtype != TQ_DTYPE_F16 && dtype != TQ_DTYPE_BF16) || ((uintptr_t)out_final & 15)) return TQ_ERR_ARG;
-        if (gather->q_heads_total % gather->world) return TQ_ERR_ARG;
-    }
+    if (batch <= 0 || gather->q_heads_total % gather->world) return TQ_ERR_ARG;
+    if (out_final && ((dtype != TQ_DTYPE_F16 && dtype != TQ_DTYPE_BF16) || ((uintptr_t)out_final & 15))) return TQ_ERR_ARG;
     return tq_launch_gather_wait(gather, ctx->error_flag, ctx->wait_limit_ms, batch, 2, out_final, (cudaStream_t)stream);
 }
 

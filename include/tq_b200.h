@@ -262,6 +262,27 @@ int32_t tq_decode_step_host_gather(tq_ctx *ctx, const void *q_host, const void *
 int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, int32_t batch, int32_t dtype, void *out_final,
                        tq_stream stream);
 
+/* ---- Sequence split: more ranks than KV heads (no counterpart in the reference).  `parts` ranks
+ * share a group of KV heads; rank r belongs to group r / parts and is part r % parts of it, holding
+ * a disjoint part of the cached tokens of the group's heads (which tokens is up to the caller:
+ * attention does not depend on their order).  Per step every rank calls tq_decode_attn_parts with
+ * the group's query heads q [batch, q_heads, 128] (the same on every part of a group) and ITS
+ * tokens: the kernels attend them and store the unfinished partial (max, sum, acc[128], fp32) of
+ * every row into every rank's partial-exchange buffer - the two buffers of tq_gather_desc.out,
+ * here of tq_parts_exchange_bytes(batch, q_heads_total, parts) bytes each, with
+ * q_heads_total = q_heads * world / parts.  seq_len may be 0 (a part that holds no token yet).
+ * tq_decode_parts_finish then waits (bounded, status 5) until the partials of all ranks are in,
+ * merges the parts of every row, un-rotates and writes out [batch, q_heads_total, 128] - on every
+ * rank, so no second exchange is needed.  heads_per_block (1..8, a divisor of q_heads_total) only
+ * groups the finishing kernel's work.  Host-numbered steps only (gather->seq_dev must be NULL);
+ * 16-bit dtypes; a descriptor serves steps of one shape. */
+size_t tq_parts_exchange_bytes(int32_t batch, int32_t q_heads_total, int32_t parts);
+int32_t tq_decode_attn_parts(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
+                             const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits, void *workspace,
+                             size_t workspace_bytes, const tq_gather_desc *gather, int32_t parts, tq_stream stream);
+int32_t tq_decode_parts_finish(tq_ctx *ctx, const tq_gather_desc *gather, int32_t batch, int32_t dtype,
+                               int32_t parts, int32_t heads_per_block, void *out, tq_stream stream);
+
 /* Decode attention for callers that cannot allocate (no counterpart in the reference).
  * Same computation and arguments as tq_decode_attn without a dense tail, but the scratch
  * lives in an 8 MiB array built into the library instead of a caller workspace: use it from

@@ -259,7 +259,7 @@ extern "C" int32_t tq_decode_attn_f32out(tq_ctx *ctx, const void *q, int32_t q_d
                                          void *workspace, size_t workspace_bytes, float *out, tq_stream stream) {
     if (q_dtype != TQ_DTYPE_F16 && q_dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
     if (seq_len <= 0) return TQ_ERR_ARG;
-    const TqStepExtras extras = {nullptr, nullptr, nullptr, out};
+    const TqStepExtras extras = {nullptr, nullptr, nullptr, out, 0};
     return decode_attn_impl(ctx, q, q_dtype, q_heads, cache, seq_len, nullptr, nullptr, 0, n_splits, workspace,
                             workspace_bytes, out, &extras, stream);
 }
@@ -322,7 +322,7 @@ extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const vo
     tq_dense_desc kd = {d_k, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
     tq_dense_desc vd = {d_v, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
     TqPackArgs append;
-    TqStepExtras extras = {nullptr, nullptr, nullptr, nullptr};
+    TqStepExtras extras = {nullptr, nullptr, nullptr, nullptr, 0};
     if (dtype != TQ_DTYPE_F32) {
         // the tensor-core decode path encodes the new token in its own query-preparation launch
         tq_fill_pack_args(ctx, &kd, &vd, 1, cache, pos, &append);
@@ -361,7 +361,7 @@ extern "C" int32_t tq_decode_step_host_gather(tq_ctx *ctx, const void *q_host, c
     tq_dense_desc vd = {d_v, dtype, (int64_t)cache->kv_heads * TQ_D, TQ_D, TQ_D};
     TqPackArgs append;
     tq_fill_pack_args(ctx, &kd, &vd, 1, cache, pos, &append);
-    const TqStepExtras extras = {&append, nullptr, gather, nullptr};
+    const TqStepExtras extras = {&append, nullptr, gather, nullptr, 0};
     rc = tq_launch_decode_mma4(ctx, d_q, dtype, q_heads, cache, pos + 1, nullptr, nullptr, 0, n_splits, workspace,
                                nullptr, &extras, (cudaStream_t)stream);
     if (rc) return rc;
@@ -391,7 +391,7 @@ extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_
     TqPackArgs append;
     tq_fill_pack_args(ctx, &kd, &vd, 1, cache, 0, &append);
     append.pos_ptr = pos_dev;
-    const TqStepExtras extras = {&append, pos_dev, gather, nullptr};
+    const TqStepExtras extras = {&append, pos_dev, gather, nullptr, 0};
     rc = tq_launch_decode_mma4(ctx, q, dtype, q_heads, cache, cache->capacity, nullptr, nullptr, 0, n_splits, workspace,
                                gather ? nullptr : out, &extras, (cudaStream_t)stream);
     if (rc || !gather) return rc;

@@ -128,6 +128,7 @@ struct TqStepExtras {
     const int *len_ptr;               // the sequence length lives in device memory
     const tq_gather_desc *gather;     // KV-head shard: write the outputs into every rank's gathered buffer
     float *out_f32;                   // write the result unrounded (fp32) here instead of `out`
+    int parts;                        // sequence split: ranks per KV-head group (0: off), see tq_decode_attn_parts
 };
 int tq_mma4_tokens_per_cta_step();
 int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,

@@ -310,7 +310,7 @@ template <typename T>
 __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs a) {
     __shared__ __align__(16) float s_o[4][TQ_D];
     __shared__ float s_part[4][4][TQ_D];  // [quarter of d][head][column]
-    __shared__ float s_L[4];
+    __shared__ float s_L[4], s_M[4];
     const int groups = (a.G + 3) >> 2;           // a block serves up to four heads of a KV row
     const int64_t R = blockIdx.x / groups;
     const int h0 = 4 * (blockIdx.x % groups);
@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
     }
     {   // thread (e, dq) merges the splits of head dq
         const int g = dq;
-        float o = 0.f, L = 0.f;
+        float o = 0.f, L = 0.f, Mx = -INFINITY;
         if (g < n_heads) {
             const int64_t row = R * a.G + h0 + g;
             if (n_valid <= 4) {  // the usual case: everything is requested in one batch of loads
@@ -345,6 +345,7 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
                     pa[s] = on ? a.part_acc[(row * a.n_splits + s) * TQ_D + e] : 0.f;
                 }
                 const float M = fmaxf(fmaxf(pm[0], pm[1]), fmaxf(pm[2], pm[3]));
+                Mx = M;
 #pragma unroll
                 for (int s = 0; s < 4; ++s) {
                     const float w = (pm[s] == -INFINITY) ? 0.f : expf(pm[s] - M);
@@ -354,6 +355,7 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
             } else {
                 float M = -INFINITY;
                 for (int s = 0; s < n_valid; ++s) M = fmaxf(M, a.part_m[row * a.n_splits + s]);
+                Mx = M;
                 for (int s = 0; s < n_valid; ++s) {
                     const float ms = a.part_m[row * a.n_splits + s];
                     const float w = (ms == -INFINITY) ? 0.f : expf(ms - M);
@@ -363,7 +365,33 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
             }
         }
         s_o[g][e] = o;
-        if (e == 0) s_L[g] = L;
+        if (e == 0) s_L[g] = L, s_M[g] = Mx;
+        if (a.parts > 0 && g < n_heads) {
+            // Sequence split: this rank holds only a part of the row's tokens.  Its merged partial goes,
+            // unfinished, into slot `part` of every rank's exchange buffer [row][parts] (laid out like a
+            // decode workspace: all maxima, then all sums, then the accumulators); whoever has waited for
+            // all parts finishes the rows with this same kernel (n_splits = parts).
+            const int64_t row0 = R * a.G + h0;
+            const int64_t bi = row0 / a.Hq, hl = row0 % a.Hq;
+            const int64_t grow = bi * a.gather_heads_total + (int64_t)a.head_group * a.Hq + hl + g;  // row of the whole model
+            const unsigned seq = a.gather_seq;
+            for (int p = 0; p < a.gather_world; ++p) {
+                float *base = reinterpret_cast<float *>(static_cast<char *>(a.gather_out[p]) + ((seq & 1u) ? a.gather_out_stride : 0));
+                const int64_t n_rows = a.exch_rows;
+                float *xm = base, *xl = base + n_rows * a.parts, *xacc = base + 2 * n_rows * a.parts;
+                const int64_t slot = grow * a.parts + a.part;
+                xacc[slot * TQ_D + e] = o;
+                if (e == 0) xm[slot] = Mx, xl[slot] = L;
+            }
+        }
+    }
+    if (a.parts > 0) {  // report the rows (see the gather below) and leave: nothing is finished here
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            for (int p = 0; p < a.gather_world; ++p) atomicAdd_system(a.gather_flags[p] + a.gather_rank, (unsigned)n_heads);
+        }
+        return;
     }
     __syncthreads();
     {   // thread (e, dq) un-rotates rows d in [32 dq, 32 dq + 32) for all heads
@@ -570,7 +598,8 @@ int32_t tq_launch_combine(const CombineArgs &a, int32_t q_dtype, int64_t rows, c
 }
 
 int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limit_ms, int32_t batch, size_t elem_bytes,
-                              void *out_final, cudaStream_t stream) {
+                              void *out_final, cudaStream_t stream, int64_t rows_per_step) {
+    if (rows_per_step <= 0) rows_per_step = (int64_t)batch * (g->q_heads_total / g->world);
     // out_final: the whole gathered output [batch, q_heads_total, 128], or (out_local_only) this
     // rank's heads of it [batch, q_heads_total / world, 128]
     size_t n16 = 0, row_len16 = 1, row_stride16 = 0, src_off16 = 0;
@@ -591,7 +620,7 @@ int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limi
     // rank's flag, this rank's included.
     cudaError_t e = tq_launch_kernel(tq_gather_wait_kernel, dim3(blocks < 1 ? 1 : blocks), dim3(256), 0, stream, true,
                                      (const unsigned *)g->flags[g->rank], (int)g->world, (unsigned)g->seq,
-                                     (unsigned *)g->seq_dev, (unsigned)(batch * (g->q_heads_total / g->world)),
+                                     (unsigned *)g->seq_dev, (unsigned)rows_per_step,
                                      (unsigned *)g->counter, error_flag,
                                      (unsigned long long)(limit_ms < 1 ? 1 : limit_ms) * 1000000ull,
                                      reinterpret_cast<const uint4 *>(g->out[g->rank]), (long long)g->out_stride,
@@ -657,7 +686,7 @@ int32_t tq_launch_decode_exact(tq_ctx *ctx, const void *q, int32_t q_dtype, int3
     c.n_splits = n_splits, c.Hq = q_heads, c.G = a.G;
     c.seg_chunk = 0, c.seg_npad = 0;
     c.len_ptr = nullptr, c.len_add = 0, c.capacity = 0, c.plan_rows = 0, c.plan_ctas = 0, c.plan_step = 0;
-    c.gather_world = 0;
+    c.gather_world = 0, c.parts = 0, c.part = 0, c.head_group = 0, c.exch_rows = 0;
     c.rot_v = ctx->rot_v;
     c.q = q, c.out = out, c.out_f32 = nullptr;
     c.n_tail = n_tail;

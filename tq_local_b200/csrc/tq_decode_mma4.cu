@@ -711,7 +711,11 @@ int32_t tq_launch_decode_mma4(tq_ctx *ctx, const void *q, int32_t q_dtype, int32
     c.seg_chunk = a.chunk, c.seg_npad = a.n_pad;
     c.len_ptr = len_ptr, c.len_add = a.len_add, c.capacity = a.capacity;
     c.plan_rows = a.rows, c.plan_ctas = (int)grid.x, c.plan_step = step;
-    c.gather_world = 0;
+    c.gather_world = 0, c.parts = 0, c.part = 0, c.head_group = 0, c.exch_rows = 0;
+    if (gather && extras->parts > 0) {
+        c.parts = extras->parts, c.part = gather->rank % extras->parts, c.head_group = gather->rank / extras->parts;
+        c.exch_rows = (int64_t)cache->batch * gather->q_heads_total;
+    }
     if (gather) {
         c.gather_world = gather->world, c.gather_rank = gather->rank, c.gather_heads_total = gather->q_heads_total;
         c.gather_seq = gather->seq;

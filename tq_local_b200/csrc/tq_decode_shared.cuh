@@ -22,6 +22,12 @@ struct CombineArgs {
     long long gather_out_stride;     // bytes between a rank's two gathered buffers (step s uses buffer s & 1)
     void *gather_out[TQ_MAX_PEERS];
     unsigned *gather_flags[TQ_MAX_PEERS];
+    // Sequence split (fewer KV heads than ranks): `parts` ranks share a group of KV heads, each
+    // holding a disjoint part of the tokens.  When parts > 0 (grouped combine, gather_world > 0) the
+    // block does not finish its rows: it stores the merged partial (max, sum, acc[128], fp32,
+    // rotated space) of every head into slot `part` of the partial-exchange buffer of every rank.
+    int parts, part, head_group;
+    int64_t exch_rows;  // rows of the whole model (batch x q_heads_total): the exchange buffer's extent
     const float *rot_v;  // R_v[d][e]
     const void *q;       // original-dtype query, for the dense tail
     void *out;
@@ -41,8 +47,9 @@ struct DecodeWorkspace {
 };
 
 DecodeWorkspace tq_carve_workspace(void *workspace, int64_t rows, int n_splits);
+// rows_per_step: how many rows every rank reports per step (0: batch * q_heads_total / world)
 int32_t tq_launch_gather_wait(const tq_gather_desc *g, int *error_flag, int limit_ms, int32_t batch, size_t elem_bytes,
-                              void *out_final, cudaStream_t stream);
+                              void *out_final, cudaStream_t stream, int64_t rows_per_step = 0);
 int32_t tq_launch_qprep(tq_ctx *ctx, const void *q, int32_t q_dtype, int64_t rows, float *qrot, float *qproj,
                         cudaStream_t stream);
 // Query preparation for the tensor-core kernel; with `append` the same launch also encodes and

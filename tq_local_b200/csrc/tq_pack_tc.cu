@@ -290,11 +290,14 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
         __syncthreads();
         const float nrm = sqrtf((s_sq[0][vrow] + s_sq[1][vrow]) + (s_sq[2][vrow] + s_sq[3][vrow]));
         const float safe = nrm > 0.0f ? nrm : 1.0f;
+        // x * (1 / n) instead of x / n: at most one ulp from the quotient, i.e. 1e-8 on a unit
+        // vector's coordinate, two orders below the 1e-6 band in which a code may differ at all
+        const float inv = valid ? 1.0f / safe : 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) split3(valid ? x[8 * c + i] / safe : 0.f, t1[i], t2[i], t3[i]);
+            for (int i = 0; i < 8; ++i) split3(x[8 * c + i] * inv, t1[i], t2[i], t3[i]);
             const int off = operand_offset(vrow, 32 * hsel + 8 * c);
             *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
             *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
@@ -373,11 +376,12 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
             __syncthreads();
             const float rn = sqrtf((s_sq[0][vrow] + s_sq[1][vrow]) + (s_sq[2][vrow] + s_sq[3][vrow]));
             const float rsafe = rn > 0.0f ? rn : 1.0f;
+            const float rinv = valid ? 1.0f / rsafe : 0.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) split3(valid ? x[8 * c + i] / rsafe : 0.f, t1[i], t2[i], t3[i]);
+                for (int i = 0; i < 8; ++i) split3(x[8 * c + i] * rinv, t1[i], t2[i], t3[i]);
                 const int off = operand_offset(vrow, 32 * hsel + 8 * c);
                 *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
                 *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);

@@ -23,6 +23,7 @@ EXPORTS = (
     "tq_decode_attn_static", "tq_decode_step_workspace_bytes", "tq_decode_step_host", "tq_decode_step_dev",
     "tq_peer_buffer_create", "tq_peer_buffer_open", "tq_peer_buffer_close", "tq_peer_buffer_destroy",
     "tq_decode_attn_gather", "tq_gather_wait", "tq_decode_step_host_gather", "tq_set_wait_limit_ms", "tq_decode_attn_f32out",
+    "tq_parts_exchange_bytes", "tq_decode_attn_parts", "tq_decode_parts_finish",
 )
 
 _ERRORS = {-1: "bad argument", -2: "unsupported shape or mode", -3: "CUDA error", -4: "workspace too small"}
@@ -138,6 +139,14 @@ def lib() -> C.CDLL:
     L.tq_decode_attn_f32out.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.POINTER(CacheDesc), C.c_int32,
                                         C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
     L.tq_decode_attn_f32out.restype = C.c_int32
+    L.tq_parts_exchange_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+    L.tq_parts_exchange_bytes.restype = C.c_size_t
+    L.tq_decode_attn_parts.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.POINTER(CacheDesc), C.c_int32,
+                                       C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(GatherDesc), C.c_int32, C.c_void_p]
+    L.tq_decode_attn_parts.restype = C.c_int32
+    L.tq_decode_parts_finish.argtypes = [C.c_void_p, C.POINTER(GatherDesc), C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                         C.c_void_p, C.c_void_p]
+    L.tq_decode_parts_finish.restype = C.c_int32
     L.tq_set_wait_limit_ms.argtypes = [C.c_void_p, C.c_int32]
     L.tq_set_wait_limit_ms.restype = C.c_int32
     for name in ("tq_peer_buffer_create", "tq_peer_buffer_open", "tq_peer_buffer_close", "tq_peer_buffer_destroy",

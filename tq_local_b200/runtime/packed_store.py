@@ -230,6 +230,38 @@ class PackedStore:
                       "tq_gather_wait")
         return view
 
+    def decode_attn_parts(self, q: torch.Tensor, gather, *, seq_len: int | None = None, splits: int | None = None,
+                          out: torch.Tensor | None = None) -> torch.Tensor:
+        """Decode attention when more ranks than KV heads share the cache: ``gather.parts`` ranks
+        hold disjoint parts of the tokens of one group of KV heads (this store holds this rank's
+        part, possibly no token at all), ``q`` [B, Hq_group, 1, 128] holds the group's query heads.
+        The kernels exchange unfinished partials through ``gather`` (a ``PeerGather`` created with
+        ``parts=``) and every rank finishes all rows: the result is the output of the whole model
+        [B, Hq_total, 1, 128].  Every rank must make the same calls."""
+        b, hq = int(q.shape[0]), int(q.shape[1])
+        if q.shape[-1] != 128 or q.numel() != b * hq * 128 or b != self.batch:
+            raise ValueError(f"expected a single-token query [B={self.batch}, Hq, 1, 128], got {tuple(q.shape)}")
+        if not gather.parts:
+            raise ValueError("decode_attn_parts needs a PeerGather created with parts=")
+        qc = q.reshape(b, hq, 128)
+        if not qc.is_contiguous():
+            qc = qc.contiguous()
+        n = self.length if seq_len is None else int(seq_len)
+        splits = self.suggest_splits(max(n, 1)) if splits is None else int(splits)
+        ws = self._get_workspace(hq, splits)
+        desc, _ = gather.next_desc()
+        if out is None:
+            out = torch.empty(gather.shape, dtype=q.dtype, device=q.device)
+        stream = self._stream_ptr()
+        with torch.cuda.device(self.codec.device):
+            ffi.check(ffi.lib().tq_decode_attn_parts(self.codec.handle, qc.data_ptr(), tq_dtype(q.dtype), hq,
+                                                     C.byref(self._desc), n, splits, ws.data_ptr(), ws.numel(),
+                                                     C.byref(desc), gather.parts, stream), "tq_decode_attn_parts")
+            ffi.check(ffi.lib().tq_decode_parts_finish(self.codec.handle, C.byref(desc), b, tq_dtype(q.dtype),
+                                                       gather.parts, hq // self.kv_heads, out.data_ptr(), stream),
+                      "tq_decode_parts_finish")
+        return out
+
     def decode_step_host(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, out: torch.Tensor,
                          splits: int | None = None) -> torch.Tensor:
         """One decode step with HOST tensors (pinned memory keeps the copies asynchronous): append

@@ -99,14 +99,22 @@ class PeerGather:
     gather must not be used through ``next_desc``."""
 
     def __init__(self, shard: HeadShard, batch: int, q_heads_total: int, dtype: torch.dtype, device: torch.device,
-                 device_sequence: bool = False):
+                 device_sequence: bool = False, parts: int = 0):
         from tq_local_b200.runtime import ffi
 
         if shard.world_size > ffi.TQ_MAX_PEERS:
             raise ValueError(f"at most {ffi.TQ_MAX_PEERS} ranks")
         self.shard, self.device, self.dtype = shard, torch.device(device), dtype
         self.shape = (int(batch), int(q_heads_total), 1, 128)
-        self.out_bytes = (batch * q_heads_total * 128 * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256
+        # parts > 0: the buffers exchange unfinished fp32 partials of a sequence split (every rank
+        # finishes all rows itself, see PackedStore.decode_attn_parts) instead of finished outputs
+        self.parts = int(parts)
+        if self.parts:
+            if device_sequence or shard.world_size % self.parts:
+                raise ValueError("a sequence split needs host-numbered steps and a world size that is a multiple of parts")
+            self.out_bytes = int(ffi.lib().tq_parts_exchange_bytes(batch, q_heads_total, self.parts))
+        else:
+            self.out_bytes = (batch * q_heads_total * 128 * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256
         self.total = 2 * self.out_bytes + 256
         self.seq = 0
         self.seq_dev = torch.zeros(1, dtype=torch.int32, device=self.device) if device_sequence else None
@@ -144,8 +152,8 @@ class PeerGather:
             self._release()
             raise ffi.TQError(f"peer buffers unavailable: {problem}")
         raw = torch.as_tensor(_DeviceBytes(self.bases[shard.rank], 2 * self.out_bytes), device=self.device)
-        self._views = [raw[i * self.out_bytes:i * self.out_bytes + self._numel_bytes()].view(dtype).view(self.shape)
-                       for i in range(2)]
+        self._views = None if self.parts else [
+            raw[i * self.out_bytes:i * self.out_bytes + self._numel_bytes()].view(dtype).view(self.shape) for i in range(2)]
 
     def _numel_bytes(self) -> int:
         b, h, _, d = self.shape
@@ -172,7 +180,7 @@ class PeerGather:
         self.seq += 1
         d = self._desc()
         d.seq = self.seq
-        return d, self._views[self.seq & 1]
+        return d, (None if self._views is None else self._views[self.seq & 1])
 
     def last_view(self) -> torch.Tensor:
         """This rank's gathered output [batch, q_heads_total, 1, 128] of the latest host-numbered step."""

@@ -192,3 +192,13 @@ def test_sequence_split_on_one_gpu_matches_the_undivided_cache(setup_golden, Hq,
         err2 = float((outs[0].float() - whole.decode_attn(q.cuda()).float()).abs().max() / want.abs().max())
         assert err2 <= 2.0 ** -7
     assert codec.device_status() == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_split_between_two_gpus_through_the_cache_layer():
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_parts_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29617", worker],
+                         capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0 and "PARTS_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-3000:]

@@ -171,6 +171,7 @@ class PackedMSELayer(CacheLayerMixin):
         self._static_pos: torch.Tensor | None = None  # see begin_static_decode
         self._stream_threshold: float | None = None   # see build_streaming_prefill_cache
         self._mask_bound = False                      # see bind_attention_mask
+        self._tokens_seen = 0                         # tokens handed to this layer (sequence split: not all are stored here)
         self._window: tuple[int, int] | None = None   # (first batch row, total batch) of a prompt pass run in row blocks
         self._window_dense: bool | None = None        # the norm-guard decision of such a pass (taken on its first block)
         self._window_norm = [0.0, 0]                  # running (sum of block means x rows, rows) of such a pass
@@ -259,10 +260,24 @@ class PackedMSELayer(CacheLayerMixin):
 
     def _ensure_store(self, key_states: torch.Tensor) -> None:
         if self.store is None:
-            local = self.shard.local_kv(key_states)
-            cap = int(key_states.shape[2]) + self.reserve_tokens
+            local = self.shard.local_tokens(self.shard.local_kv(key_states), int(key_states.shape[1]), self._tokens_seen)
+            cap = int(local.shape[2]) + self.reserve_tokens
             self.store = PackedStore(self.codec, int(local.shape[0]), int(local.shape[1]), cap)
             self._kv_heads_total = int(key_states.shape[1])
+
+    @property
+    def seq_parts(self) -> int:
+        """Ranks that share the tokens of each of this layer's KV heads (1: plain head sharding)."""
+        return 1 if self._kv_heads_total is None else self.shard.seq_parts(self._kv_heads_total)
+
+    def _local(self, key_states: torch.Tensor, value_states: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """This rank's share of new K/V [B, Hkv, T, D]: its KV heads and, when several ranks share
+        a head, its tokens.  Counts the tokens as seen."""
+        heads = int(key_states.shape[1])
+        k = self.shard.local_tokens(self.shard.local_kv(key_states), heads, self._tokens_seen)
+        v = self.shard.local_tokens(self.shard.local_kv(value_states), heads, self._tokens_seen)
+        self._tokens_seen += int(key_states.shape[2])
+        return k, v
 
     def initialize_from_dense(self, key_states: torch.Tensor, value_states: torch.Tensor, *,
                               force_dense: bool = False) -> None:
@@ -277,14 +292,14 @@ class PackedMSELayer(CacheLayerMixin):
         if not self.is_initialized:
             self.lazy_initialization(key_states, value_states)
         self._ensure_store(key_states)
-        self.store.pack(self.shard.local_kv(key_states), self.shard.local_kv(value_states))
+        self.store.pack(*self._local(key_states, value_states))
 
     # ---------------------------------------------------------------- replayable decode
     def supports_static_decode(self, q_heads: int) -> bool:
         """Whether this layer can serve decode steps whose length lives on the device (packed,
         quantised appends, 16-bit cache, at most 8 query heads per KV head).  A sharded layer
         additionally needs a device-sequenced ``PeerGather`` (see ``begin_static_decode``)."""
-        return (self.store is not None and not self._force_dense and self.quantize_decode
+        return (self.store is not None and not self._force_dense and self.quantize_decode and self.seq_parts == 1
                 and self._dense_k.length == 0 and self.dtype in (torch.float16, torch.bfloat16)
                 and q_heads // self._kv_heads_total <= 8)
 
@@ -336,7 +351,10 @@ class PackedMSELayer(CacheLayerMixin):
         # Eager path: hand back the dequantised history plus the new token, then store it.
         prev_k, prev_v = self._decode_keys_full(), self._decode_values_full()
         self._ensure_store(key_states)
-        self.store.pack(self.shard.local_kv(key_states), self.shard.local_kv(value_states))
+        if self.seq_parts > 1:
+            raise NotImplementedError("a sequence-split cache serves attention through the 'turboquant' backend only "
+                                      "(enable_turboquant_attention); it cannot hand back dequantised history")
+        self.store.pack(*self._local(key_states, value_states))
         if prev_k is None:
             return key_states, value_states
         return (torch.cat((prev_k, self.shard.local_kv(key_states)), dim=-2),
@@ -369,11 +387,14 @@ class PackedMSELayer(CacheLayerMixin):
             return
         if not self.is_initialized:
             self.lazy_initialization(key_states, value_states)
-        local_k, local_v = self.shard.local_kv(key_states), self.shard.local_kv(value_states)
+        self._kv_heads_total = int(key_states.shape[1])
+        seen = self._tokens_seen
+        local_k, local_v = self._local(key_states, value_states)
+        self._tokens_seen = seen  # (every row block brings the same token positions; finish_prefill counts them once)
         if self.store is None:
-            self.store = PackedStore(self.codec, total, int(local_k.shape[1]), int(n) + self.reserve_tokens)
-            self._kv_heads_total = int(key_states.shape[1])
+            self.store = PackedStore(self.codec, total, int(local_k.shape[1]), int(local_k.shape[2]) + self.reserve_tokens)
         self.store.pack_rows(local_k, local_v, b0, 0)
+        self._window_local = int(local_k.shape[2])
 
     def begin_prefill_block(self, b0: int, total_batch: int, threshold: float) -> None:
         """Arm the layer for the prompt K/V of batch rows starting at ``b0`` (of ``total_batch``)."""
@@ -387,7 +408,8 @@ class PackedMSELayer(CacheLayerMixin):
         if self._force_dense:
             self._dense_k.length = self._dense_v.length = int(n_tokens)
         elif self.store is not None:
-            self.store.length = int(n_tokens)
+            self.store.length = int(getattr(self, "_window_local", n_tokens))  # (a sequence split stores a piece)
+        self._tokens_seen = int(n_tokens)
         s, rows = self._window_norm
         return rows == 0 or ((s / rows) > threshold) == bool(self._window_dense)
 
@@ -396,10 +418,13 @@ class PackedMSELayer(CacheLayerMixin):
         quantised in place when ``quantize_decode``, otherwise appended to the dense tail."""
         if self.quantize_decode:
             self._ensure_store(key_states)
-            self.store.pack(self.shard.local_kv(key_states), self.shard.local_kv(value_states))
+            self.store.pack(*self._local(key_states, value_states))
         else:
+            if self.seq_parts > 1:
+                raise NotImplementedError("quantize_decode=False is not available when several ranks share a KV head")
             self._dense_k.append(self.shard.local_kv(key_states), self.reserve_tokens)
             self._dense_v.append(self.shard.local_kv(value_states), self.reserve_tokens)
+            self._tokens_seen += int(key_states.shape[2])
         return key_states, value_states
 
     def _update_dense_decode(self, key_states, value_states):
@@ -425,6 +450,8 @@ class PackedMSELayer(CacheLayerMixin):
         and spares every layer and step the look at the mask the model passes down."""
         if self.store is None or self._force_dense:
             return
+        if mask is not None and self.seq_parts > 1:
+            raise NotImplementedError("padded batches are not available when several ranks share a KV head")
         self.store.set_seq_start(None if mask is None else leading_masked_tokens(mask))
         self._mask_bound = (mask is not None) if lock is None else bool(lock)
 
@@ -450,6 +477,15 @@ class PackedMSELayer(CacheLayerMixin):
                                               gather=self._static_gather)
         b, hq, sq, d = query_states.shape
         q_local = self.shard.local_q(query_states, self._kv_heads_total)
+        if self.seq_parts > 1:
+            # Several ranks share each KV head: every rank attends its part of the tokens, the partials
+            # are exchanged and every rank finishes the whole output (no gather of outputs afterwards).
+            if sq != 1:
+                raise NotImplementedError("a sequence-split cache serves one query token per step")
+            from tq_local_b200.runtime.sharding import PeerGather
+
+            gather = PeerGather.shared(self.shard, b, hq, query_states.dtype, query_states.device, self.seq_parts)
+            return self.store.decode_attn_parts(q_local, gather)
         tail_k, tail_v = self._dense_k.view(), self._dense_v.view()
         n_tail = 0 if tail_k is None else int(tail_k.shape[2])
         outs = []
@@ -508,6 +544,8 @@ class PackedMSELayer(CacheLayerMixin):
         return 0 if self.store is None else int(self.store.length)
 
     def get_seq_length(self) -> int:
+        if self.seq_parts > 1:
+            return self._tokens_seen  # (this rank stores only its part of them)
         return self.packed_seq_length() + self._dense_k.length
 
     def get_mask_sizes(self, cache_position) -> tuple[int, int]:
@@ -655,7 +693,9 @@ def verify_packed_reconstruction(original_cache, packed_cache: Cache) -> list[di
         if dense:
             k1, v1 = layer._dense_keys, layer._dense_values
         else:
-            k0, v0 = layer.shard.local_kv(k0), layer.shard.local_kv(v0)
+            heads = int(k0.shape[1])  # (a sequence split holds a piece of the prompt's tokens on this rank)
+            k0 = layer.shard.local_tokens(layer.shard.local_kv(k0), heads, 0)
+            v0 = layer.shard.local_tokens(layer.shard.local_kv(v0), heads, 0)
             k1, v1 = layer._decode_keys_full(), layer._decode_values_full()
         k0, v0, k1, v1 = k0.float(), v0.float(), k1.float(), v1.float()
         dk, dv = k0 - k1, v0 - v1

@@ -34,16 +34,39 @@ class HeadShard:
     def check(self, kv_heads: int, q_heads: int) -> None:
         if self.world_size < 1 or not 0 <= self.rank < self.world_size:
             raise ValueError(f"bad shard: rank {self.rank} of {self.world_size}")
-        if kv_heads % self.world_size:
+        if kv_heads % self.world_size and self.world_size % kv_heads:
             raise ValueError(
-                f"{kv_heads} KV heads do not divide over {self.world_size} ranks; "
-                "use a world size that divides the KV-head count")
+                f"{kv_heads} KV heads and {self.world_size} ranks: one count must divide the other "
+                "(heads are sharded over the ranks, or several ranks share the tokens of each head)")
         if q_heads % kv_heads:
             raise ValueError(f"{q_heads} query heads are not a multiple of {kv_heads} KV heads")
 
+    def seq_parts(self, kv_heads: int) -> int:
+        """How many ranks share the tokens of one KV head: 1 while there are at least as many KV
+        heads as ranks, else ``world_size // kv_heads`` (Qwen2.5-7B's 4 KV heads on 8 GPUs: 2)."""
+        return self.world_size // kv_heads if kv_heads < self.world_size else 1
+
     def kv_range(self, kv_heads: int) -> tuple[int, int]:
+        parts = self.seq_parts(kv_heads)
+        if parts > 1:
+            head = self.rank // parts
+            return head, head + 1
         per = kv_heads // self.world_size
         return self.rank * per, (self.rank + 1) * per
+
+    def local_tokens(self, t: torch.Tensor, kv_heads: int, seen: int) -> torch.Tensor:
+        """The tokens of ``t`` [B, H, T, D] this rank stores when ``seq_parts`` ranks share a head:
+        a prompt (T > 1) is cut into ``parts`` contiguous pieces, single decoded tokens go to the
+        parts in turn (``seen`` = tokens the cache has been handed so far).  Attention over a set
+        of tokens does not depend on their order, so any disjoint cover works."""
+        parts = self.seq_parts(kv_heads)
+        if parts == 1:
+            return t
+        part, n = self.rank % parts, int(t.shape[2])
+        if n == 1:
+            return t if seen % parts == part else t[:, :, :0]
+        piece = (n + parts - 1) // parts
+        return t[:, :, part * piece:(part + 1) * piece]
 
     def q_range(self, kv_heads: int, q_heads: int) -> tuple[int, int]:
         lo, hi = self.kv_range(kv_heads)
@@ -185,6 +208,26 @@ class PeerGather:
     def last_view(self) -> torch.Tensor:
         """This rank's gathered output [batch, q_heads_total, 1, 128] of the latest host-numbered step."""
         return self._views[self.seq & 1]
+
+    _shared: dict = {}
+
+    @classmethod
+    def shared(cls, shard: HeadShard, batch: int, q_heads_total: int, dtype: torch.dtype, device: torch.device,
+               parts: int) -> "PeerGather":
+        """One partial-exchange ``PeerGather`` per (group, shape) for all layers of a model whose
+        KV heads are fewer than its ranks.  Created on first use, collectively (every rank reaches
+        its first sequence-split attention call at the same point of the model)."""
+        key = (id(shard.group), shard.rank, int(batch), int(q_heads_total), dtype, str(device), int(parts))
+        if key not in cls._shared:
+            cls._shared[key] = cls(shard, batch, q_heads_total, dtype, device, parts=parts)
+        return cls._shared[key]
+
+    @classmethod
+    def close_shared(cls) -> None:
+        """Collective: release every shared partial-exchange buffer."""
+        for gather in list(cls._shared.values()):
+            gather.close()
+        cls._shared.clear()
 
     def static_desc(self):
         """Descriptor for steps numbered on the device (the same for every step)."""

@@ -293,13 +293,16 @@ def run_gpu_arm(args) -> None:
         w["bits"] = args.bits
     if args.batch_per_gpu or args.context or args.q_heads or args.kv_heads or args.bits:
         w["name"] += " (shape overridden)"
-    if w["kv_heads"] % world:
-        raise SystemExit(f"{w['kv_heads']} KV heads do not shard over {world} ranks")
+    if w["kv_heads"] % world and world % w["kv_heads"]:
+        raise SystemExit(f"{w['kv_heads']} KV heads and {world} ranks: one count must divide the other")
     dtype = getattr(torch, w["dtype"])
     batch = w["batch_per_gpu"] * world
-    hkv = w["kv_heads"] // world
-    hq = w["q_heads"] // world
-    n_ctx = w["context"]
+    # fewer KV heads than ranks (e.g. 4 on 8 GPUs): `parts` ranks share each head, each holding a
+    # contiguous piece of its tokens; unfinished partials are exchanged instead of outputs
+    parts = world // w["kv_heads"] if w["kv_heads"] < world else 1
+    hkv = max(1, w["kv_heads"] // world)
+    hq = w["q_heads"] // (world // parts)
+    n_ctx = w["context"] // parts
     steps, warmup = args.steps, max(args.warmup, 3)
     unit_bytes = bytes_per_unit(w["bits"], w["use_qjl"])
 
@@ -326,7 +329,12 @@ def run_gpu_arm(args) -> None:
     # buffers).  If the peer buffers cannot be set up on this box, or a trial step reports a
     # device-side problem on any rank, every rank falls back to an NCCL all-gather.
     peer = None
-    if world > 1 and args.gather in ("auto", "p2p"):
+    if parts > 1:
+        from tq_local_b200.runtime.sharding import HeadShard, PeerGather
+
+        peer = PeerGather(HeadShard.from_process_group(), batch, w["q_heads"], dtype, dev, parts=parts)
+        args.skip_e2e = True  # (the host-buffer step has no sequence-split form)
+    elif world > 1 and args.gather in ("auto", "p2p"):
         from tq_local_b200.runtime.sharding import HeadShard, PeerGather
 
         ok = torch.ones(1, device=dev)
@@ -352,7 +360,7 @@ def run_gpu_arm(args) -> None:
     # One-off, untimed: the fused gather must give, bit for bit, what an NCCL all-gather of the plain
     # decode outputs gives (the only multi-GPU correctness evidence a run on this box can carry).
     gather_check = None
-    if world > 1 and peer is not None:
+    if world > 1 and peer is not None and parts == 1:
         view = store.decode_attn_gather(q, peer, seq_len=n_ctx, splits=splits)
         store.decode_attn(q, seq_len=n_ctx, splits=splits, out=out)
         dist.all_gather_into_tensor(gathered, out)
@@ -362,7 +370,12 @@ def run_gpu_arm(args) -> None:
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
         gather_check = "bitexact" if same.item() > 0 else "MISMATCH"
 
+    out_full = torch.empty(batch, w["q_heads"], 1, HEAD_DIM, dtype=dtype, device=dev) if parts > 1 else None
+
     def step():
+        if parts > 1:  # partials of all parts are exchanged, every rank finishes the whole output
+            store.decode_attn_parts(q, peer, seq_len=n_ctx, splits=splits, out=out_full)
+            return
         if peer is not None:  # the combine kernel writes every rank's gathered buffer itself
             store.decode_attn_gather(q, peer, seq_len=n_ctx, splits=splits)
             return
@@ -496,8 +509,10 @@ def run_gpu_arm(args) -> None:
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {
                 "workload": w["name"], "global_batch": batch, "q_heads": w["q_heads"], "kv_heads": w["kv_heads"],
-                "context": n_ctx, "bits": w["bits"], "mode": "Q_prod", "bytes_per_token_head": unit_bytes,
-                "parallelism": (f"kv-head-shard{world}, outputs gathered by "
+                "context": w["context"], "bits": w["bits"], "mode": "Q_prod", "bytes_per_token_head": unit_bytes,
+                "parallelism": (f"kv-head-shard{world // parts} x sequence-split{parts}, partials exchanged by peer stores"
+                                if parts > 1 else
+                                f"kv-head-shard{world}, outputs gathered by "
                                 + ("peer stores from the combine kernel" if peer is not None else "NCCL all-gather"))
                 if world > 1 else "single",
                 "splits": splits, "l2": f"inputs larger than L2 ({unit_bytes * batch * hkv * n_ctx / 1e6:.0f} MB of packed cache per GPU per step vs 126 MB)",

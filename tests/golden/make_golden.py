@@ -25,11 +25,18 @@ import numpy as np
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the unmodified reference project (its root)")
+    ap.add_argument("--out", default=None, help="folder to write the fixtures to (default: beside this script)")
     args = ap.parse_args()
     here = os.path.dirname(os.path.abspath(__file__))
     # The reference must shadow any other package called ``turboquant``.
     sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != os.path.dirname(os.path.dirname(here))]
     sys.path.insert(0, os.path.join(args.reference, "src"))
+
+    script_dir = here
+    if args.out:
+        here = os.path.abspath(args.out)
+        os.makedirs(here, exist_ok=True)
+    del script_dir
 
     import torch
     import turboquant  # noqa: F401  (the reference)
@@ -207,6 +214,35 @@ def main() -> None:
         e2e[f"{tag}_recon_key_cos"] = np.array([r["key_cosine_sim"] for r in met["reconstruction_quality"]])
         e2e[f"{tag}_recon_val_cos"] = np.array([r["val_cosine_sim"] for r in met["reconstruction_quality"]])
     np.savez_compressed(os.path.join(here, "e2e_tiny_llama.npz"), **e2e)
+
+    # ---------------- the unpacked "qmse" variant (quantise-dequantise in place) -----------------
+    from turboquant.quantization.turboquant_mse import quantize_past_key_values_mse, quantize_vectors_mse
+    from turboquant.runtime.generation import greedy_decode_with_prefill_cache
+
+    qm: dict[str, np.ndarray] = {}
+    g = torch.Generator().manual_seed(17)
+    vec = torch.randn(257, 128, generator=g) * torch.exp(0.5 * torch.randn(257, 1, generator=g))
+    vec[5] = 0.0  # a zero vector keeps norm 1
+    qm["vectors"] = vec.numpy().copy()
+    for bits, seed in ((3, 0), (4, 5)):
+        rec, idx = quantize_vectors_mse(vec.numpy(), bits=bits, seed=seed)
+        qm[f"rec_b{bits}_s{seed}"], qm[f"idx_b{bits}_s{seed}"] = rec, idx
+    kv = tuple((torch.randn(1, 2, 9, 128, generator=g), torch.randn(1, 2, 9, 128, generator=g)) for _ in range(2))
+    qm["kv"] = torch.stack([torch.stack(pair) for pair in kv]).numpy().copy()
+    full = quantize_past_key_values_mse(kv, bits=4, seed=0)
+    last = quantize_past_key_values_mse(kv, bits=4, seed=0, token_slice=slice(-1, None))
+    qm["kv_full"] = torch.stack([torch.stack(list(pair)) for pair in full]).numpy().copy()
+    qm["kv_last"] = torch.stack([torch.stack(list(pair)) for pair in last]).numpy().copy()
+    out = greedy_decode_with_prefill_cache(model=model, tokenizer=Tok(), inputs={"input_ids": ids}, max_new_tokens=8,
+                                           variant="qmse", qmse_bits=4)
+    qm["gen_text_ids"] = np.array([int(t) for t in out.text.split()])
+    qm["gen_metrics_keys"] = np.array(sorted(out.metrics.to_dict().keys()))
+    qm["gen_qmse_bits"] = np.int64(out.metrics.qmse_bits)
+    qm["gen_packed_estimate_total"] = np.int64(out.metrics.turboquant_mse_packed_estimate["total_bytes"]
+                                               if "total_bytes" in out.metrics.turboquant_mse_packed_estimate
+                                               else sum(v for v in out.metrics.turboquant_mse_packed_estimate.values()
+                                                        if isinstance(v, (int, np.integer))))
+    np.savez_compressed(os.path.join(here, "qmse.npz"), **qm)
     print("golden fixtures written to", here)
 
 

@@ -368,3 +368,56 @@ def test_generate_with_a_left_padded_batch_matches_the_unpadded_prompt():
             model.generate(batch, attention_mask=torch.flip(mask, dims=[1]), max_new_tokens=4)
         finally:
             turboquant.deactivate(model, quiet=True)
+
+
+class _CallableTokenizer(StubTokenizer):
+    """The stub plus what ``TurboQuantSession.generate`` uses: a call that tokenises a prompt
+    ("12 7 300" -> ids) and a chat template that joins the messages' contents."""
+
+    def __call__(self, text, return_tensors="pt"):
+        ids = torch.tensor([[int(t) for t in text.split()]], dtype=torch.long)
+        return {"input_ids": ids, "attention_mask": torch.ones_like(ids)}
+
+    def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True):
+        return " ".join(m["content"] for m in messages) + (" 1" if add_generation_prompt else "")
+
+
+def test_session_generate_telemetry_and_errors():
+    """``TurboQuantSession`` (reference: adapters/transformers.py:180-311): prompt and chat-message
+    input, text or full output, metrics / telemetry / compatibility report, and its error cases;
+    it must produce what ``activate`` + ``generate`` produces with the same settings."""
+    import turboquant
+    from turboquant import TurboQuantSession
+
+    model = _tiny_model()
+    tok = _CallableTokenizer()
+    prompt = " ".join(str(3 + 5 * i % 500) for i in range(40))
+    session = TurboQuantSession(model=model, tokenizer=tok, bits=4, use_qjl_keys=True, quantize_decode=True)
+    assert session.last_metrics() is None and session.last_telemetry() is None
+    text = session.generate(prompt=prompt, max_new_tokens=6)
+    assert isinstance(text, str) and len(text.split()) == 6
+    full = session.generate(prompt=prompt, max_new_tokens=6, return_output=True)
+    assert full.text == text  # reproducible
+    tel, met = session.last_telemetry(), session.last_metrics()
+    assert tel["prompt_tokens"] == 40 and tel["completion_tokens"] == 6 and tel["qmse_bits"] == 4
+    assert tel["packed_actual_bytes"] < tel["dense_kv_bytes"] and met["variant"] == "qmse_packed"
+    assert met["reconstruction_quality"] is not None  # the session verifies like the reference's
+    assert session.compatibility_report()["compatible"] is True
+    # the same settings through activate() give the same tokens
+    ids = tok(prompt)["input_ids"].cuda()
+    turboquant.activate(model, tok, quiet=True, bits=4, use_qjl_keys=True, quantize_decode=True)
+    out = model.generate(ids, max_new_tokens=6)
+    turboquant.deactivate(model, quiet=True)
+    assert " ".join(str(int(t)) for t in out[0, 40:]) == text
+    # chat messages go through the tokenizer's template
+    chat = session.generate(messages=[{"role": "user", "content": prompt}], max_new_tokens=3)
+    assert len(chat.split()) == 3
+    with pytest.raises(ValueError):
+        session.generate(max_new_tokens=3)  # neither prompt nor messages
+    with pytest.raises(ValueError):
+        TurboQuantSession(model=model, tokenizer=StubTokenizer()).generate(messages=[{"role": "user", "content": "1"}])
+    # the uncompressed comparison run the reference's CLI offers
+    base = TurboQuantSession(model=model, tokenizer=tok, variant="baseline").generate(prompt=prompt, max_new_tokens=6,
+                                                                                     return_output=True)
+    assert base.metrics.variant == "baseline" and base.metrics.turboquant_mse_packed_actual is None
+    assert base.text.split()[0] == text.split()[0]  # the first token comes from the same dense prompt pass

@@ -177,7 +177,60 @@ def test_generation_variant_validation():
 
     validate_generation_variant("baseline")
     validate_generation_variant("qmse_packed")
+    validate_generation_variant("qmse")
     with pytest.raises(ValueError):
         validate_generation_variant("nope")
-    with pytest.raises(NotImplementedError):
-        validate_generation_variant("qmse")
+
+
+def test_unpacked_qmse_variant_matches_the_reference():
+    """The unpacked ``qmse`` variant (quantise-dequantise in place; reference turboquant_mse.py:124-217,
+    generation.py:104-113,170-178) against the reference's own outputs: per-vector reconstruction and
+    indices, in-place treatment of a cache (whole, and last token only), and a greedy generation
+    on the tiny Llama.  Plain tensor arithmetic on the tensors' device, so it runs here on the CPU."""
+    import numpy as np
+    import torch
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from conftest import Golden
+    from tq_local_b200.quantization.turboquant_mse import quantize_past_key_values_mse, quantize_vectors_mse
+    from tq_local_b200.runtime.generation import greedy_decode_with_prefill_cache
+
+    g = Golden("qmse")
+    vec = g.z["vectors"]
+    for bits, seed in ((3, 0), (4, 5)):
+        rec, idx = quantize_vectors_mse(vec, bits=bits, seed=seed)
+        assert isinstance(rec, np.ndarray) and rec.dtype == np.float32 and idx.dtype == np.int16
+        want_idx, want_rec = g.z[f"idx_b{bits}_s{seed}"], g.z[f"rec_b{bits}_s{seed}"]
+        # (BLAS summation order may move a value across a boundary it sits on: at most a few codes)
+        assert (idx != want_idx).mean() < 1e-4 and np.abs(idx.astype(int) - want_idx).max() <= 1
+        same = (idx == want_idx).all(axis=1)
+        assert np.abs(rec[same] - want_rec[same]).max() <= 2e-6 * np.abs(want_rec).max()
+    kv = torch.from_numpy(g.z["kv"])
+    as_tuple = lambda t: tuple((t[i, 0], t[i, 1]) for i in range(t.shape[0]))
+    for key, sl in (("kv_full", None), ("kv_last", slice(-1, None))):
+        got = quantize_past_key_values_mse(as_tuple(kv), bits=4, seed=0, token_slice=sl)
+        want = torch.from_numpy(g.z[key])
+        for i, (k_, v_) in enumerate(got):
+            assert float((k_ - want[i, 0]).abs().max()) <= 1e-5 and float((v_ - want[i, 1]).abs().max()) <= 1e-5
+    assert torch.equal(quantize_past_key_values_mse(as_tuple(kv), 4, token_slice=slice(-1, None))[0][0][:, :, :-1],
+                       kv[0, 0][:, :, :-1])  # earlier tokens untouched
+
+    class Tok:
+        eos_token_id = None
+
+        def decode(self, ids, skip_special_tokens=True):
+            return " ".join(str(int(i)) for i in ids)
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=512)
+    model = LlamaForCausalLM(cfg).eval()
+    ids = torch.from_numpy(Golden("e2e_tiny_llama").z["input_ids"])
+    out = greedy_decode_with_prefill_cache(model=model, tokenizer=Tok(), inputs={"input_ids": ids}, max_new_tokens=8,
+                                           variant="qmse", qmse_bits=4)
+    got_ids = [int(t) for t in out.text.split()]
+    want_ids = list(g.z["gen_text_ids"])
+    assert got_ids[0] == want_ids[0] and sum(a == b for a, b in zip(got_ids, want_ids)) >= 7
+    assert out.metrics.variant == "qmse" and out.metrics.qmse_bits == int(g.z["gen_qmse_bits"])
+    assert sorted(out.metrics.to_dict().keys()) == list(g.z["gen_metrics_keys"])
+    assert out.metrics.turboquant_mse_packed_actual is None and out.metrics.reconstruction_quality is None

@@ -185,6 +185,7 @@ int tq_check_cache(const tq_ctx *ctx, const tq_cache_desc *c) {
 
 extern "C" int32_t tq_pack(tq_ctx *ctx, const tq_dense_desc *k, const tq_dense_desc *v, int32_t n_tokens,
                            const tq_cache_desc *cache, int32_t pos0, tq_stream stream) {
+    TqRange range_("tq_pack");
     if (!ctx || !k || !v || !k->data || !v->data) return TQ_ERR_ARG;
     int rc = tq_check_cache(ctx, cache);
     if (rc) return rc;
@@ -250,6 +251,7 @@ extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, i
                                   const tq_cache_desc *cache, int32_t seq_len, const tq_dense_desc *tail_k,
                                   const tq_dense_desc *tail_v, int32_t n_tail, int32_t n_splits,
                                   void *workspace, size_t workspace_bytes, void *out, tq_stream stream) {
+    TqRange range_("tq_decode_attn");
     return decode_attn_impl(ctx, q, q_dtype, q_heads, cache, seq_len, tail_k, tail_v, n_tail, n_splits, workspace,
                             workspace_bytes, out, nullptr, stream);
 }
@@ -257,6 +259,7 @@ extern "C" int32_t tq_decode_attn(tq_ctx *ctx, const void *q, int32_t q_dtype, i
 extern "C" int32_t tq_decode_attn_f32out(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
                                          const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits,
                                          void *workspace, size_t workspace_bytes, float *out, tq_stream stream) {
+    TqRange range_("tq_decode_attn_f32out");
     if (q_dtype != TQ_DTYPE_F16 && q_dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
     if (seq_len <= 0) return TQ_ERR_ARG;
     const TqStepExtras extras = {nullptr, nullptr, nullptr, out, 0};
@@ -288,6 +291,7 @@ extern "C" int32_t tq_decode_step_host(tq_ctx *ctx, const void *q_host, const vo
                                        int32_t dtype, int32_t q_heads, const tq_cache_desc *cache, int32_t pos,
                                        int32_t n_splits, void *workspace, size_t workspace_bytes, void *out_host,
                                        tq_stream stream) {
+    TqRange range_("tq_decode_step_host");
     // every check comes before the first copy or launch: a call that fails leaves the cache and
     // the workspace untouched
     if (!ctx || !q_host || !k_host || !v_host || !out_host || !workspace || !cache) return TQ_ERR_ARG;
@@ -342,6 +346,7 @@ extern "C" int32_t tq_decode_step_host_gather(tq_ctx *ctx, const void *q_host, c
                                               int32_t dtype, int32_t q_heads, const tq_cache_desc *cache, int32_t pos,
                                               int32_t n_splits, void *workspace, size_t workspace_bytes,
                                               const tq_gather_desc *gather, void *out_host, tq_stream stream) {
+    TqRange range_("tq_decode_step_host_gather");
     if (!ctx || !q_host || !k_host || !v_host || !out_host || !workspace || !cache || !gather) return TQ_ERR_ARG;
     if (pos < 0 || pos >= cache->capacity || n_splits < 1) return TQ_ERR_ARG;
     if (dtype != TQ_DTYPE_F16 && dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
@@ -372,6 +377,7 @@ extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_
                                       int32_t q_heads, const tq_cache_desc *cache, const int32_t *pos_dev,
                                       int32_t n_splits, void *workspace, size_t workspace_bytes, void *out,
                                       const tq_gather_desc *gather, tq_stream stream) {
+    TqRange range_("tq_decode_step_dev");
     if (!ctx || !q || !k_new || !v_new || !out || !workspace || !pos_dev) return TQ_ERR_ARG;
     int32_t rc = tq_check_cache(ctx, cache);
     if (rc) return rc;
@@ -400,6 +406,7 @@ extern "C" int32_t tq_decode_step_dev(tq_ctx *ctx, const void *q, const void *k_
 
 extern "C" int32_t tq_dequant(tq_ctx *ctx, const tq_cache_desc *cache, int32_t which, int32_t pos0,
                               int32_t n_tokens, const tq_dense_desc *out, tq_stream stream) {
+    TqRange range_("tq_dequant");
     if (!ctx || !out || !out->data) return TQ_ERR_ARG;
     int rc = tq_check_cache(ctx, cache);
     if (rc) return rc;

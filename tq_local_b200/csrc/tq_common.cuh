@@ -52,6 +52,16 @@ void tq_prof_count(tq_ctx *ctx, int n_launches);
 
 void tq_set_cuda_error(cudaError_t e, const char *where);
 
+// Named NVTX range around the host side of an entry point (header-only NVTX: a no-op unless a
+// profiler is attached), so that a timeline shows pack / append / decode / gather calls by name.
+#include <nvtx3/nvToolsExt.h>
+struct TqRange {
+    explicit TqRange(const char *name) { nvtxRangePushA(name); }
+    ~TqRange() { nvtxRangePop(); }
+    TqRange(const TqRange &) = delete;
+    TqRange &operator=(const TqRange &) = delete;
+};
+
 #define TQ_CUDA_CHECK(expr)                         \
     do {                                            \
         cudaError_t _e = (expr);                    \

@@ -53,6 +53,7 @@ extern "C" size_t tq_static_scratch_bytes(void) { return kStaticScratchBytes; }
 extern "C" int32_t tq_decode_attn_static(tq_ctx *ctx, const void *q, int32_t q_dtype, int32_t q_heads,
                                          const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits, void *out,
                                          tq_stream stream) {
+    TqRange range_("tq_decode_attn_static");
     if (!ctx || !q || !out) return TQ_ERR_ARG;
     int32_t rc = tq_check_cache(ctx, cache);  // the same descriptor checks as tq_decode_attn
     if (rc) return rc;

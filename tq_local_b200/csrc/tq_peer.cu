@@ -56,6 +56,7 @@ extern "C" int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_d
                                          const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits,
                                          void *workspace, size_t workspace_bytes, const tq_gather_desc *gather,
                                          tq_stream stream) {
+    TqRange range_("tq_decode_attn_gather");
     if (!ctx || !q || !workspace) return TQ_ERR_ARG;
     int rc = tq_check_gather(gather);
     if (rc) return rc;
@@ -74,6 +75,7 @@ extern "C" int32_t tq_decode_attn_gather(tq_ctx *ctx, const void *q, int32_t q_d
 
 extern "C" int32_t tq_gather_wait(tq_ctx *ctx, const tq_gather_desc *gather, int32_t batch, int32_t dtype,
                                   void *out_final, tq_stream stream) {
+    TqRange range_("tq_gather_wait");
     if (!ctx) return TQ_ERR_ARG;
     int rc = tq_check_gather(gather);
     if (rc) return rc;
@@ -102,6 +104,7 @@ extern "C" int32_t tq_decode_attn_parts(tq_ctx *ctx, const void *q, int32_t q_dt
                                         const tq_cache_desc *cache, int32_t seq_len, int32_t n_splits, void *workspace,
                                         size_t workspace_bytes, const tq_gather_desc *gather, int32_t parts,
                                         tq_stream stream) {
+    TqRange range_("tq_decode_attn_parts");
     if (!ctx || !q || !workspace) return TQ_ERR_ARG;
     int rc = check_parts(gather, parts, q_heads);
     if (rc) return rc;
@@ -131,6 +134,7 @@ extern "C" int32_t tq_decode_attn_parts(tq_ctx *ctx, const void *q, int32_t q_dt
 
 extern "C" int32_t tq_decode_parts_finish(tq_ctx *ctx, const tq_gather_desc *gather, int32_t batch, int32_t dtype,
                                           int32_t parts, int32_t heads_per_block, void *out, tq_stream stream) {
+    TqRange range_("tq_decode_parts_finish");
     if (!ctx || !out || batch <= 0 || ((uintptr_t)out & 15)) return TQ_ERR_ARG;
     if (dtype != TQ_DTYPE_F16 && dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
     int rc = tq_check_gather(gather);

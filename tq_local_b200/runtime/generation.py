@@ -76,8 +76,6 @@ def validate_generation_variant(variant: str) -> None:
         raise ValueError(
             f"Unsupported generation variant={variant!r}. Choose from ['baseline', 'qmse', 'qmse_packed']."
         )
-    if variant == "qmse":
-        raise NotImplementedError("the unpacked 'qmse' variant is not provided; use 'qmse_packed'")
 
 
 def eos_token_ids(model, tokenizer) -> set[int]:
@@ -357,12 +355,21 @@ def greedy_decode_with_prefill_cache(
             dense_breakdown = streamed_prefill_memory_breakdown(packed_cache)
         else:
             dense_breakdown = past_key_values_memory_breakdown(cache)
-        if variant == "qmse_packed":
+        if variant == "qmse":
+            # unpacked variant (reference: generation.py:104-113): the prompt's dense cache is replaced by
+            # its quantise-dequantise reconstruction; nothing is packed, attention stays the model's own
+            from tq_local_b200.quantization.turboquant_mse import quantize_past_key_values_mse
+
+            t0 = time.monotonic()
+            cache = quantize_past_key_values_mse(cache, bits=qmse_bits, seed=rotation_seed)
+            quant_seconds += time.monotonic() - t0
+        if variant in ("qmse", "qmse_packed"):
             estimate = turboquant_mse_packed_bytes(
                 num_vectors_per_kind=dense_breakdown["num_key_value_vectors_per_kind"],
                 vector_dimension=dense_breakdown["vector_dimension"],
                 bits=qmse_bits,
             )
+        if variant == "qmse_packed":
             t0 = time.monotonic()
             if not streaming:
                 packed_cache = build_packed_mse_cache(
@@ -419,6 +426,11 @@ def greedy_decode_with_prefill_cache(
                     mask = torch.cat((mask, mask.new_ones((mask.shape[0], 1))), dim=-1)
                 out = model(input_ids=next_token, attention_mask=mask, past_key_values=cache, use_cache=True)
                 cache = out.past_key_values
+                if variant == "qmse":  # the token just appended gets quantised in place (generation.py:170-178)
+                    t0 = time.monotonic()
+                    cache = quantize_past_key_values_mse(cache, bits=qmse_bits, seed=rotation_seed,
+                                                         token_slice=slice(-1, None))
+                    quant_seconds += time.monotonic() - t0
                 next_token = torch.argmax(out.logits[:, -1, :], dim=-1, keepdim=True)
                 generated.append(next_token)
             if packed_cache is not None and torch.cuda.is_available():
@@ -449,7 +461,7 @@ def greedy_decode_with_prefill_cache(
     text = tokenizer.decode(completion[0, :row0_len], skip_special_tokens=True).strip()
     metrics = GenerationMetrics(
         variant=variant,
-        qmse_bits=qmse_bits if variant == "qmse_packed" else None,
+        qmse_bits=qmse_bits if variant in ("qmse", "qmse_packed") else None,
         quantization_seconds=round(quant_seconds, 4),
         generation_seconds=round(time.monotonic() - started, 4),
         prompt_tokens=int(inputs["input_ids"].shape[-1]),

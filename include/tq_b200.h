@@ -306,7 +306,8 @@ int32_t tq_set_wait_limit_ms(tq_ctx *ctx, int32_t limit_ms);
  * call synchronises with the device and returns that word: 0 = no kernel ever gave up;
  * 1 = a decode kernel's wait ran out; 2 = a decode kernel found that its shared-memory layout
  * does not fit and did not run; 3 = the encoder's wait ran out; 4 = an append addressed a
- * token past the cache's capacity and was dropped; 5 = tq_gather_wait gave up waiting for a peer.
+ * token past the cache's capacity and was dropped; 5 = tq_gather_wait gave up waiting for a peer;
+ * 6 = (bounds-checked build only) a kernel was about to read or write outside a buffer and did not.
  * The word is sticky for the context. */
 int32_t tq_device_status(tq_ctx *ctx, int32_t *status_out);
 

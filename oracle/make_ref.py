@@ -53,7 +53,8 @@ def install(reference: str, force: bool = False) -> str:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("TQ_REFERENCE_SRC"), required="TQ_REFERENCE_SRC" not in os.environ,
+                    help="root of the unmodified reference checkout")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     print(install(a.reference, a.force))

@@ -222,3 +222,23 @@ def test_one_process_two_devices(setup_golden):
             torch.cuda.synchronize(dev)
             assert codec.device_status() == 0
     assert torch.equal(outs[0], outs[1])
+
+
+def test_a_sample_of_the_suite_on_the_bounds_checked_build():
+    """The same sources built with -DTQ_DEBUG_BOUNDS check every bulk-copy request and every stored
+    partial of the decode kernel against the buffers' extents (a violation is recorded as status 6
+    and the access dropped).  The ragged-length, many-rows and left-padding cases run on that build
+    in a child process; they assert a clean status word themselves."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = os.path.join(root, "tq_local_b200", "libtq_b200_checked.so")
+    assert os.path.isfile(lib), "build it with `python -m tq_local_b200.build --checked`"
+    env = dict(os.environ, TQ_B200_LIBRARY=lib)
+    out = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_parity.py"), "-m", "gpu",
+                          "-x", "-q", "-k", "ragged or seeded or left_padded"], capture_output=True, text=True,
+                         timeout=900, env=env, cwd=root)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-2000:]
+    assert " passed" in out.stdout and "failed" not in out.stdout

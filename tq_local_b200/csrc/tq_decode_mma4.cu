@@ -276,6 +276,23 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
         const uint32_t dst = slot_u32(st), bar = full_u32 + st * 8;
         const int64_t r = sg.row0 + base;
         const uint32_t total = n * (16 * KB + 16 * VB + 4 + (QJL ? 18 : 0));
+#ifdef TQ_DEBUG_BOUNDS
+        // Checked build: every bulk copy must read tokens [base, base + n) of a real row, inside the
+        // row's allocation, and land inside this CTA's ring slot.  A request that does not is recorded
+        // (status 6), dropped, and its barrier completed by hand so that nobody waits for it.
+        {
+            uint32_t dyn_size;
+            asm("mov.u32 %0, %%dynamic_smem_size;\n" : "=r"(dyn_size));
+            const bool ok = sg.bh >= 0 && sg.bh < a.rows && base >= 0 && n > 0 && n <= kGroupTok &&
+                            base + n <= a.capacity && dst >= dyn_base && dst + L::kBytes <= dyn_base + dyn_size &&
+                            (dst + L::kBytes <= kTableAddr || dst >= kTableAddr + kTableBytes);
+            if (!ok) {
+                atomicExch(a.error_flag, 6);
+                mbar_arrive(bar);
+                return;
+            }
+        }
+#endif
         mbar_expect_tx(bar, total);
         tma_load_1d(dst + L::kK, a.k_codes + r * (16 * KB), n * 16 * KB, bar);
         tma_load_1d(dst + L::kV, a.v_codes + r * (16 * VB), n * 16 * VB, bar);
@@ -608,6 +625,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
                 A += s_acc[w * 4 * TQ_D + idx] * sc;
             }
             const int64_t prow = (q_row0 + hh) * a.n_splits + split;
+#ifdef TQ_DEBUG_BOUNDS
+            if (split < 0 || split >= a.n_splits || q_row0 + hh >= (int64_t)a.rows * G) {  // a partial slot the workspace does not have
+                atomicExch(a.error_flag, 6);
+                continue;
+            }
+#endif
             a.part_acc[prow * TQ_D + d] = A;
             if (d == 0) a.part_m[prow] = M * 0.6931471805599453f, a.part_l[prow] = Lsum;  // natural-log units
         }

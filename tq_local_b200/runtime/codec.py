@@ -130,6 +130,7 @@ class Codec:
         3: "the encoder's wait ran out",
         4: "an append addressed a token past the cache's capacity and was dropped",
         5: "the wait for a peer's attention outputs ran out (tq_gather_wait)",
+        6: "the bounds-checked build stopped a kernel from reading or writing outside a buffer",
     }
 
     def raise_on_device_status(self, where: str) -> None:

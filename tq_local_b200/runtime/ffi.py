@@ -11,7 +11,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG, "libtq_b200.so")
+# TQ_B200_LIBRARY selects another build of the same library (the bounds-checked one, see build.py)
+LIB_PATH = os.environ.get("TQ_B200_LIBRARY") or os.path.join(_PKG, "libtq_b200.so")
 
 TQ_DTYPE_F32, TQ_DTYPE_F16, TQ_DTYPE_BF16 = 0, 1, 2
 TQ_MAX_GROUPS = 8

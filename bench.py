@@ -408,15 +408,9 @@ def run_gpu_arm(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
 
-    # The timed region lasts a few milliseconds, too short for more than one clock sample: keep the
-    # identical steps running (untimed) for about half a second so that the clock / throttle record
-    # describes this load.  (Same count on every rank: the steps synchronise the ranks.)
-    for _ in range(min(20000, max(steps, int(0.5 / max(ms * 1e-3, 1e-6))))):
-        step()
-    fence()
-
-    # ---- same steps again with the library's hooks on: CUDA events around the main kernel
-    # (on its launch stream) give the roofline numerator; every launch is counted
+    # ---- same steps again, straight after the timed ones (same clocks), with the library's hooks
+    # on: CUDA events around the main kernel (on its launch stream) give the roofline numerator;
+    # every launch is counted
     codec.profile(True)
     fence()
     for _ in range(steps):
@@ -424,6 +418,13 @@ def run_gpu_arm(args) -> None:
     fence()
     main_ms, main_n, all_launches = codec.profile_read()
     codec.profile(False)
+
+    # The timed region lasts a few milliseconds, too short for more than one clock sample: keep the
+    # identical steps running (untimed) for about half a second so that the clock / throttle record
+    # describes this load.  (Same count on every rank: the steps synchronise the ranks.)
+    for _ in range(min(20000, max(steps, int(0.5 / max(ms * 1e-3, 1e-6))))):
+        step()
+    fence()
 
     # ---- end to end: host buffers in, host buffer out, one new token appended per step
     pin = dict(dtype=dtype, pin_memory=True)

@@ -231,8 +231,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     const int64_t flat_begin = (int64_t)blockIdx.x * chunk;
     const int64_t flat_end = min(flat_begin + chunk, (int64_t)a.rows * n_pad);
 
-    // ---- ring set-up: group gq owns slots gq * kStages + s
-    const int gq = warp / kGroupWarps, wq = warp % kGroupWarps;
+    // ---- ring set-up: group gq owns slots gq * kStages + s.  A group is the warps gq, gq + kGroups,
+    // gq + 2 * kGroups, ...: with four groups these are the four warps of one of the SM's four warp
+    // schedulers, so the schedulers carry identical loads and the groups finish together (with
+    // consecutive warps per group every scheduler held one warp of each group, the groups ran at
+    // different rates and the slowest one finished 4.5 us after the fastest, alone on the SM).
+    const int gq = warp % kGroups, wq = warp / kGroups;
     auto slot_u32 = [&](int st) -> uint32_t {
         const int q = gq * kStages + st;
         return q < slots_low ? dyn_base + q * L::kBytes : high_base + (q - slots_low) * L::kBytes;

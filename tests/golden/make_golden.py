@@ -159,6 +159,59 @@ def main() -> None:
         np.savez_compressed(os.path.join(here, f"layer_{name}.npz"), **out)
         print(name, "ok", {k_: v_.shape for k_, v_ in out.items() if hasattr(v_, "shape") and v_.ndim > 1 and "codes" in k_})
 
+    # ---------------- outlier-channel split (num_outlier_channels > 0) ----------------------------
+    ocases = [
+        # name, bits, qjl, dtype, n_outlier, extra_bits, B, Hq, Hkv, S, n_append, seed
+        ("mse3_o8_f32", 3, False, torch.float32, 8, 1, 2, 4, 2, 21, 2, 11),
+        ("prod4_o16_bf16", 4, True, torch.bfloat16, 16, 1, 1, 8, 2, 26, 2, 12),
+        ("prod3_o32_f16", 3, True, torch.float16, 32, 2, 1, 4, 2, 19, 1, 13),
+    ]
+    for name, bits, qjl, dtype, n_out, extra, B, Hq, Hkv, S, n_app, seed in ocases:
+        k, v, q = synth(B, Hq, Hkv, S + n_app, seed, dtype)
+        # a few channels carry more energy, as outlier channels of a real model do
+        gg = torch.Generator().manual_seed(1000 + seed)
+        boost = torch.ones(128)
+        boost[torch.randperm(128, generator=gg)[:n_out]] = 4.0
+        k, v = (k.float() * boost).to(dtype), (v.float() * boost).to(dtype)
+        out = {"bits": np.int64(bits), "qjl": np.int64(qjl), "n_outlier": np.int64(n_out), "extra_bits": np.int64(extra),
+               "B": np.int64(B), "Hq": np.int64(Hq), "Hkv": np.int64(Hkv), "S": np.int64(S), "n_append": np.int64(n_app),
+               "dtype": np.array(str(dtype).replace("torch.", ""))}
+        store(k, "k", out)
+        store(v, "v", out)
+        store(q, "q", out)
+        layer = pc.PackedMSELayer(bits=bits, seed=0, num_outlier_channels=n_out, outlier_extra_bits=extra,
+                                  use_qjl_keys=qjl, quantize_decode=True)
+        layer.initialize_from_dense(k[:, :, :S].contiguous(), v[:, :, :S].contiguous())
+        out["outlier_indices"] = layer._outlier_indices.numpy().copy()
+        out["normal_indices"] = layer._normal_indices.numpy().copy()
+        groups = Hq // Hkv
+
+        def odump(tag):
+            for part, kp, vp, kq in (("n", layer.keys_packed, layer.values_packed, layer._keys_qjl),
+                                     ("o", layer._keys_outlier, layer._values_outlier, layer._keys_outlier_qjl)):
+                out[f"{tag}_{part}_k_codes"] = kp.packed_indices.numpy().copy()
+                out[f"{tag}_{part}_k_norms_bits16"] = bits16(kp.norms)
+                out[f"{tag}_{part}_v_codes"] = vp.packed_indices.numpy().copy()
+                out[f"{tag}_{part}_v_norms_bits16"] = bits16(vp.norms)
+                if qjl:
+                    out[f"{tag}_{part}_k_signs"] = kq.packed_signs.numpy().copy()
+                    out[f"{tag}_{part}_k_rnorms_bits16"] = bits16(kq.residual_norms)
+            out[f"{tag}_storage_bytes"] = np.int64(layer.storage_bytes())
+            store(layer._decode_keys_full(), f"{tag}_k_dequant", out)
+            store(layer._decode_values_full(), f"{tag}_v_dequant", out)
+            store(chunked_turboquant_attention(q, layer, n_kv_groups=groups, chunk_size=8), f"{tag}_attn_chunked", out)
+
+        odump("prefill")
+        # (the reference's lazy update does not serve a split layer; its eager update does and
+        # hands back the dequantised history followed by the new token)
+        for t in range(n_app):
+            ret_k, ret_v = layer.update(k[:, :, S + t:S + t + 1].contiguous(), v[:, :, S + t:S + t + 1].contiguous())
+        store(ret_k, "update_ret_k", out)
+        store(ret_v, "update_ret_v", out)
+        odump("appended")
+        np.savez_compressed(os.path.join(here, f"outlier_{name}.npz"), **out)
+        print("outlier", name, "ok")
+
     # ---------------- norm guard -----------------------------------------------------
     ng: dict[str, np.ndarray] = {}
     k, v, _ = synth(1, 4, 4, 64, 11, torch.float32, mode="asym")

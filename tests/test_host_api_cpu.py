@@ -90,8 +90,9 @@ def test_activate_rejects_bad_models():
     with pytest.raises(ValueError, match="not compatible"):
         turboquant.activate(model, StubTokenizer(), quiet=True)
     model.config.use_cache = True
-    with pytest.raises(NotImplementedError):
-        turboquant.activate(model, StubTokenizer(), quiet=True, num_outlier_channels=8)
+    turboquant.activate(model, StubTokenizer(), quiet=True, num_outlier_channels=8)
+    assert model._tq_state.num_outlier_channels == 8
+    turboquant.deactivate(model)
     report = turboquant.inspect_transformers_model_compatibility(model)
     assert report.compatible and report.backend == "transformers" and report.details["num_key_value_heads"] == 2
 
@@ -162,8 +163,8 @@ def test_norm_threshold_and_layer_interface():
     assert layer.get_seq_length() == 0 and layer.get_max_cache_shape() == -1 and layer.is_sliding is False
     assert layer.get_mask_sizes(3) == (3, 0) and layer.get_mask_sizes(torch.arange(2)) == (2, 0)
     assert layer.keys_packed is None and layer.storage_bytes() == 0
-    with pytest.raises(NotImplementedError):
-        PackedMSELayer(bits=4, num_outlier_channels=4)
+    split = PackedMSELayer(bits=4, num_outlier_channels=4)
+    assert not split._outlier_enabled and split.keys_packed is None  # (decided with the first tensors it sees)
     # force-dense layers never touch the GPU
     k = torch.randn(1, 2, 6, 128)
     layer.initialize_from_dense(k, k, force_dense=True)

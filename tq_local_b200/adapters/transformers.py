@@ -240,8 +240,6 @@ def activate(model, tokenizer=None, *, bits: int = 4, rotation_seed: int = 0, nu
     report = inspect_transformers_model_compatibility(model)
     if not report.compatible:
         raise ValueError(f"Model is not compatible with TurboQuant: {report.reasons}")
-    if num_outlier_channels:
-        raise NotImplementedError("outlier-channel splitting is not provided by the B200 kernels")
     if tokenizer is None:
         name = getattr(model.config, "_name_or_path", None)
         if not name:

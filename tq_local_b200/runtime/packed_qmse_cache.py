@@ -15,7 +15,8 @@ reference                                    here
 ``fused_attention`` / chunked fallback          ``tq_decode_attn`` (:meth:`PackedMSELayer.attend`)
 ===========================================  ==========================================
 
-Outlier-channel splitting (``num_outlier_channels > 0``) is not part of this library.
+Outlier-channel splitting (``num_outlier_channels > 0``) is served by ``outlier_split.SplitStore``
+(tensor arithmetic on the cache's device; the kernels handle 128-coordinate vectors only).
 """
 
 from __future__ import annotations
@@ -146,8 +147,8 @@ class PackedMSELayer(CacheLayerMixin):
         shard: HeadShard | None = None,
     ):
         super().__init__()
-        if num_outlier_channels:
-            raise NotImplementedError("outlier-channel splitting is not provided by the B200 kernels")
+        if num_outlier_channels and shard is not None and shard.world_size > 1:
+            raise NotImplementedError("the outlier-channel split is not available for a sharded cache")
         self.is_initialized = False
         self.bits = bits
         self.seed = seed
@@ -178,39 +179,57 @@ class PackedMSELayer(CacheLayerMixin):
         self._prefill_shape: tuple[int, ...] | None = None
         self._static_kv: tuple[torch.Tensor, torch.Tensor] | None = None
         self._static_gather = None
+        self._split = False  # outlier-channel split in use (see lazy_initialization)
 
     # ---------------------------------------------------------------- reference attributes
     @property
     def _outlier_enabled(self) -> bool:
-        return False
+        """Whether this layer splits off outlier channels (decided with the first tensors it sees:
+        the reference needs ``0 < num_outlier_channels < head_dim``, packed_qmse_cache.py:243)."""
+        return self._split
+
+    def _table(self, name: str, key_side: bool = False):
+        if key_side and not self.use_qjl_keys:
+            return None
+        if self._split:
+            return getattr(self.store.normal, name) if self.store is not None else None
+        return self.codec.table(name) if self.codec else None
 
     @property
     def rotation(self):
-        return self.codec.table("rot_v") if self.codec else None
+        return self._table("rot_v")
 
     @property
     def centers(self):
-        return self.codec.table("cen_v") if self.codec else None
+        return self._table("cen_v")
 
     @property
     def boundaries(self):
-        return self.codec.table("bnd_v") if self.codec else None
+        return self._table("bnd_v")
 
     @property
     def _key_rotation(self):
-        return self.codec.table("rot_k") if self.codec and self.use_qjl_keys else None
+        return self._table("rot_k", True)
 
     @property
     def _key_centers(self):
-        return self.codec.table("cen_k") if self.codec and self.use_qjl_keys else None
+        return self._table("cen_k", True)
 
     @property
     def _key_boundaries(self):
-        return self.codec.table("bnd_k") if self.codec and self.use_qjl_keys else None
+        return self._table("bnd_k", True)
 
     @property
     def _qjl_matrix(self):
-        return self.codec.table("qjl") if self.codec and self.use_qjl_keys else None
+        return self._table("qjl", True)
+
+    @property
+    def _outlier_indices(self):
+        return self.store.outlier.index if self._split and self.store is not None else None
+
+    @property
+    def _normal_indices(self):
+        return self.store.normal.index if self._split and self.store is not None else None
 
     @property
     def _dense_keys(self):
@@ -224,8 +243,24 @@ class PackedMSELayer(CacheLayerMixin):
         s = self.store
         return (s.batch, s.kv_heads, s.length, 128)
 
+    def _group_view(self, group: int, which: str):
+        """The reference's view of one channel group of a split layer (0: the normal channels,
+        1: the outlier channels; packed_qmse_cache.py:199-213,351-358)."""
+        s = self.store
+        if not self._split or s is None or s.length == 0 or (which == "qjl" and not self.use_qjl_keys):
+            return None
+        gs, n = s.groups[group], s.length
+        shape = (s.batch, s.kv_heads, n, gs.g.dim)
+        if which == "keys":
+            return PackedTensorMSE(gs.k_codes[:, :, :n], gs.k_norms[:, :, :n], shape, self.dtype, gs.g.key_bits)
+        if which == "values":
+            return PackedTensorMSE(gs.v_codes[:, :, :n], gs.v_norms[:, :, :n], shape, self.dtype, gs.g.bits)
+        return PackedQJL(gs.k_signs[:, :, :n], gs.k_rnorms[:, :, :n], gs.g.dim)
+
     @property
     def keys_packed(self) -> PackedTensorMSE | None:
+        if self._split:
+            return self._group_view(0, "keys")
         s = self.store
         if s is None or s.length == 0:
             return None
@@ -234,6 +269,8 @@ class PackedMSELayer(CacheLayerMixin):
 
     @property
     def values_packed(self) -> PackedTensorMSE | None:
+        if self._split:
+            return self._group_view(0, "values")
         s = self.store
         if s is None or s.length == 0:
             return None
@@ -242,11 +279,25 @@ class PackedMSELayer(CacheLayerMixin):
 
     @property
     def _keys_qjl(self) -> PackedQJL | None:
+        if self._split:
+            return self._group_view(0, "qjl")
         s = self.store
         if s is None or s.length == 0 or not self.use_qjl_keys:
             return None
         n = s.length
         return PackedQJL(s.k_signs[:, :, :n], s.k_rnorms[:, :, :n], 128)
+
+    @property
+    def _keys_outlier(self) -> PackedTensorMSE | None:
+        return self._group_view(1, "keys")
+
+    @property
+    def _values_outlier(self) -> PackedTensorMSE | None:
+        return self._group_view(1, "values")
+
+    @property
+    def _keys_outlier_qjl(self) -> PackedQJL | None:
+        return self._group_view(1, "qjl")
 
     # ---------------------------------------------------------------- set-up
     def lazy_initialization(self, key_states: torch.Tensor, value_states: torch.Tensor) -> None:
@@ -254,15 +305,30 @@ class PackedMSELayer(CacheLayerMixin):
         (reference: packed_qmse_cache.py:237-283)."""
         self.dtype = key_states.dtype
         self.device = key_states.device
-        self.codec = Codec.get(self.device, self.bits, self.use_qjl_keys, self.seed, self.grid_size,
-                               int(key_states.shape[-1]))
+        self._split = 0 < self.num_outlier_channels < int(key_states.shape[-1])
+        if not self._split:  # (a split layer is served by tensor arithmetic: it needs no kernel context)
+            self.codec = Codec.get(self.device, self.bits, self.use_qjl_keys, self.seed, self.grid_size,
+                                   int(key_states.shape[-1]))
         self.is_initialized = True
 
-    def _ensure_store(self, key_states: torch.Tensor) -> None:
+    def _new_store(self, key_states: torch.Tensor, value_states: torch.Tensor, batch: int, heads: int, capacity: int):
+        if self._split:
+            # the outlier channels are chosen on these very tensors: the first K/V the layer sees
+            # (packed_qmse_cache.py:243-247)
+            from tq_local_b200.runtime import ffi, outlier_split
+            from tq_local_b200.runtime.outlier_split import SplitStore
+
+            if key_states.device.type != "cuda" and not outlier_split.HOST_TENSORS_FOR_TESTS:
+                raise ffi.TQError("TurboQuant-B200 runs on CUDA devices only; there is no CPU path")
+            return SplitStore(key_states, value_states, self.bits, self.num_outlier_channels, self.outlier_extra_bits,
+                              self.use_qjl_keys, self.seed, self.grid_size, batch, capacity)
+        return PackedStore(self.codec, batch, heads, capacity)
+
+    def _ensure_store(self, key_states: torch.Tensor, value_states: torch.Tensor | None = None) -> None:
         if self.store is None:
             local = self.shard.local_tokens(self.shard.local_kv(key_states), int(key_states.shape[1]), self._tokens_seen)
             cap = int(local.shape[2]) + self.reserve_tokens
-            self.store = PackedStore(self.codec, int(local.shape[0]), int(local.shape[1]), cap)
+            self.store = self._new_store(key_states, value_states, int(local.shape[0]), int(local.shape[1]), cap)
             self._kv_heads_total = int(key_states.shape[1])
 
     @property
@@ -291,7 +357,7 @@ class PackedMSELayer(CacheLayerMixin):
             return
         if not self.is_initialized:
             self.lazy_initialization(key_states, value_states)
-        self._ensure_store(key_states)
+        self._ensure_store(key_states, value_states)
         self.store.pack(*self._local(key_states, value_states))
 
     # ---------------------------------------------------------------- replayable decode
@@ -299,7 +365,8 @@ class PackedMSELayer(CacheLayerMixin):
         """Whether this layer can serve decode steps whose length lives on the device (packed,
         quantised appends, 16-bit cache, at most 8 query heads per KV head).  A sharded layer
         additionally needs a device-sequenced ``PeerGather`` (see ``begin_static_decode``)."""
-        return (self.store is not None and not self._force_dense and self.quantize_decode and self.seq_parts == 1
+        return (self.store is not None and not self._split and not self._force_dense and self.quantize_decode
+                and self.seq_parts == 1
                 and self._dense_k.length == 0 and self.dtype in (torch.float16, torch.bfloat16)
                 and q_heads // self._kv_heads_total <= 8)
 
@@ -350,7 +417,7 @@ class PackedMSELayer(CacheLayerMixin):
             return self._update_dense_decode(key_states, value_states)
         # Eager path: hand back the dequantised history plus the new token, then store it.
         prev_k, prev_v = self._decode_keys_full(), self._decode_values_full()
-        self._ensure_store(key_states)
+        self._ensure_store(key_states, value_states)
         if self.seq_parts > 1:
             raise NotImplementedError("a sequence-split cache serves attention through the 'turboquant' backend only "
                                       "(enable_turboquant_attention); it cannot hand back dequantised history")
@@ -391,8 +458,9 @@ class PackedMSELayer(CacheLayerMixin):
         seen = self._tokens_seen
         local_k, local_v = self._local(key_states, value_states)
         self._tokens_seen = seen  # (every row block brings the same token positions; finish_prefill counts them once)
-        if self.store is None:
-            self.store = PackedStore(self.codec, total, int(local_k.shape[1]), int(local_k.shape[2]) + self.reserve_tokens)
+        if self.store is None:  # (a split layer chooses its outlier channels on this first block)
+            self.store = self._new_store(key_states, value_states, total, int(local_k.shape[1]),
+                                         int(local_k.shape[2]) + self.reserve_tokens)
         self.store.pack_rows(local_k, local_v, b0, 0)
         self._window_local = int(local_k.shape[2])
 
@@ -417,7 +485,7 @@ class PackedMSELayer(CacheLayerMixin):
         """Store the new token without touching history (reference: packed_qmse_cache.py:626-679):
         quantised in place when ``quantize_decode``, otherwise appended to the dense tail."""
         if self.quantize_decode:
-            self._ensure_store(key_states)
+            self._ensure_store(key_states, value_states)
             self.store.pack(*self._local(key_states, value_states))
         else:
             if self.seq_parts > 1:

@@ -173,9 +173,10 @@ template <int VB> __device__ __forceinline__ uint64_t lds_v_chunk(const uint8_t 
         return *reinterpret_cast<const unsigned long long *>(row + 8 * g);
     } else if (VB == 2) {
         return *reinterpret_cast<const unsigned int *>(row + 4 * g);
-    } else {  // 3 bits: 6 bytes at byte 6g, as three 16-bit reads
-        const uint16_t *p = reinterpret_cast<const uint16_t *>(row + 6 * g);
-        return (uint64_t)p[0] | ((uint64_t)p[1] << 16) | ((uint64_t)p[2] << 32);
+    } else {  // 3 bits: 6 bytes at byte 6g, inside the two aligned words that start at 6g rounded down to 4
+        const uint32_t *p = reinterpret_cast<const uint32_t *>(row + ((6 * g) & ~3));
+        const uint64_t w = (uint64_t)p[0] | ((uint64_t)p[1] << 32);
+        return (g & 1) ? w >> 16 : w;  // (what lies beyond the 48 bits is never looked at)
     }
 }
 

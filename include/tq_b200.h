@@ -203,8 +203,9 @@ int32_t tq_key_norm_sum(const tq_dense_desc *k, int32_t batch, int32_t heads, in
  * single-GPU).  Rank r serves kv_heads / world KV heads and their query heads; the only exchange
  * per decode step is the per-head attention outputs.  tq_decode_attn_gather fuses that exchange
  * into the combine kernel: every block stores its finished rows straight into the gathered-output
- * buffer of EVERY rank (plain stores to peer memory over NVLink) and then, after a system-scope
- * fence, adds the number of rows it stored to this rank's word in every rank's flag block.
+ * buffer of EVERY rank (plain stores to peer memory over NVLink) and then adds the number of rows
+ * it stored to this rank's word in every rank's flag block, with a release reduction at system
+ * scope (the waiting side reads the words with acquire loads).
  * tq_gather_wait (one small kernel, stream-ordered before the consumer of the gathered output)
  * waits - with a time limit, reporting through tq_device_status (5) instead of hanging - until
  * every rank's word has reached step * batch * (q_heads_total / world): all rows of the step are

@@ -306,6 +306,22 @@ __global__ void __launch_bounds__(4 * TQ_D, 2) tq_step_prologue_kernel(TqQprepAr
 
 // Split combine for up to four heads of one (batch, KV head) row per block (no dense tail):
 // the un-rotation matrix is read once for the G heads.
+// Publishing rows to the peers and waiting for theirs (system scope, PTX memory model):
+// a block's threads store their rows with plain stores, the block barrier orders those stores
+// before thread 0, which adds the block's row count to the flag word with a RELEASE reduction at
+// system scope (cumulative over what the barrier ordered before it); the waiting side polls the
+// word with ACQUIRE loads at system scope, and its own block barrier orders the data reads of
+// the other threads behind the observation.  No separate fence on either side: on a B200 pair
+// the two full system fences this replaces cost 3.3 us of a 92 us step.
+__device__ __forceinline__ void tq_release_add_sys(unsigned *word, unsigned value) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;\n" ::"l"(word), "r"(value) : "memory");
+}
+__device__ __forceinline__ unsigned tq_acquire_load_sys(const unsigned *word) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(word) : "memory");
+    return v;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs a) {
     __shared__ __align__(16) float s_o[4][TQ_D];
@@ -387,10 +403,8 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
     }
     if (a.parts > 0) {  // report the rows (see the gather below) and leave: nothing is finished here
         __syncthreads();
-        if (tid == 0) {
-            __threadfence_system();
-            for (int p = 0; p < a.gather_world; ++p) atomicAdd_system(a.gather_flags[p] + a.gather_rank, (unsigned)n_heads);
-        }
+        // (lane p of the first warp reports to rank p: one instruction, so one wait for the stores)
+        if (tid < a.gather_world) tq_release_add_sys(a.gather_flags[tid] + a.gather_rank, (unsigned)n_heads);
         return;
     }
     __syncthreads();
@@ -440,10 +454,10 @@ __global__ void __launch_bounds__(4 * TQ_D) tq_combine_group_kernel(CombineArgs 
         // every peer's flag block.  A peer has all of this rank's rows of step s once that word has
         // reached s * (rows per step); no block waits for another, no counter round trip.
         __syncthreads();
-        if (tid == 0) {
-            __threadfence_system();
-            for (int p = 0; p < a.gather_world; ++p) atomicAdd_system(a.gather_flags[p] + a.gather_rank, (unsigned)n_heads);
-        }
+        // (lane p of the first warp reports to rank p: the release reductions of all peers are one
+        // instruction and wait for the block's stores once; one after the other they cost one such
+        // wait per peer)
+        if (tid < a.gather_world) tq_release_add_sys(a.gather_flags[tid] + a.gather_rank, (unsigned)n_heads);
     }
 }
 
@@ -474,16 +488,14 @@ __global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned
     __syncthreads();
     if ((int)threadIdx.x < world) {
         const unsigned long long t0 = tq_global_ns();
-        const volatile unsigned *f = flags + threadIdx.x;
         unsigned polls = 0;
-        while ((int)(*f - target) < 0) {  // (the words only grow; a peer may already be a step ahead)
+        while ((int)(tq_acquire_load_sys(flags + threadIdx.x) - target) < 0) {  // (the words only grow; a peer may already be a step ahead)
             if ((++polls & 63u) == 0 && tq_global_ns() - t0 > limit_ns) {
                 atomicExch(error_flag, 5);
                 s_failed = 1;
                 break;
             }
         }
-        __threadfence_system();
     }
     __syncthreads();
     if (dst && !s_failed) {

@@ -210,7 +210,10 @@ def test_one_process_two_devices(setup_golden):
     from tq_local_b200.runtime.codec import Codec
     from tq_local_b200.runtime.packed_store import PackedStore
 
+    import gc
+
     outs = []
+    current = torch.cuda.current_device()
     k, v, q = O.synth_kvq(2, 8, 2, 700, 128, seed=5, dtype=torch.bfloat16)
     for idx in (0, 1):
         dev = torch.device("cuda", idx)
@@ -222,6 +225,14 @@ def test_one_process_two_devices(setup_golden):
             torch.cuda.synchronize(dev)
             assert codec.device_status() == 0
     assert torch.equal(outs[0], outs[1])
+    # creating a context on another device, and destroying it whenever the collector gets to it,
+    # leaves the process's current device alone
+    created = Codec(torch.device("cuda", 1), 4, True, seed=0, rot_v=setup_golden.z["rotation_s0"],
+                    rot_k=setup_golden.z["rotation_s1"])
+    assert torch.cuda.current_device() == current
+    del created, codec, store
+    gc.collect()
+    assert torch.cuda.current_device() == current
 
 
 def test_a_sample_of_the_suite_on_the_bounds_checked_build():

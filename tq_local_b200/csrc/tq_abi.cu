@@ -72,12 +72,31 @@ extern "C" int32_t tq_profile_read(tq_ctx *ctx, double *main_ms, int64_t *main_l
 }
 extern "C" int32_t tq_abi_version(void) { return 1; }
 
+namespace {
+// Makes `device` current for the lifetime of the guard and puts the caller's device back
+// afterwards: creating or destroying a context must not change the device the host program
+// (PyTorch, say) believes to be current - least of all from a destructor run by a garbage collector.
+struct DeviceGuard {
+    int previous = -1;
+    cudaError_t status;
+    explicit DeviceGuard(int device) {
+        status = cudaGetDevice(&previous);
+        if (status == cudaSuccess && previous != device) status = cudaSetDevice(device);
+        else if (status != cudaSuccess) previous = -1;
+    }
+    ~DeviceGuard() {
+        if (previous >= 0) cudaSetDevice(previous);
+    }
+};
+}  // namespace
+
 extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_desc *c) {
     if (!out || !c || !c->rot_k || !c->rot_v || !c->centers_k || !c->bounds_k || !c->centers_v || !c->bounds_v)
         return TQ_ERR_ARG;
     if (c->head_dim != TQ_D || c->bits < 2 || c->bits > 4) return TQ_ERR_UNSUPPORTED;
     if (c->use_qjl && !c->qjl) return TQ_ERR_ARG;
-    TQ_CUDA_CHECK(cudaSetDevice(device));
+    DeviceGuard guard(device);
+    TQ_CUDA_CHECK(guard.status);
 
     const int kb = c->use_qjl ? c->bits - 1 : c->bits;
     const size_t M = (size_t)TQ_D * TQ_D;
@@ -160,7 +179,7 @@ extern "C" int32_t tq_ctx_create(tq_ctx **out, int32_t device, const tq_codec_de
 
 extern "C" int32_t tq_ctx_destroy(tq_ctx *ctx) {
     if (!ctx) return TQ_OK;
-    cudaSetDevice(ctx->device);
+    DeviceGuard guard(ctx->device);
     if (ctx->base) cudaFree(ctx->base);
     if (ctx->prof) {
         for (cudaEvent_t e : ctx->prof->events) cudaEventDestroy(e);

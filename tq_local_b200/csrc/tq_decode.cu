@@ -481,6 +481,7 @@ __global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned
     // (the combine kernel of a device-numbered step reads the same word: it must be complete
     // before this kernel may advance it; a host-numbered step may start polling early)
     if (seq_ptr) tq_grid_dependency_wait();
+    tq_launch_dependents();  // the next kernel of the stream may be placed while this one polls
     const unsigned seq = seq_ptr ? *seq_ptr + 1u : seq_arg;
     const unsigned target = seq * rows_per_step;
     __shared__ int s_failed;
@@ -512,6 +513,8 @@ __global__ void tq_gather_wait_kernel(const unsigned *flags, int world, unsigned
             *seq_ptr = seq;
         }
     }
+    // (a host-numbered wait began before the combine kernel was done: it ends only after it)
+    if (!seq_ptr) tq_grid_dependency_wait();
 }
 
 // The decode kernels run with the largest shared-memory carve-out.  The small kernels around

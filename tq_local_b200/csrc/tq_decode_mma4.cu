@@ -645,6 +645,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) tq_decode_mma4_kernel(Mma4Args
     ++seg_no;
     }  // segment loop
     if (timed_out && lane == 0) atomicExch(a.error_flag, 1);
+    // (a CTA without work still waits for the kernel before this one: a grid that completes must
+    // imply that everything ordered before it has completed)
+    if (first_segment) tq_grid_dependency_wait();
     TQ_STAMP(14);
 }
 

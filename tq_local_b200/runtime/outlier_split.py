@@ -294,4 +294,4 @@ class SplitStore:
             step(self.dequant("keys", lo, hi, q.dtype), self.dequant("values", lo, hi, q.dtype), lo)
         if tail_k is not None and tail_k.shape[2]:
             step(tail_k, tail_v, None)
-        return (acc / l.unsqueeze(-1)).to(q.dtype).view(b, hq, 1, d)
+        return (acc / l.clamp(min=1e-8).unsqueeze(-1)).to(q.dtype).view(b, hq, 1, d)  # (clamp: attention.py:303)

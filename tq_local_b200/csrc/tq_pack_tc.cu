@@ -110,6 +110,18 @@ __device__ __forceinline__ void split3(float v, __nv_bfloat16 &t1, __nv_bfloat16
     t2 = __float2bfloat16_rn(r1);
     t3 = __float2bfloat16_rn(r1 - __bfloat162float(t2));
 }
+// The same split for two values at a time: the conversions are packed (two floats -> one bf16x2),
+// the way back to float is a shift / a mask.  Bit-identical to split3 on each value.
+__device__ __forceinline__ void split3x2(float v0, float v1, uint32_t &t1, uint32_t &t2, uint32_t &t3) {
+    auto pack = [](float lo, float hi) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    };
+    t1 = pack(v0, v1);
+    const float r0 = v0 - __uint_as_float(t1 << 16), r1 = v1 - __uint_as_float(t1 & 0xffff0000u);
+    t2 = pack(r0, r1);
+    t3 = pack(r0 - __uint_as_float(t2 << 16), r1 - __uint_as_float(t2 & 0xffff0000u));
+}
 
 template <typename T> struct RowLoader;
 template <> struct RowLoader<float> {  // 8 floats = two 16-byte loads
@@ -295,9 +307,9 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
         const float inv = valid ? 1.0f / safe : 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
+            __align__(16) uint32_t t1[4], t2[4], t3[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) split3(x[8 * c + i] * inv, t1[i], t2[i], t3[i]);
+            for (int i = 0; i < 4; ++i) split3x2(x[8 * c + 2 * i] * inv, x[8 * c + 2 * i + 1] * inv, t1[i], t2[i], t3[i]);
             const int off = operand_offset(vrow, 32 * hsel + 8 * c);
             *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
             *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);
@@ -379,9 +391,9 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
             const float rinv = valid ? 1.0f / rsafe : 0.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
+                __align__(16) uint32_t t1[4], t2[4], t3[4];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) split3(x[8 * c + i] * rinv, t1[i], t2[i], t3[i]);
+                for (int i = 0; i < 4; ++i) split3x2(x[8 * c + 2 * i] * rinv, x[8 * c + 2 * i + 1] * rinv, t1[i], t2[i], t3[i]);
                 const int off = operand_offset(vrow, 32 * hsel + 8 * c);
                 *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
                 *reinterpret_cast<uint4 *>(a_tiles + kTermBytes + off) = *reinterpret_cast<const uint4 *>(t2);

@@ -104,6 +104,10 @@ __host__ __device__ inline int operand_offset(int row, int k) {
     return slab * kSlabBytes + (row >> 3) * 1024 + (row & 7) * 128 + (((kk >> 3) ^ (row & 7)) << 4) + (kk & 7) * 2;
 }
 
+// (low half of a, low half of b) and (high half of a, high half of b) as one word
+__device__ __forceinline__ uint32_t prmt_lo_lo(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x5410); }
+__device__ __forceinline__ uint32_t prmt_hi_hi(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x7632); }
+
 __device__ __forceinline__ void split3(float v, __nv_bfloat16 &t1, __nv_bfloat16 &t2, __nv_bfloat16 &t3) {
     t1 = __float2bfloat16_rn(v);
     const float r1 = v - __bfloat162float(t1);
@@ -121,6 +125,20 @@ __device__ __forceinline__ void split3x2(float v0, float v1, uint32_t &t1, uint3
     const float r0 = v0 - __uint_as_float(t1 << 16), r1 = v1 - __uint_as_float(t1 & 0xffff0000u);
     t2 = pack(r0, r1);
     t3 = pack(r0 - __uint_as_float(t2 << 16), r1 - __uint_as_float(t2 & 0xffff0000u));
+}
+
+// Two values rounded through the cache dtype and back (the reference's `.to(dtype).float()`), with
+// one packed conversion for both.
+template <typename T> __device__ __forceinline__ void round_through2(float &a, float &b);
+template <> __device__ __forceinline__ void round_through2<float>(float &, float &) {}
+template <> __device__ __forceinline__ void round_through2<__nv_bfloat16>(float &a, float &b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    const uint32_t u = *reinterpret_cast<const uint32_t *>(&h);
+    a = __uint_as_float(u << 16), b = __uint_as_float(u & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void round_through2<__half>(float &a, float &b) {
+    const float2 f = __half22float2(__floats2half2_rn(a, b));
+    a = f.x, b = f.y;
 }
 
 template <typename T> struct RowLoader;
@@ -172,7 +190,7 @@ template <typename T, int BITS, bool QJL>
 __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ float s_bnd[16];
-    __shared__ __align__(16) __nv_bfloat16 s_cen3[3][16];  // bf16 terms of the key centres
+    __shared__ __align__(8) uint2 s_cen3[16];  // the three bf16 terms of a key centre: x = t1 | t2 << 16, y = t3
     __shared__ __align__(8) uint64_t s_bar[2];  // [0] B operand landed, [1] MMAs of a stage done
     __shared__ uint32_t s_tmem;
     const uint32_t raw = smem_u32(smem_raw);
@@ -238,7 +256,12 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
 
     if (tid < 16) {
         s_bnd[tid] = a.bounds[tid];
-        if (QJL) split3(a.centers[tid], s_cen3[0][tid], s_cen3[1][tid], s_cen3[2][tid]);
+        if (QJL) {
+            __nv_bfloat16 c1, c2, c3;
+            split3(a.centers[tid], c1, c2, c3);
+            s_cen3[tid] = make_uint2((uint32_t)__bfloat16_as_ushort(c1) | ((uint32_t)__bfloat16_as_ushort(c2) << 16),
+                                     (uint32_t)__bfloat16_as_ushort(c3));
+        }
     }
     if (warp == 0) {  // TMEM: 128 columns of fp32 accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)),
@@ -354,14 +377,17 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
             // ---------------- stage 2: A = centres[codes] (three bf16 terms from a 2^BITS-entry table)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int bit = (8 * c + i) * BITS, w = bit >> 5, sh = bit & 31;
+                __align__(16) uint32_t t1[4], t2[4], t3[4];
+                auto code = [&](int e) {  // code of the thread's element e
+                    const int bit = e * BITS, w = bit >> 5, sh = bit & 31;
                     uint32_t idx = words[w] >> sh;
                     if (sh + BITS > 32) idx |= words[w + 1] << (32 - sh);
-                    idx &= (1u << BITS) - 1u;
-                    t1[i] = s_cen3[0][idx], t2[i] = s_cen3[1][idx], t3[i] = s_cen3[2][idx];
+                    return idx & ((1u << BITS) - 1u);
+                };
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint2 e0 = s_cen3[code(8 * c + 2 * i)], e1 = s_cen3[code(8 * c + 2 * i + 1)];
+                    t1[i] = prmt_lo_lo(e0.x, e1.x), t2[i] = prmt_hi_hi(e0.x, e1.x), t3[i] = prmt_lo_lo(e0.y, e1.y);
                 }
                 const int off = operand_offset(vrow, 32 * hsel + 8 * c);
                 *reinterpret_cast<uint4 *>(a_tiles + off) = *reinterpret_cast<const uint4 *>(t1);
@@ -379,9 +405,12 @@ __global__ void __launch_bounds__(kThreads, 1) tq_pack_tc_kernel(PackTcArgs a) {
                 uint32_t r[32];
                 tmem_ld32(my_tmem, r);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    x[i] -= tq_round_through<T>(__uint_as_float(r[i]) * nf);  // x becomes the residual
+                for (int i = 0; i < 32; i += 2) {
+                    float r0 = __uint_as_float(r[i]) * nf, r1 = __uint_as_float(r[i + 1]) * nf;
+                    round_through2<T>(r0, r1);
+                    x[i] -= r0, x[i + 1] -= r1;  // x becomes the residual
                     rs = fmaf(x[i], x[i], rs);
+                    rs = fmaf(x[i + 1], x[i + 1], rs);
                 }
             }
             s_sq[hsel][vrow] = rs;  // (its last readers passed the barrier inside the first GEMM)
